@@ -1,0 +1,134 @@
+"""The oracle is pinned against outputs of the reference's own specification functions
+(fixtures made by ``tests/golden/make_golden.py``)."""
+import zlib
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import paged_decode_oracle as O
+
+
+def crc(t):
+    return zlib.crc32(t.contiguous().view(torch.uint8).numpy().tobytes())
+
+
+def _paged_kv(kc, vc, bt, lens, head_dim, fmt, mode, ks=None, vs=None):
+    return O.PagedKV(key_cache=kc, value_cache=vc, block_tables=bt, context_lens=lens,
+                     page_size=cases.PAGE, head_dim=head_dim, k_format=fmt, v_format=fmt,
+                     k_scale_mode=mode, v_scale_mode=mode, k_scale=ks, v_scale=vs)
+
+
+@pytest.mark.parametrize("case", list(cases.paged_cases()), ids=lambda c: c[0])
+def test_paged_matches_reference(golden, case):
+    name, dtype, hd, lens = case
+    q, k, v, lens_t = cases.paged_inputs(dtype, hd, lens)
+    bt = torch.from_numpy(golden[f"{name}/bt"])
+    perm = bt.reshape(-1).to(torch.int64)
+    kc = O.paged_layout_from_dense(k, cases.PAGE, perm)
+    vc = O.paged_layout_from_dense(v, cases.PAGE, perm)
+    # inputs and the page layout are bit-identical to what the reference built
+    assert [crc(q), crc(kc), crc(vc)] == golden[f"{name}/crc"].tolist()
+    kv = _paged_kv(kc, vc, bt, lens_t, hd, O.KV_F32, O.SCALE_NONE)
+    ref = torch.from_numpy(golden[f"{name}/out"])
+    out_sdpa = O.ref_paged_decode_sdpa(q, kv)
+    assert torch.equal(out_sdpa, ref) or (out_sdpa - ref).abs().max() < 2e-6
+    out = O.ref_paged_decode(q, kv)
+    assert (out - ref).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("case", list(cases.fp8_cases()), ids=lambda c: c[0])
+def test_fp8_matches_reference(golden, case):
+    name, dtype, hd, lens = case
+    q, k, v, lens_t = cases.paged_inputs(dtype, hd, lens)
+    k8, v8, ks, vs, k_deq, v_deq = cases.fp8_quantise(k, v)
+    bt = torch.from_numpy(golden[f"{name}/bt"])
+    perm = bt.reshape(-1).to(torch.int64)
+    kc = O.paged_layout_from_dense(k8, cases.PAGE, perm)
+    vc = O.paged_layout_from_dense(v8, cases.PAGE, perm)
+    assert [crc(q), crc(kc), crc(vc), crc(ks), crc(vs)] == golden[f"{name}/crc"].tolist()
+    # E4M3 table (built from the format definition) == torch's cast on every finite code
+    kv = _paged_kv(kc, vc, bt, lens_t, hd, O.KV_FP8_E4M3, O.SCALE_PER_HEAD, ks, vs)
+    for s, L in enumerate(lens):
+        kk, vv = O.gather_sequence(kv, s)
+        assert torch.equal(kk, k_deq[s, :, :L])       # dequant + block-table gather: bit-exact
+        assert torch.equal(vv, v_deq[s, :, :L])
+    ref = torch.from_numpy(golden[f"{name}/out"])
+    out = O.ref_paged_decode(q, kv)
+    assert (out - ref).abs().max() < 1e-5
+    out_sdpa = O.ref_paged_decode_sdpa(q, kv)
+    assert (out_sdpa - ref).abs().max() < 2e-6
+
+
+@pytest.mark.parametrize("case", list(cases.decode_cases()), ids=lambda c: c[0])
+def test_decode_matches_reference(golden, case):
+    name, dtype, hd, kv_len = case
+    q, k, v = cases.decode_inputs(dtype, hd, kv_len)
+    assert [crc(q), crc(k), crc(v)] == golden[f"{name}/crc"].tolist()
+    ref = torch.from_numpy(golden[f"{name}/out"])
+    assert (O.ref_flash_decode(q, k, v) - ref).abs().max() < 2e-6
+
+
+def test_gqa_convention(golden):
+    torch.manual_seed(0)
+    q = torch.randn(2, 8, 1, 64)
+    k = torch.randn(2, 2, 77, 64)
+    v = torch.randn(2, 2, 77, 64)
+    assert [crc(q), crc(k), crc(v)] == golden["gqa_decode/crc"].tolist()
+    ref = torch.from_numpy(golden["gqa_decode/out"])            # [2,8,1,64]
+    # page the GQA case and run the oracle: kv_head = q_head // group
+    perm = torch.randperm(2 * 5)
+    kc = O.paged_layout_from_dense(k, 16, perm)
+    vc = O.paged_layout_from_dense(v, 16, perm)
+    kv = O.PagedKV(kc, vc, perm.view(2, 5).to(torch.int32), torch.tensor([77, 77], dtype=torch.int32),
+                   16, 64, O.KV_F32, O.KV_F32, O.SCALE_NONE, O.SCALE_NONE)
+    out = O.ref_paged_decode(q[:, :, 0], kv)
+    assert (out - ref[:, :, 0]).abs().max() < 1e-5
+    assert (O.ref_paged_decode_sdpa(q[:, :, 0], kv) - ref[:, :, 0]).abs().max() < 2e-6
+
+
+def test_code_tables_match_torch():
+    codes = torch.arange(256, dtype=torch.uint8)
+    t = codes.view(torch.float8_e4m3fn).float()
+    mine = torch.from_numpy(O.E4M3_TABLE)
+    fin = torch.isfinite(t)
+    assert torch.equal(mine[fin], t[fin]) and torch.isnan(mine[~fin]).all() and (~fin).sum() == 2
+    e = codes.view(torch.float8_e8m0fnu).float()
+    mine = torch.from_numpy(O.E8M0_TABLE)
+    assert torch.equal(mine[:255], e[:255]) and torch.isnan(mine[255])
+    import ml_dtypes
+    f4 = np.arange(16, dtype=np.uint8).view(ml_dtypes.float4_e2m1fn).astype(np.float32)
+    assert np.array_equal(O.E2M1_TABLE, f4)
+
+
+def test_split_merge_equals_full():
+    from cuda_b200 import workloads as W
+    wl = W.build_workload("t", context_lens=[1, 37, 200, 0, 64], q_lens=[1, 4, 1, 1, 4],
+                          num_q_heads=8, num_kv_heads=2, head_dim=64, page_size=16,
+                          q_dtype=torch.float32, scale_mode=W.SCALE_PER_TOKEN, pool_factor=1.5, seed=3)
+    kv = to_oracle(wl)
+    full, lse = O.ref_paged_decode(wl.query, kv, wl.softmax_scale, wl.cu_q_lens, return_lse=True)
+    assert torch.isfinite(full).all()
+    parts = [O.ref_paged_decode(wl.query, kv, wl.softmax_scale, wl.cu_q_lens, tok_range=r, return_lse=True)
+             for r in ((0, 48), (48, 50), (50, 130), (130, 4096))]
+    o, l = O.merge_partials(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]))
+    assert (o - full).abs().max() < 1e-5
+    fin = torch.isfinite(lse)
+    assert (l[fin] - lse[fin]).abs().max() < 1e-5 and torch.equal(torch.isfinite(l), fin)
+
+
+def to_oracle(wl):
+    return O.PagedKV(wl.key_cache, wl.value_cache, wl.block_tables, wl.context_lens, wl.page_size,
+                     wl.head_dim, wl.k_format, wl.v_format, wl.k_scale_mode, wl.v_scale_mode,
+                     wl.k_scale, wl.v_scale)
+
+
+@pytest.mark.parametrize("cfg", [1, 2, 3, 4, 5])
+def test_configs_small_are_finite_and_causal(cfg):
+    from cuda_b200 import workloads as W
+    wl = W.make_config(cfg, batch=3, ctx_scale=1 / 32)
+    kv = to_oracle(wl)
+    out = O.ref_paged_decode(wl.query, kv, wl.softmax_scale, wl.cu_q_lens)
+    assert torch.isfinite(out).all()        # poisoned tails / unused pages are never read
+    assert out.shape == wl.query.shape
