@@ -1,0 +1,339 @@
+"""Benchmark of the paged FP8 decode-attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+
+One step = one decode-attention pass over one batch of the workload (default: the
+Llama-3-8B-shaped FP8 paged decode configuration: batch 64, 32/8 heads, head_dim 128, page 16,
+context lengths U[1024, 8192], per-(token, KV-head) fp32 scales, pool 1.25x).  The metric is
+HBM throughput on the algorithmic K+V bytes (payload + scales of valid tokens only), the
+reference benchmark's own "effective KV GB/s" (benchmark_pytorch.py:160,611 in the reference
+project).  With N > 1 (torchrun, one rank per GPU) every rank holds its own batch (sequence
+sharding, no collective on the data path): weak scaling, value = all ranks' bytes / max time.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {"cfg1": 1, "cfg2": 2, "cfg3": 3, "cfg4": 4, "cfg5": 5}
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                               f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def cpu_reference_run(wl_cpu, budget_s: float, max_seqs=None):
+    """Time the CPU restatement of the reference's PyTorch path (per sequence: gather pages
+    through the block table, dequantise, scaled-dot-product attention) on the host cores.
+    Returns (seconds, kv_bytes_processed, tokens, n_seqs, max_abs_vs_none)."""
+    from oracle import paged_decode_oracle as O
+    from cuda_b200.workloads import bytes_per_token_head
+    kv = O.PagedKV(wl_cpu.key_cache, wl_cpu.value_cache, wl_cpu.block_tables, wl_cpu.context_lens,
+                   wl_cpu.page_size, wl_cpu.head_dim, wl_cpu.k_format, wl_cpu.v_format,
+                   wl_cpu.k_scale_mode, wl_cpu.v_scale_mode, wl_cpu.k_scale, wl_cpu.v_scale)
+    per = (bytes_per_token_head(wl_cpu.head_dim, wl_cpu.k_format, wl_cpu.k_scale_mode)
+           + bytes_per_token_head(wl_cpu.head_dim, wl_cpu.v_format, wl_cpu.v_scale_mode)) * wl_cpu.num_kv_heads
+    S = wl_cpu.num_seqs if max_seqs is None else min(max_seqs, wl_cpu.num_seqs)
+    cu = list(range(S + 1)) if wl_cpu.cu_q_lens is None else wl_cpu.cu_q_lens.tolist()
+    t0 = time.perf_counter()
+    done, nbytes, qtok = 0, 0, 0
+    for s in range(S):
+        sub = O.PagedKV(kv.key_cache, kv.value_cache, kv.block_tables[s:s + 1], kv.context_lens[s:s + 1],
+                        kv.page_size, kv.head_dim, kv.k_format, kv.v_format, kv.k_scale_mode,
+                        kv.v_scale_mode, kv.k_scale, kv.v_scale)
+        q = wl_cpu.query[cu[s]:cu[s + 1]]
+        if q.shape[0] == 1:
+            O.ref_paged_decode_sdpa(q, sub, wl_cpu.softmax_scale)
+        else:
+            O.ref_paged_decode(q, sub, wl_cpu.softmax_scale,
+                               torch.tensor([0, q.shape[0]], dtype=torch.int32))
+        done += 1
+        nbytes += int(wl_cpu.context_lens[s]) * per
+        qtok += q.shape[0]
+        if time.perf_counter() - t0 > budget_s:
+            break
+    return time.perf_counter() - t0, nbytes, qtok, done
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=None, help="override the batch (smaller ncu captures)")
+    ap.add_argument("--ctx-scale", type=float, default=1.0)
+    ap.add_argument("--cpu-budget-s", type=float, default=15.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true", help="only the attention-kernel loop (ncu)")
+    args = ap.parse_args()
+    rank, world, local = dist_env()
+    if args.warmup < 3:
+        args.warmup = 3
+    from cuda_b200 import workloads
+    cfg_id = WORKLOADS[args.workload]
+    seed = 1000 + cfg_id + 7919 * rank
+
+    # ------------------------------------------------------------------ reference arm (CPU)
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        ncores = os.cpu_count() or 1
+        torch.set_num_threads(ncores)
+        wl = workloads.make_config(cfg_id, "cpu", batch=args.batch or 8, ctx_scale=args.ctx_scale,
+                                   seed=seed, poison=False)
+        per_step_budget = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+        for _ in range(min(args.warmup, 1)):
+            cpu_reference_run(wl, per_step_budget)
+        tot_t, tot_b, tot_q, n = 0.0, 0, 0, 0
+        for _ in range(args.steps):
+            t, b, q, done = cpu_reference_run(wl, per_step_budget)
+            tot_t, tot_b, tot_q, n = tot_t + t, tot_b + b, tot_q + q, n + done
+        val = tot_b / tot_t / 1e12
+        line = {
+            "metric": "paged_fp8_decode_kv_hbm_throughput", "value": val, "unit": "TB/s", "impl": "reference",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": tot_t / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3->f32", "data": "synthetic",
+            "tokens_per_s": tot_q / tot_t,
+            "config": {"workload": wl.name, "sample": f"{n // max(1, args.steps)} sequences per step of a batch-"
+                       f"{wl.num_seqs} draw of the same length distribution", "heads": "32q/8kv",
+                       "head_dim": wl.head_dim, "page_size": wl.page_size},
+            "cpu_baseline": {"value": val, "unit": "TB/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": f"{n} sequences in {tot_t:.1f} s"},
+            "e2e": {"value": val, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line), flush=True)
+        return
+
+    # ------------------------------------------------------------------ our arm (GPU)
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from cuda_b200 import ops
+    ops.L.load()
+
+    wl = workloads.make_config(cfg_id, dev, batch=args.batch, ctx_scale=args.ctx_scale, seed=seed,
+                               poison=False)
+    kv_bytes = wl.kv_bytes()
+    q_tokens = wl.query.shape[0]
+    need = ops.L.load().cuda_llm_paged_decode_workspace_bytes(
+        wl.num_seqs, wl.num_q_heads, wl.num_kv_heads, wl.head_dim, wl.page_size, wl.max_q_len, 0)
+    ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+    out = torch.empty_like(wl.query)
+
+    def step(flags=0):
+        return ops.run_workload(wl, out=out, workspace=ws, flags=flags)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    st = ops.decode_status(ws)
+    assert st == 0, f"device status 0x{st:x}"
+
+    if args.kernel_only:
+        ms = timed(lambda: step(ops.L.FLAG_SKIP_MERGE), args.steps)
+        if rank == 0:
+            print(json.dumps({"kernel_only_ms": ms / args.steps, "kv_bytes": kv_bytes,
+                              "GBs": kv_bytes / (ms / args.steps) / 1e6}), flush=True)
+        return
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # (1) whole step resident in HBM: attention kernel + split merge
+    ms_total = timed(step, args.steps)
+    # (2) the dominant kernel alone (roofline numerator / denominator)
+    ms_kernel = timed(lambda: step(ops.L.FLAG_SKIP_MERGE), args.steps) / args.steps
+    step()
+    # (3) end to end through the public op with host buffers: the step's inputs (query, block
+    #     tables, context lengths, query offsets) come from pinned host memory, the result goes back
+    host_in = [t.cpu().pin_memory() for t in (wl.query, wl.block_tables, wl.context_lens)]
+    host_cu = wl.cu_q_lens.cpu().pin_memory() if wl.cu_q_lens is not None else None
+    dev_in = [torch.empty_like(t, device=dev) for t in host_in]
+    dev_cu = torch.empty_like(host_cu, device=dev) if host_cu is not None else None
+    host_out = torch.empty(wl.query.shape, dtype=wl.query.dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host_in) + (host_cu.numel() * 4 if host_cu is not None else 0)
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        for d, h in zip(dev_in, host_in):
+            d.copy_(h, non_blocking=True)
+        if dev_cu is not None:
+            dev_cu.copy_(host_cu, non_blocking=True)
+        o = ops.fp8_paged_attention_forward(dev_in[0], wl.key_cache, wl.value_cache, wl.k_scale, wl.v_scale,
+                                            dev_in[1], dev_in[2], wl.softmax_scale, cu_q_lens=dev_cu,
+                                            max_q_len=wl.max_q_len, workspace=ws)
+        host_out.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    st = ops.decode_status(ws)
+    assert st == 0, f"device status 0x{st:x}"
+
+    # totals over ranks
+    tot_bytes, tot_q = float(kv_bytes), float(q_tokens)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([tot_bytes, tot_q], device=dev, dtype=torch.float64)
+        dist.all_reduce(t)
+        tot_bytes, tot_q = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_peak()
+    ms_step = ms_total / args.steps
+    value = tot_bytes / (ms_step * 1e-3) / 1e12
+    achieved = kv_bytes / (ms_kernel * 1e-3) / 1e9
+    line = {
+        "metric": "paged_fp8_decode_kv_hbm_throughput", "value": value, "unit": "TB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3->f16 mma, f32 acc",
+        "data": "synthetic", "tokens_per_s": tot_q / (ms_step * 1e-3),
+        "pct_of_nominal_8TBs": 100.0 * value * 1e3 / (NOMINAL_HBM_GBS * world),
+        "pct_of_measured_copy_peak": 100.0 * value * 1e3 / (peak * world),
+        "config": {"workload": wl.name, "batch_per_gpu": wl.num_seqs, "heads": f"{wl.num_q_heads}q/{wl.num_kv_heads}kv",
+                   "head_dim": wl.head_dim, "page_size": wl.page_size,
+                   "kv_tokens_per_gpu": int(wl.context_lens.sum().item()), "kv_bytes_per_gpu": kv_bytes,
+                   "pool_pages": wl.meta["pool_pages"], "parallelism": f"sequence-sharded x{world}",
+                   "l2": "inputs larger than L2 (KV working set per step >> 126 MB), no flush needed"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": peak_src, "kernel": "paged_decode_kernel", "kernel_ms": ms_kernel,
+                     "traffic": None},
+        "e2e": {"value": tot_bytes / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TB/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps,
+                "note": "KV cache resident in HBM (it is decode state, like weights); per-step inputs "
+                        "(query, block tables, context lengths) from pinned host memory, output read back"},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            tj = json.load(open(traffic_file)).get(wl.name)
+            if tj:
+                line["roofline"]["traffic"] = tj["dram_bytes_per_kv_byte"] * kv_bytes
+        except Exception:
+            pass
+    if not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        t, b, q, n = cpu_reference_run(wl.to("cpu"), args.cpu_budget_s)
+        line["cpu_baseline"] = {"value": b / t / 1e12, "unit": "TB/s", "cores": torch.get_num_threads(),
+                                "kind": "port", "tokens_per_s": q / t,
+                                "sample": f"first {n} of {wl.num_seqs} sequences of the same batch, {t:.1f} s"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,95 @@
+"""In-tree build of libcuda_llm_b200.so for sm_100a.
+
+``python -m cuda_b200.build`` compiles every ``csrc/*.cu`` unit with nvcc (in parallel) and
+links them into ``cuda_b200/lib/libcuda_llm_b200.so``.  The reference builds one extension
+through ``setup.py`` with a kernel registry and an arch list (``setup.py:40-52,70-76`` in the
+reference project); this build has one target architecture and no registry.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+OBJ = os.path.join(HERE, "build")
+LIBDIR = os.path.join(HERE, "lib")
+LIB = os.path.join(LIBDIR, "libcuda_llm_b200.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-diag-suppress", "177",
+    "-I", os.path.join(ROOT, "include"), "-I", CSRC,
+]
+
+
+def _nvcc() -> str:
+    for c in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if c and os.path.exists(c):
+            return c
+    raise RuntimeError("nvcc not found")
+
+
+def _digest(paths) -> str:
+    h = hashlib.sha256()
+    for p in sorted(paths):
+        with open(p, "rb") as f:
+            h.update(p.encode())
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> str:
+    os.makedirs(OBJ, exist_ok=True)
+    os.makedirs(LIBDIR, exist_ok=True)
+    units = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    headers += [os.path.join(ROOT, "include", f) for f in os.listdir(os.path.join(ROOT, "include"))]
+    hdr_digest = _digest(headers)
+    nvcc = _nvcc()
+    jobs = []
+    for u in units:
+        src = os.path.join(CSRC, u)
+        obj = os.path.join(OBJ, u[:-3] + ".o")
+        stamp = obj + ".stamp"
+        want = _digest([src]) + hdr_digest
+        have = open(stamp).read() if os.path.exists(stamp) else ""
+        if force or have != want or not os.path.exists(obj):
+            jobs.append((src, obj, stamp, want))
+
+    def run(job):
+        src, obj, stamp, want = job
+        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+        with open(stamp, "w") as f:
+            f.write(want)
+        return src, r.stderr
+
+    if jobs:
+        workers = int(os.environ.get("MAX_JOBS", str(min(len(jobs), os.cpu_count() or 4))))
+        with ThreadPoolExecutor(max_workers=workers) as ex:
+            for src, log in ex.map(run, jobs):
+                if verbose or ptxas_info:
+                    print(f"[build] {os.path.basename(src)}\n{log}" if ptxas_info else
+                          f"[build] {os.path.basename(src)}", flush=True)
+    objs = [os.path.join(OBJ, u[:-3] + ".o") for u in units]
+    if jobs or not os.path.exists(LIB):
+        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
+                                                     "-lcudart"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    path = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    print(path)

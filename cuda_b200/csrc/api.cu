@@ -1,0 +1,293 @@
+// C ABI of libcuda_llm_b200: argument validation, shared-memory / workspace layout and
+// kernel selection for the paged decode path.  Mirrors the checks the reference binding makes
+// before it calls dispatch_fp8_paged_attention (fused_softmax_binding.cpp:645-669 in the
+// reference project) and turns the dispatcher's silent no-op on an unsupported shape
+// (fp8_paged_attention_kernel.cuh:176-190) into an error code.
+#include <cstdio>
+#include <cstring>
+#include <cmath>
+
+#include "decode_launch.cuh"
+
+namespace b200 {
+cudaError_t launch_merge_partials(const float*, const float*, int, long long, int, void*, int,
+                                  float*, cudaStream_t);
+cudaError_t launch_dequant_pages(const void*, const void*, const int32_t*, int, int, int, int, int,
+                                 int, float*, cudaStream_t);
+
+static thread_local char g_err[256] = "";
+static int fail_cuda(cudaError_t e, const char* where) {
+  snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));
+  return CUDA_LLM_ECUDA;
+}
+static int fail(int code, const char* msg) {
+  snprintf(g_err, sizeof(g_err), "%s", msg);
+  return code;
+}
+
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct Layout {
+  int HG, TS, n_hg, NT, rows_max, PPS, n_stages, grid;
+  uint32_t stage_bytes, off_v, off_ks, off_vs;
+  uint32_t k_page_stride, v_page_stride, ks_page_stride, vs_page_stride;
+  uint32_t k_chunk, v_chunk, ks_chunk, vs_chunk;
+  size_t smem_bytes;
+  // workspace
+  size_t ws_table, ws_lse, ws_o, ws_total;
+};
+
+static int sm_count_cached() {
+  static int counts[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev >= 64) dev = 63;
+  if (!counts[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    counts[dev] = n;
+  }
+  return counts[dev];
+}
+
+// Pure arithmetic (no device access when num_ctas > 0): shared-memory stage layout and
+// workspace carving for one problem shape.
+static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, int v_format,
+                       int scale_mode, int num_ctas, Layout& L) {
+  if (S < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return fail(CUDA_LLM_EINVAL, "num_q_heads must be a positive multiple of num_kv_heads");
+  if (D != 64 && D != 128) return fail(CUDA_LLM_EINVAL, "Only head_dim 64 and 128 supported");
+  if (page != 16 && page != 32 && page != 64) return fail(CUDA_LLM_EINVAL, "Only page_size 16, 32 and 64 supported");
+  const int group = Hq / Hkv;
+  if (max_q_len < 1) max_q_len = 1;
+  if (group * max_q_len > 16) return fail(CUDA_LLM_EINVAL, "(num_q_heads/num_kv_heads) * max_q_len must be <= 16");
+  L.NT = (group * max_q_len <= 8) ? 1 : 2;
+  L.rows_max = 8 * L.NT;
+  int HG = 8;
+  while (Hkv % HG) HG >>= 1;
+  if (page == 64 && HG > 4) HG = 4;  // a stage must hold whole pages: 32*TS >= page
+  L.HG = HG;
+  L.TS = 8 / HG;
+  L.n_hg = Hkv / HG;
+  L.PPS = (32 * L.TS >= page) ? 32 * L.TS / page : 1;
+  if (L.PPS > kMaxPagesPerStage) return fail(CUDA_LLM_EINVAL, "internal: too many pages per stage");
+  const uint32_t pad = (page == 16) ? 64u : 0u;  // keeps the two pages of a sub-tile on different banks
+  const int DV = (v_format == CUDA_LLM_KV_FP4_E2M1) ? D / 2 : D;
+  L.k_chunk = (uint32_t)HG * D * page;
+  L.v_chunk = (uint32_t)HG * DV * page;
+  if (scale_mode == CUDA_LLM_SCALE_PER_TOKEN) L.ks_chunk = L.vs_chunk = (uint32_t)HG * page * 4;
+  else if (scale_mode == CUDA_LLM_SCALE_MX_E8M0) L.ks_chunk = L.vs_chunk = (uint32_t)HG * (D / 32) * page;
+  else L.ks_chunk = L.vs_chunk = 0;
+  L.k_page_stride = L.k_chunk + pad;
+  L.v_page_stride = L.v_chunk + pad;
+  L.ks_page_stride = L.ks_chunk;
+  L.vs_page_stride = L.vs_chunk;
+  L.off_v = L.PPS * L.k_page_stride;
+  L.off_ks = L.off_v + L.PPS * L.v_page_stride;
+  L.off_vs = L.off_ks + L.PPS * L.ks_page_stride;
+  L.stage_bytes = (uint32_t)align_up(L.off_vs + L.PPS * L.vs_page_stride, 128);
+  const uint32_t stages_off = 256 + kMaxStages * sizeof(StageMeta);
+  int ns = (int)((kSmemBudget - stages_off) / L.stage_bytes);
+  if (ns > kMaxStages) ns = kMaxStages;
+  if (ns < 2) return fail(CUDA_LLM_EINVAL, "internal: stage does not fit in shared memory twice");
+  L.n_stages = ns;
+  L.smem_bytes = stages_off + (size_t)ns * L.stage_bytes;
+  if (L.smem_bytes < stages_off + kDecodeThreads * 8) L.smem_bytes = stages_off + kDecodeThreads * 8;
+  if (num_ctas <= 0) num_ctas = sm_count_cached();
+  if (num_ctas <= 0) return fail(CUDA_LLM_ECUDA, "cannot query the SM count");
+  L.grid = num_ctas;
+  const size_t n_slots = (size_t)S * L.n_hg + L.grid;
+  const size_t rows = n_slots * L.TS * L.HG * L.rows_max;
+  L.ws_table = 256;
+  L.ws_lse = align_up(L.ws_table + (size_t)S * L.n_hg * 16, 256);
+  L.ws_o = align_up(L.ws_lse + rows * 4, 256);
+  L.ws_total = align_up(L.ws_o + rows * D * 4, 256);
+  return CUDA_LLM_OK;
+}
+
+using LaunchFn = cudaError_t (*)(const DecodeArgs&, int, size_t, cudaStream_t);
+
+template <int D, int MODE>
+static LaunchFn pick_page_nt(int page, int NT, bool precise) {
+#define B200_PICK(P)                                                             \
+  if (page == P) {                                                               \
+    if (NT == 2) return launch_paged_decode<D, P, MODE, 2, false>;               \
+    return precise ? launch_paged_decode<D, P, MODE, 1, true>                    \
+                   : launch_paged_decode<D, P, MODE, 1, false>;                  \
+  }
+  B200_PICK(16)
+  B200_PICK(32)
+  B200_PICK(64)
+#undef B200_PICK
+  return nullptr;
+}
+template <int MODE>
+static LaunchFn pick_d(int D, int page, int NT, bool precise) {
+  return D == 64 ? pick_page_nt<64, MODE>(page, NT, precise) : pick_page_nt<128, MODE>(page, NT, precise);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char* cuda_llm_last_cuda_error(void) { return g_err; }
+const char* cuda_llm_version(void) { return "cuda_llm_b200 0.1 (sm_100a)"; }
+
+size_t cuda_llm_paged_decode_workspace_bytes(int32_t num_seqs, int32_t num_q_heads,
+                                             int32_t num_kv_heads, int32_t head_dim,
+                                             int32_t page_size, int32_t max_q_len,
+                                             int32_t num_ctas) {
+  Layout L;
+  // the workspace does not depend on the formats
+  if (make_layout(num_seqs, num_q_heads, num_kv_heads, head_dim, page_size, max_q_len,
+                  CUDA_LLM_KV_FP8_E4M3, CUDA_LLM_SCALE_PER_TOKEN, num_ctas, L) != CUDA_LLM_OK)
+    return 0;
+  return L.ws_total;
+}
+
+int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
+  if (!p) return fail(CUDA_LLM_EINVAL, "params is null");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (p->num_seqs == 0) return CUDA_LLM_OK;
+  if (!p->query || !p->key_cache || !p->value_cache || !p->block_tables || !p->context_lens || !p->out)
+    return fail(CUDA_LLM_EINVAL, "a required tensor pointer is null");
+  if (!p->k_scale || !p->v_scale) return fail(CUDA_LLM_EINVAL, "scale tensors are required for a quantised cache");
+  if (p->k_format != CUDA_LLM_KV_FP8_E4M3)
+    return fail(CUDA_LLM_EINVAL, "K must be FP8-E4M3 (the int8 reading of the reference kernel is not provided)");
+  if (p->v_format != CUDA_LLM_KV_FP8_E4M3 && p->v_format != CUDA_LLM_KV_FP4_E2M1)
+    return fail(CUDA_LLM_EINVAL, "V must be FP8-E4M3 or FP4-E2M1");
+  if (p->v_format == CUDA_LLM_KV_FP4_E2M1 && p->scale_mode != CUDA_LLM_SCALE_MX_E8M0)
+    return fail(CUDA_LLM_EINVAL, "FP4 V needs E8M0 block scales");
+  if (p->scale_mode < 0 || p->scale_mode > CUDA_LLM_SCALE_MX_E8M0) return fail(CUDA_LLM_EINVAL, "unknown scale_mode");
+  if (p->q_dtype < 0 || p->q_dtype > CUDA_LLM_BF16 || p->out_dtype < 0 || p->out_dtype > CUDA_LLM_BF16)
+    return fail(CUDA_LLM_EINVAL, "unknown dtype");
+  if (p->max_blocks_per_seq <= 0 || p->num_blocks <= 0) return fail(CUDA_LLM_EINVAL, "max_blocks_per_seq and num_blocks must be positive");
+  const uintptr_t al = (uintptr_t)p->key_cache | (uintptr_t)p->value_cache | (uintptr_t)p->k_scale |
+                       (uintptr_t)p->v_scale | (uintptr_t)p->workspace;
+  if (al & 15) return fail(CUDA_LLM_EALIGN, "caches, scales and workspace must be 16-byte aligned");
+
+  Layout L;
+  int rc = make_layout(p->num_seqs, p->num_q_heads, p->num_kv_heads, p->head_dim, p->page_size,
+                       p->max_q_len, p->v_format, p->scale_mode, p->num_ctas, L);
+  if (rc != CUDA_LLM_OK) return rc;
+  if (!p->workspace || p->workspace_bytes < L.ws_total)
+    return fail(CUDA_LLM_EWORKSPACE, "workspace missing or smaller than cuda_llm_paged_decode_workspace_bytes()");
+
+  const int D = p->head_dim, page = p->page_size, Hkv = p->num_kv_heads;
+  const int DV = (p->v_format == CUDA_LLM_KV_FP4_E2M1) ? D / 2 : D;
+  DecodeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.q = p->query;
+  a.kc = (const uint8_t*)p->key_cache;
+  a.vc = (const uint8_t*)p->value_cache;
+  a.ks = (const uint8_t*)p->k_scale;
+  a.vs = (const uint8_t*)p->v_scale;
+  a.bt = p->block_tables;
+  a.ctx = p->context_lens;
+  a.cuq = p->cu_q_lens;
+  a.out = p->out;
+  a.lse = p->lse;
+  uint8_t* ws = (uint8_t*)p->workspace;
+  a.status = (uint32_t*)ws;
+  a.table = (int32_t*)(ws + L.ws_table);
+  a.part_lse = (float*)(ws + L.ws_lse);
+  a.part_o = (float*)(ws + L.ws_o);
+  a.S = p->num_seqs;
+  a.Hq = p->num_q_heads;
+  a.Hkv = Hkv;
+  a.group = p->num_q_heads / Hkv;
+  a.max_blocks = p->max_blocks_per_seq;
+  a.num_blocks = p->num_blocks;
+  a.HG = L.HG;
+  a.TS = L.TS;
+  a.n_hg = L.n_hg;
+  a.rows_max = L.rows_max;
+  a.q_dtype = p->q_dtype;
+  a.out_dtype = p->out_dtype;
+  a.per_block = (p->scale_mode == CUDA_LLM_SCALE_PER_BLOCK);
+  a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  a.n_stages = L.n_stages;
+  a.stage_bytes = L.stage_bytes;
+  a.off_v = L.off_v;
+  a.off_ks = L.off_ks;
+  a.off_vs = L.off_vs;
+  a.k_page_stride = L.k_page_stride;
+  a.v_page_stride = L.v_page_stride;
+  a.ks_page_stride = L.ks_page_stride;
+  a.vs_page_stride = L.vs_page_stride;
+  a.k_chunk = L.k_chunk;
+  a.v_chunk = L.v_chunk;
+  a.ks_chunk = L.ks_chunk;
+  a.vs_chunk = L.vs_chunk;
+  a.k_blk_stride = (uint64_t)Hkv * D * page;
+  a.v_blk_stride = (uint64_t)Hkv * DV * page;
+  if (p->scale_mode == CUDA_LLM_SCALE_PER_TOKEN) a.ks_blk_stride = a.vs_blk_stride = (uint64_t)Hkv * page * 4;
+  else if (p->scale_mode == CUDA_LLM_SCALE_MX_E8M0) a.ks_blk_stride = a.vs_blk_stride = (uint64_t)Hkv * (D / 32) * page;
+
+  const bool precise = (p->q_dtype == CUDA_LLM_F32) && L.NT == 1;
+  LaunchFn fn = nullptr;
+  if (p->scale_mode == CUDA_LLM_SCALE_PER_HEAD || p->scale_mode == CUDA_LLM_SCALE_PER_BLOCK)
+    fn = pick_d<MODE_PAGE_SCALE>(D, page, L.NT, precise);
+  else if (p->scale_mode == CUDA_LLM_SCALE_PER_TOKEN)
+    fn = pick_d<MODE_TOKEN_SCALE>(D, page, L.NT, precise);
+  else if (p->v_format == CUDA_LLM_KV_FP4_E2M1)
+    fn = pick_d<MODE_MX8K_MX4V>(D, page, L.NT, precise);
+  else
+    fn = pick_d<MODE_MX8>(D, page, L.NT, precise);
+  if (!fn) return fail(CUDA_LLM_EINVAL, "no kernel for this shape");
+
+  cudaError_t e = fn(a, L.grid, L.smem_bytes, st);
+  if (e != cudaSuccess) return fail_cuda(e, "paged_decode_kernel launch");
+  if (p->flags & CUDA_LLM_FLAG_SKIP_MERGE) return CUDA_LLM_OK;
+  e = (D == 64) ? launch_merge_splits<64>(a, page, st) : launch_merge_splits<128>(a, page, st);
+  if (e != cudaSuccess) return fail_cuda(e, "merge_splits_kernel launch");
+  return CUDA_LLM_OK;
+}
+
+int cuda_llm_decode_status(void* workspace, void* stream, uint32_t* status_out) {
+  if (!workspace || !status_out) return fail(CUDA_LLM_EINVAL, "null argument");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(status_out, workspace, 4, cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) return fail_cuda(e, "status copy");
+  e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail_cuda(e, "status sync");
+  if (*status_out) {
+    e = cudaMemsetAsync(workspace, 0, 4, st);
+    if (e != cudaSuccess) return fail_cuda(e, "status clear");
+  }
+  return CUDA_LLM_OK;
+}
+
+int cuda_llm_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < 256) return fail(CUDA_LLM_EWORKSPACE, "workspace missing or too small");
+  cudaError_t e = cudaMemsetAsync(workspace, 0, 256, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "workspace init");
+}
+
+int cuda_llm_dequant_pages(const void* cache, const void* scale, const int32_t* pages,
+                           int32_t n_pages, int32_t num_kv_heads, int32_t head_dim,
+                           int32_t page_size, int32_t format, int32_t scale_mode, float* out,
+                           void* stream) {
+  if (!cache || !scale || !pages || !out) return fail(CUDA_LLM_EINVAL, "null argument");
+  if (head_dim % 32 || page_size <= 0 || num_kv_heads <= 0 || n_pages < 0) return fail(CUDA_LLM_EINVAL, "bad dimensions");
+  if (format != CUDA_LLM_KV_FP8_E4M3 && format != CUDA_LLM_KV_FP4_E2M1) return fail(CUDA_LLM_EINVAL, "unknown format");
+  if (scale_mode < 0 || scale_mode > CUDA_LLM_SCALE_MX_E8M0) return fail(CUDA_LLM_EINVAL, "unknown scale_mode");
+  cudaError_t e = launch_dequant_pages(cache, scale, pages, n_pages, num_kv_heads, head_dim, page_size,
+                                       format, scale_mode, out, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "dequant_pages_kernel launch");
+}
+
+int cuda_llm_merge_partials(const float* parts_out, const float* parts_lse, int32_t num_parts,
+                            int64_t rows, int32_t head_dim, void* out, int32_t out_dtype,
+                            float* lse, void* stream) {
+  if (!parts_out || !parts_lse || !out) return fail(CUDA_LLM_EINVAL, "null argument");
+  if (head_dim != 64 && head_dim != 128) return fail(CUDA_LLM_EINVAL, "Only head_dim 64 and 128 supported");
+  if (num_parts < 1 || rows < 0) return fail(CUDA_LLM_EINVAL, "num_parts >= 1 and rows >= 0 required");
+  if (out_dtype < 0 || out_dtype > CUDA_LLM_BF16) return fail(CUDA_LLM_EINVAL, "unknown dtype");
+  cudaError_t e = launch_merge_partials(parts_out, parts_lse, num_parts, rows, head_dim, out,
+                                        out_dtype, lse, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "merge_partials_kernel launch");
+}
+
+}  // extern "C"

@@ -1,0 +1,67 @@
+// Split merge kernel launches and the stand-alone partial merge used after the all-gather of
+// the split-context mode.
+#include "decode_launch.cuh"
+
+namespace b200 {
+
+template <int D>
+cudaError_t launch_merge_splits(const DecodeArgs& a, int page, cudaStream_t st) {
+  const long long warps = (long long)a.S * a.Hq;
+  if (warps == 0) return cudaSuccess;
+  const int grid = (int)((warps + 3) / 4);
+  merge_splits_kernel<D><<<grid, 128, 0, st>>>(a, page);
+  return cudaGetLastError();
+}
+template cudaError_t launch_merge_splits<64>(const DecodeArgs&, int, cudaStream_t);
+template cudaError_t launch_merge_splits<128>(const DecodeArgs&, int, cudaStream_t);
+
+// parts_out [P, rows, D] fp32, parts_lse [P, rows] natural log.  One warp per row.
+template <int D>
+__global__ void __launch_bounds__(128)
+merge_partials_kernel(const float* __restrict__ parts_out, const float* __restrict__ parts_lse,
+                      int num_parts, long long rows, void* out, int out_dtype, float* lse) {
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  constexpr int VPL = D / 32;
+  constexpr float LOG2E = 1.4426950408889634f;
+  float mx = -__builtin_huge_valf();
+  for (int p = lane; p < num_parts; p += 32) mx = fmaxf(mx, parts_lse[(size_t)p * rows + row]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  const float mu = (mx == -__builtin_huge_valf()) ? 0.f : mx;
+  float acc[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) acc[v] = 0.f;
+  float wsum = 0.f;
+  for (int p = 0; p < num_parts; ++p) {
+    const float w = fast_exp2((parts_lse[(size_t)p * rows + row] - mu) * LOG2E);
+    if (w > 0.f) {
+      wsum += w;
+      const float* po = parts_out + ((size_t)p * rows + row) * D + lane * VPL;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) acc[v] = fmaf(w, po[v], acc[v]);
+    }
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+#pragma unroll
+  for (int v = 0; v < VPL; ++v)
+    store_out_elem(out, out_dtype, (size_t)row * D + lane * VPL + v, acc[v] * inv);
+  if (lse && lane == 0) lse[row] = wsum > 0.f ? mu + logf(wsum) : -__builtin_huge_valf();
+}
+
+cudaError_t launch_merge_partials(const float* parts_out, const float* parts_lse, int num_parts,
+                                  long long rows, int head_dim, void* out, int out_dtype,
+                                  float* lse, cudaStream_t st) {
+  if (rows == 0) return cudaSuccess;
+  const int grid = (int)((rows + 3) / 4);
+  if (head_dim == 64)
+    merge_partials_kernel<64><<<grid, 128, 0, st>>>(parts_out, parts_lse, num_parts, rows, out,
+                                                    out_dtype, lse);
+  else
+    merge_partials_kernel<128><<<grid, 128, 0, st>>>(parts_out, parts_lse, num_parts, rows, out,
+                                                     out_dtype, lse);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

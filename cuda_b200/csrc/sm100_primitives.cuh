@@ -1,0 +1,155 @@
+// Device primitives for sm_100a used by the paged decode kernels: mbarrier with bounded
+// waits, 1-D bulk (TMA) global->shared copies, warp-level f16 MMA, E4M3 -> f16
+// conversion and byte shuffles.
+//
+// Every wait in this file gives up after a fixed number of polls and reports failure to
+// its caller instead of spinning forever; callers turn that into a status word the host
+// reads (the reference's only wait primitive spins without bound,
+// cuda_compat.h:174-193 in the reference project).
+#pragma once
+#include <cstdint>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace b200 {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ----------------------------------------------------------------------------------------
+// mbarrier
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false after kMaxPolls unsuccessful polls (each poll may itself suspend for
+// a hardware-defined time, so the bound is of the order of a second).
+constexpr uint32_t kMaxPolls = 1u << 22;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+
+// ----------------------------------------------------------------------------------------
+// 1-D bulk copy global -> shared, completion counted on an mbarrier (bytes).
+// Both addresses 16-byte aligned, size a multiple of 16.
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// ----------------------------------------------------------------------------------------
+// Shared-memory loads
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+
+// ----------------------------------------------------------------------------------------
+// Byte permute and conversions
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+// two E4M3 bytes (low 16 bits of x) -> f16x2; low byte -> low half.  Exact for every code.
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2_lo(uint32_t x) {
+  uint32_t d;
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}"
+      : "=r"(d) : "r"(x));
+  return d;
+}
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2_hi(uint32_t x) {
+  uint32_t d;
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, hi;\n\t}"
+      : "=r"(d) : "r"(x));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// E8M0 byte -> fp32 2^(e-127).  0 -> 2^-127 (fp32 subnormal), 255 -> NaN.
+__device__ __forceinline__ float e8m0_to_f32(uint32_t e) {
+  uint32_t bits = (e == 0u) ? 0x00400000u : (e == 255u ? 0x7fc00000u : (e << 23));
+  return __uint_as_float(bits);
+}
+
+// ----------------------------------------------------------------------------------------
+// Warp MMA m16n8k16, f16 inputs, fp32 accumulate:  D(16x8) += A(16x16) * B(16x8)
+// Fragment ownership (g = lane/4, t = lane%4):
+//   a0:(row g,   k 2t..2t+1)  a1:(row g+8, k 2t..2t+1)  a2:(row g, k 2t+8..9)  a3:(row g+8, k 2t+8..9)
+//   b0:(k 2t..2t+1, col g)    b1:(k 2t+8..9, col g)
+//   c0:(row g, col 2t) c1:(row g, col 2t+1) c2:(row g+8, col 2t) c3:(row g+8, col 2t+1)
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                        uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 8x8 b16 transpose across the warp: thread (g,t) gives row g cols 2t..2t+1 and receives
+// {M[2t][g], M[2t+1][g]}.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+
+}  // namespace b200

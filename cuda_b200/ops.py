@@ -1,0 +1,212 @@
+"""Host-side mirror of the reference's Python entry points for the decode path.
+
+Signatures follow the reference binding (module ``fused_online_softmax_cuda``,
+``fused_softmax_binding.cpp`` in the reference project):
+
+* ``paged_attention_forward(query, key_cache, value_cache, block_tables, context_lens,
+  softmax_scale=None)``                                             binding ``:109-173``
+* ``fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, v_scale,
+  block_tables, context_lens, softmax_scale=None)``                 binding ``:634-718``
+* ``async_flash_decode(q, k, v, softmax_scale=None)``               binding ``:308-360``
+
+and raise ``RuntimeError`` with the reference's messages where the reference's ``TORCH_CHECK``s
+fire.  Capabilities the reference does not have (GQA at decode, per-token / microscaling
+scales, page sizes 32 and 64, q_len > 1, returned log-sum-exp) are keyword-only extensions.
+All compute happens in libcuda_llm_b200.so; torch supplies device memory and the stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+
+_DTYPE = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}
+_workspaces = {}
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def get_workspace(device, nbytes: int) -> torch.Tensor:
+    """A zero-initialised, per-(device, stream) scratch buffer that only grows."""
+    key = (torch.device(device).index, _stream_ptr(device))
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        L.check(L.load().cuda_llm_workspace_init(ws.data_ptr(), ws.numel(), _stream_ptr(device)),
+                "cuda_llm_workspace_init")
+        _workspaces[key] = ws
+    return ws
+
+
+def _scale_mode(k_scale: torch.Tensor) -> int:
+    if k_scale.dtype in (torch.uint8, getattr(torch, "float8_e8m0fnu", torch.uint8)):
+        if k_scale.dim() != 4:
+            raise RuntimeError("E8M0 scales must be 4D [num_blocks, num_kv_heads, head_dim/32, page_size]")
+        return L.SCALE_MX_E8M0
+    if k_scale.dim() == 1:
+        return L.SCALE_PER_HEAD
+    if k_scale.dim() == 2:
+        return L.SCALE_PER_BLOCK       # reference: per_block_scales = (k_scale.dim() == 2)
+    if k_scale.dim() == 3:
+        return L.SCALE_PER_TOKEN
+    raise RuntimeError("Scale tensors must be 1D [heads], 2D [blocks, heads], 3D [blocks, heads, page] "
+                       "or 4D E8M0 [blocks, heads, head_dim/32, page]")
+
+
+def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, v_scale,
+                                block_tables, context_lens, softmax_scale=None, *,
+                                cu_q_lens: Optional[torch.Tensor] = None, max_q_len: int = 1,
+                                return_lse: bool = False, out: Optional[torch.Tensor] = None,
+                                workspace: Optional[torch.Tensor] = None, num_ctas: int = 0,
+                                check_status: bool = False, flags: int = 0):
+    """Decode attention over a paged FP8 / MXFP8 / MXFP4 KV cache.
+
+    query ``[total_q, Hq, D]``; caches ``[num_blocks, Hkv, D, page]`` bytes (V may be packed
+    E2M1 ``[num_blocks, Hkv, D/2, page]`` with E8M0 scales); ``Hkv = cache.shape[1]`` may be
+    smaller than ``Hq`` (GQA: kv_head = q_head // (Hq // Hkv), the rule of
+    ``fused_gqa_kernel.cuh:39-41`` in the reference project).  Bytes are E4M3 codes: this is
+    the semantics the reference's own test specifies (``tests/test_kernels_misc.py:42-64``),
+    not the int8 cast its kernel performs.
+    """
+    if not (query.is_cuda and key_cache_fp8.is_cuda and value_cache_fp8.is_cuda):
+        raise RuntimeError("Inputs must be on CUDA")
+    if not (k_scale.is_cuda and v_scale.is_cuda):
+        raise RuntimeError("Scale tensors must be on CUDA")
+    if not (block_tables.is_cuda and context_lens.is_cuda):
+        raise RuntimeError("Metadata tensors must be on CUDA")
+    if query.dim() != 3:
+        raise RuntimeError("Query must be 3D [num_seqs, num_heads, head_dim]")
+    if key_cache_fp8.dim() != 4 or value_cache_fp8.dim() != 4:
+        raise RuntimeError("KV caches must be 4D [num_blocks, num_heads, head_dim, page_size]")
+    byte_types = (torch.int8, torch.uint8, torch.float8_e4m3fn)
+    if key_cache_fp8.dtype not in byte_types or value_cache_fp8.dtype not in byte_types:
+        raise RuntimeError("KV caches must be 8-bit quantized (int8 or uint8)")
+    if query.dtype not in _DTYPE:
+        raise RuntimeError("Unsupported query scalar type for FP8 PagedAttention. "
+                           "Supported: Float32, Float16, BFloat16.")
+    total_q, hq, d = query.shape
+    nb, hkv, dk, page = key_cache_fp8.shape
+    if d not in (64, 128):
+        raise RuntimeError("Only head_dim 64 and 128 supported")
+    if page not in (16, 32, 64):
+        raise RuntimeError("Only page_size 16, 32 and 64 are supported")
+    if dk != d:
+        raise RuntimeError("key cache head_dim does not match the query")
+    if value_cache_fp8.shape[2] == d:
+        v_format = L.KV_FP8_E4M3
+    elif value_cache_fp8.shape[2] * 2 == d:
+        v_format = L.KV_FP4_E2M1
+    else:
+        raise RuntimeError("value cache head_dim does not match the query")
+    if hq % hkv:
+        raise RuntimeError("num_heads must be a multiple of the cache's num_kv_heads")
+    if block_tables.dtype != torch.int32 or context_lens.dtype != torch.int32:
+        raise RuntimeError("block_tables and context_lens must be int32")
+    num_seqs = context_lens.shape[0]
+    if cu_q_lens is None and total_q != num_seqs:
+        raise RuntimeError("query has more rows than sequences: pass cu_q_lens")
+    for t, name in ((query, "query"), (key_cache_fp8, "key_cache"), (value_cache_fp8, "value_cache"),
+                    (block_tables, "block_tables"), (context_lens, "context_lens")):
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    mode = _scale_mode(k_scale)
+    if mode != L.SCALE_MX_E8M0:
+        # the reference converts scales to fp32 contiguous temporaries (binding :680-681)
+        k_scale = k_scale.to(torch.float32).contiguous()
+        v_scale = v_scale.to(torch.float32).contiguous()
+    else:
+        k_scale = k_scale.contiguous()
+        v_scale = v_scale.contiguous()
+    scale = 1.0 / math.sqrt(d) if softmax_scale is None else float(softmax_scale)
+
+    lib = L.load()
+    with torch.cuda.device(query.device):
+        if out is None:
+            out = torch.empty_like(query)                        # reference: empty_like(query)
+        lse = torch.empty(total_q, hq, dtype=torch.float32, device=query.device) if return_lse else None
+        need = lib.cuda_llm_paged_decode_workspace_bytes(num_seqs, hq, hkv, d, page, max_q_len, num_ctas)
+        if need == 0:
+            raise L.CudaLlmError(L.EINVAL, "cuda_llm_paged_decode_workspace_bytes")
+        ws = workspace if workspace is not None else get_workspace(query.device, need)
+        p = L.PagedDecodeParams(
+            query=query.data_ptr(), key_cache=key_cache_fp8.data_ptr(),
+            value_cache=value_cache_fp8.data_ptr(), k_scale=k_scale.data_ptr(),
+            v_scale=v_scale.data_ptr(), block_tables=block_tables.data_ptr(),
+            context_lens=context_lens.data_ptr(), cu_q_lens=_ptr(cu_q_lens), out=out.data_ptr(),
+            lse=_ptr(lse), workspace=ws.data_ptr(), workspace_bytes=ws.numel(),
+            num_seqs=num_seqs, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page,
+            max_blocks_per_seq=block_tables.shape[1], num_blocks=nb, max_q_len=max_q_len,
+            q_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[out.dtype], k_format=L.KV_FP8_E4M3,
+            v_format=v_format, scale_mode=mode, softmax_scale=scale, num_ctas=num_ctas, flags=flags)
+        L.check(lib.cuda_llm_paged_decode(C.byref(p), _stream_ptr(query.device)), "cuda_llm_paged_decode")
+        if check_status:
+            st = decode_status(ws, query.device)
+            if st:
+                raise RuntimeError(f"paged decode reported device status 0x{st:x}")
+    return (out, lse) if return_lse else out
+
+
+def decode_status(workspace: torch.Tensor, device=None) -> int:
+    """Read and clear the device status word (synchronises the current stream)."""
+    device = workspace.device if device is None else device
+    st = C.c_uint32(0)
+    L.check(L.load().cuda_llm_decode_status(workspace.data_ptr(), _stream_ptr(device), C.byref(st)),
+            "cuda_llm_decode_status")
+    return int(st.value)
+
+
+def merge_partials(parts_out: torch.Tensor, parts_lse: torch.Tensor, out_dtype=torch.float32,
+                   return_lse: bool = False):
+    """parts_out [P, ..., D] fp32, parts_lse [P, ...] -> merged [..., D] (and lse [...])."""
+    if not parts_out.is_cuda:
+        raise RuntimeError("Inputs must be on CUDA")
+    parts_out = parts_out.contiguous().float()
+    parts_lse = parts_lse.contiguous().float()
+    P, d = parts_out.shape[0], parts_out.shape[-1]
+    rows = parts_lse[0].numel()
+    with torch.cuda.device(parts_out.device):
+        out = torch.empty(parts_out.shape[1:], dtype=out_dtype, device=parts_out.device)
+        lse = torch.empty(parts_lse.shape[1:], dtype=torch.float32, device=parts_out.device) if return_lse else None
+        L.check(L.load().cuda_llm_merge_partials(parts_out.data_ptr(), parts_lse.data_ptr(), P, rows, d,
+                                                 out.data_ptr(), _DTYPE[out_dtype], _ptr(lse),
+                                                 _stream_ptr(parts_out.device)), "cuda_llm_merge_partials")
+    return (out, lse) if return_lse else out
+
+
+def dequant_pages(cache: torch.Tensor, scale: torch.Tensor, pages: torch.Tensor, head_dim: int,
+                  fmt: int, scale_mode: int) -> torch.Tensor:
+    """fp32 [n, Hkv, D, page] of the listed pages (bit-exact decode of the stored codes)."""
+    nb, hkv, _, page = cache.shape
+    pages = pages.to(torch.int32).contiguous()
+    with torch.cuda.device(cache.device):
+        out = torch.empty(pages.numel(), hkv, head_dim, page, dtype=torch.float32, device=cache.device)
+        L.check(L.load().cuda_llm_dequant_pages(cache.data_ptr(), scale.data_ptr(), pages.data_ptr(),
+                                                pages.numel(), hkv, head_dim, page, fmt, scale_mode,
+                                                out.data_ptr(), _stream_ptr(cache.device)),
+                "cuda_llm_dequant_pages")
+    return out
+
+
+_FMT = {"fp8_e4m3": L.KV_FP8_E4M3, "fp4_e2m1": L.KV_FP4_E2M1}
+_MODE = {"per_head": L.SCALE_PER_HEAD, "per_block": L.SCALE_PER_BLOCK, "per_token": L.SCALE_PER_TOKEN,
+         "mx_e8m0": L.SCALE_MX_E8M0}
+
+
+def run_workload(wl, *, return_lse=False, out=None, num_ctas=0, check_status=False, workspace=None,
+                 flags=0):
+    """Run a ``workloads.DecodeWorkload`` through ``fp8_paged_attention_forward``."""
+    return fp8_paged_attention_forward(
+        wl.query, wl.key_cache, wl.value_cache, wl.k_scale, wl.v_scale, wl.block_tables,
+        wl.context_lens, wl.softmax_scale, cu_q_lens=wl.cu_q_lens, max_q_len=wl.max_q_len,
+        return_lse=return_lse, out=out, num_ctas=num_ctas, check_status=check_status,
+        workspace=workspace, flags=flags)

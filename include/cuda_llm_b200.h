@@ -1,0 +1,135 @@
+/* C ABI of the B200 paged decode-attention library (libcuda_llm_b200.so).
+ *
+ * Every entry point takes plain device pointers and sizes, launches asynchronously on the
+ * stream it is given, and returns 0 on success or a negative CUDA_LLM_E* code.  Nothing here
+ * traps, asserts or aborts; faults a kernel detects at run time (a block-table entry out of
+ * range, a wait that ran out) are recorded in a status word inside the workspace and read
+ * with cuda_llm_decode_status().
+ *
+ * Reference interfaces these replace (paths in the reference project):
+ *   kernels_api.h:35-41    dispatch_paged_attention<T>
+ *   kernels_api.h:58-62    dispatch_async_flash_decode<T>
+ *   kernels_api.h:94-101   dispatch_fp8_paged_attention<T_OUT,T_Q>
+ * The reference dispatchers return void and silently launch nothing for an unsupported shape
+ * (paged_attention_kernel.cuh:169-181); these return an error code instead.
+ */
+#ifndef CUDA_LLM_B200_H_
+#define CUDA_LLM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error codes ---------------------------------------------------------------------- */
+#define CUDA_LLM_OK 0
+#define CUDA_LLM_EINVAL (-1)     /* bad argument (null pointer, unsupported shape/format)   */
+#define CUDA_LLM_EALIGN (-2)     /* a pointer is not 16-byte aligned                         */
+#define CUDA_LLM_EWORKSPACE (-3) /* workspace missing or too small                           */
+#define CUDA_LLM_ECUDA (-4)      /* a CUDA runtime call failed; see cuda_llm_last_cuda_error */
+#define CUDA_LLM_EDEVICE (-5)    /* not an sm_100 device                                     */
+
+/* bits of the device status word */
+#define CUDA_LLM_ST_BAD_BLOCK 1u   /* block-table entry outside [0, num_blocks)              */
+#define CUDA_LLM_ST_BAD_CTX 2u     /* context length exceeds max_blocks_per_seq * page_size  */
+#define CUDA_LLM_ST_TIMEOUT 4u     /* a bounded wait gave up                                 */
+#define CUDA_LLM_ST_BAD_QLEN 8u    /* group * q_len exceeds the rows the launch was sized for */
+
+/* bits of CudaLlmPagedDecodeParams.flags */
+#define CUDA_LLM_FLAG_SKIP_MERGE 1 /* launch the attention kernel only (profiling: sequences
+                                      that were split across CTAs are left unmerged)         */
+
+/* ---- enums ---------------------------------------------------------------------------- */
+enum CudaLlmDType { CUDA_LLM_F32 = 0, CUDA_LLM_F16 = 1, CUDA_LLM_BF16 = 2 };
+
+enum CudaLlmKvFormat {
+  CUDA_LLM_KV_FP8_E4M3 = 0, /* uint8 [num_blocks, Hkv, D,   page]                            */
+  CUDA_LLM_KV_FP4_E2M1 = 1, /* uint8 [num_blocks, Hkv, D/2, page], low nibble = even d (V only) */
+  CUDA_LLM_KV_INT8 = 2      /* reference's integer reading of the byte (fp8_paged_attention_kernel.cuh:102) */
+};
+
+enum CudaLlmScaleMode {
+  CUDA_LLM_SCALE_PER_HEAD = 0,  /* fp32 [Hkv]                                                */
+  CUDA_LLM_SCALE_PER_BLOCK = 1, /* fp32 [num_blocks, Hkv]   (reference per_block_scales)     */
+  CUDA_LLM_SCALE_PER_TOKEN = 2, /* fp32 [num_blocks, Hkv, page]                              */
+  CUDA_LLM_SCALE_MX_E8M0 = 3    /* uint8 [num_blocks, Hkv, D/32, page]                       */
+};
+
+/* ---- paged decode --------------------------------------------------------------------- */
+typedef struct CudaLlmPagedDecodeParams {
+  /* device tensors, all borrowed */
+  const void* query;           /* [total_q, Hq, D] of q_dtype                                */
+  const void* key_cache;       /* see CudaLlmKvFormat                                        */
+  const void* value_cache;
+  const void* k_scale;         /* see CudaLlmScaleMode                                       */
+  const void* v_scale;
+  const int32_t* block_tables; /* [num_seqs, max_blocks_per_seq]                             */
+  const int32_t* context_lens; /* [num_seqs]                                                 */
+  const int32_t* cu_q_lens;    /* [num_seqs+1] prefix of per-sequence query lengths, or NULL
+                                  when every sequence has exactly one query token            */
+  void* out;                   /* [total_q, Hq, D] of out_dtype                              */
+  float* lse;                  /* optional [total_q, Hq] natural-log sum-exp, or NULL        */
+  void* workspace;             /* cuda_llm_paged_decode_workspace_bytes() bytes, 256-aligned */
+  size_t workspace_bytes;
+
+  int32_t num_seqs;
+  int32_t num_q_heads;
+  int32_t num_kv_heads;        /* divides num_q_heads; kv_head = q_head / (Hq/Hkv)           */
+  int32_t head_dim;            /* 64 or 128                                                  */
+  int32_t page_size;           /* 16, 32 or 64                                               */
+  int32_t max_blocks_per_seq;
+  int32_t num_blocks;          /* pages in the pool (bounds check of block-table entries)    */
+  int32_t max_q_len;           /* upper bound of per-sequence q_len; (Hq/Hkv)*max_q_len <= 16 */
+  int32_t q_dtype;             /* CudaLlmDType                                               */
+  int32_t out_dtype;           /* CudaLlmDType                                               */
+  int32_t k_format;            /* CudaLlmKvFormat                                            */
+  int32_t v_format;
+  int32_t scale_mode;          /* CudaLlmScaleMode, same for K and V                         */
+  float softmax_scale;
+  int32_t num_ctas;            /* 0 = one per SM                                             */
+  int32_t flags;               /* CUDA_LLM_FLAG_* bits, normally 0                          */
+} CudaLlmPagedDecodeParams;
+
+/* Bytes of workspace cuda_llm_paged_decode needs for these dimensions on the current device. */
+size_t cuda_llm_paged_decode_workspace_bytes(int32_t num_seqs, int32_t num_q_heads,
+                                             int32_t num_kv_heads, int32_t head_dim,
+                                             int32_t page_size, int32_t max_q_len,
+                                             int32_t num_ctas);
+
+/* Zero the workspace header (the device status word).  Call once after allocating a
+ * workspace, before its first use. */
+int cuda_llm_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Decode attention over a paged, quantised KV cache (replaces dispatch_fp8_paged_attention,
+ * kernels_api.h:94-101, extended with GQA, per-token and microscaling formats, q_len > 1 and
+ * split-KV).  Launches the attention kernel and the split merge on `stream`. */
+int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* params, void* stream);
+
+/* Read (and clear) the device status word of a workspace; synchronises `stream`. */
+int cuda_llm_decode_status(void* workspace, void* stream, uint32_t* status_out);
+
+/* Merge `num_parts` split-KV partials: parts_out [num_parts, rows, D] fp32 (each normalised
+ * inside its own KV range), parts_lse [num_parts, rows] natural-log sum-exp (-inf = empty).
+ * Writes out [rows, D] of out_dtype and, if not NULL, lse [rows].  Used after the all-gather
+ * of the split-context mode; algebra of combine_softmax_state
+ * (fused_online_softmax_kernel.cuh:40-49). */
+int cuda_llm_merge_partials(const float* parts_out, const float* parts_lse, int32_t num_parts,
+                            int64_t rows, int32_t head_dim, void* out, int32_t out_dtype,
+                            float* lse, void* stream);
+
+/* Bit-exact dequantisation of whole pages to fp32 (test and debugging aid):
+ * out [n_pages, Hkv, D, page] fp32 for the pages listed in `pages`. */
+int cuda_llm_dequant_pages(const void* cache, const void* scale, const int32_t* pages,
+                           int32_t n_pages, int32_t num_kv_heads, int32_t head_dim,
+                           int32_t page_size, int32_t format, int32_t scale_mode, float* out,
+                           void* stream);
+
+const char* cuda_llm_last_cuda_error(void);
+const char* cuda_llm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUDA_LLM_B200_H_ */

@@ -1,0 +1,87 @@
+"""The C-ABI library loads, exports every declared symbol, and rejects bad arguments before
+touching a device (no compute calls: these run without a GPU)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from cuda_b200 import _lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(L.LIB_PATH):
+        from cuda_b200 import build
+        build.build()
+    return L.load()
+
+
+def test_exports_every_declared_symbol(lib):
+    hdr = open(os.path.join(ROOT, "include", "cuda_llm_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    declared = set(re.findall(r"\b(cuda_llm_[a-z0-9_]+)\s*\(", hdr))
+    assert declared, "no declarations parsed"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert declared == set(L.SYMBOLS), (declared ^ set(L.SYMBOLS))
+    assert b"sm_100a" in lib.cuda_llm_version()
+
+
+def test_workspace_bytes_arithmetic(lib):
+    f = lib.cuda_llm_paged_decode_workspace_bytes
+    # S=64, Hq=32, Hkv=8, D=128, page=16, q_len 1, 148 CTAs: (64+148) slots * 64 rows * 129 floats
+    n = f(64, 32, 8, 128, 16, 1, 148)
+    rows = (64 + 148) * 8 * 8
+    assert n >= rows * 129 * 4 and n < rows * 129 * 4 + 4096 + 64 * 16
+    assert f(64, 32, 8, 128, 16, 4, 148) > n          # 16 rows per KV head
+    assert f(64, 32, 8, 96, 16, 1, 148) == 0          # unsupported head_dim
+    assert f(64, 32, 8, 128, 8, 1, 148) == 0          # unsupported page size
+    assert f(64, 32, 5, 128, 16, 1, 148) == 0         # Hq not a multiple of Hkv
+    assert f(64, 64, 2, 128, 16, 1, 148) == 0         # group 32 > 16 rows
+
+
+def test_bad_arguments_return_codes(lib):
+    assert lib.cuda_llm_paged_decode(None, None) == L.EINVAL
+    p = L.PagedDecodeParams()
+    p.num_seqs = 0
+    assert lib.cuda_llm_paged_decode(C.byref(p), None) == L.OK       # nothing to do
+    p.num_seqs = 1
+    assert lib.cuda_llm_paged_decode(C.byref(p), None) == L.EINVAL   # null tensors
+    assert b"null" in lib.cuda_llm_last_cuda_error()
+    assert lib.cuda_llm_merge_partials(None, None, 1, 1, 128, None, 0, None, None) == L.EINVAL
+    assert lib.cuda_llm_workspace_init(None, 0, None) == L.EWORKSPACE
+    st = C.c_uint32(0)
+    assert lib.cuda_llm_decode_status(None, None, C.byref(st)) == L.EINVAL
+    assert lib.cuda_llm_dequant_pages(None, None, None, 0, 8, 128, 16, 0, 0, None, None) == L.EINVAL
+
+
+def test_misaligned_and_unsupported(lib):
+    p = L.PagedDecodeParams()
+    for f in ("query", "key_cache", "value_cache", "k_scale", "v_scale", "block_tables",
+              "context_lens", "out", "workspace"):
+        setattr(p, f, 0x1000)
+    p.workspace_bytes = 1 << 30
+    p.num_seqs, p.num_q_heads, p.num_kv_heads, p.head_dim, p.page_size = 2, 8, 8, 64, 16
+    p.max_blocks_per_seq, p.num_blocks, p.max_q_len, p.num_ctas = 4, 8, 1, 148
+    p.k_format = L.KV_INT8
+    assert lib.cuda_llm_paged_decode(C.byref(p), None) == L.EINVAL   # int8 reading is rejected loudly
+    p.k_format = L.KV_FP8_E4M3
+    p.key_cache = 0x1008
+    assert lib.cuda_llm_paged_decode(C.byref(p), None) == L.EALIGN
+    p.key_cache = 0x1000
+    p.head_dim = 96
+    assert lib.cuda_llm_paged_decode(C.byref(p), None) == L.EINVAL
+    assert b"head_dim" in lib.cuda_llm_last_cuda_error()
+    p.head_dim = 64
+    p.workspace_bytes = 16
+    assert lib.cuda_llm_paged_decode(C.byref(p), None) == L.EWORKSPACE
+
+
+def test_ops_fail_loudly_without_library(monkeypatch):
+    monkeypatch.setattr(L, "_lib", None)
+    monkeypatch.setattr(L, "LIB_PATH", "/nonexistent/libcuda_llm_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        L.load()

@@ -1,0 +1,221 @@
+"""Parity of the CUDA paged decode path (through the C ABI) against the CPU oracle."""
+import pytest
+import torch
+
+import cases
+from helpers import assert_parity, oracle_out, to_oracle
+from oracle import paged_decode_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cuda_b200 import ops as _ops
+    _ops.L.load()
+    return _ops
+
+
+def _W():
+    from cuda_b200 import workloads
+    return workloads
+
+
+# ------------------------------------------------------------------------------------------
+# dequantisation and block-table gather: bit-exact
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("mode,vfmt", [("per_head", "fp8_e4m3"), ("per_block", "fp8_e4m3"),
+                                       ("per_token", "fp8_e4m3"), ("mx_e8m0", "fp8_e4m3"),
+                                       ("mx_e8m0", "fp4_e2m1")])
+def test_dequant_bit_exact(ops, mode, vfmt):
+    W = _W()
+    wl = W.build_workload("dq", context_lens=[70, 33, 128], q_lens=None, num_q_heads=8, num_kv_heads=4,
+                          head_dim=128, page_size=16, q_dtype=torch.bfloat16, v_format=vfmt,
+                          scale_mode=mode, pool_factor=1.5, seed=11, poison=False,
+                          mx_exponent_range=(-20, 12) if vfmt == "fp8_e4m3" else None)
+    kv = to_oracle(wl)
+    g = wl.to("cuda")
+    for s in range(3):
+        n = (int(wl.context_lens[s]) + 15) // 16
+        pages = wl.block_tables[s, :n]
+        for cache, scale, fmt, smode, ocache in (
+                (g.key_cache, g.k_scale, "fp8_e4m3", mode, kv.key_cache),
+                (g.value_cache, g.v_scale, vfmt, mode, kv.value_cache)):
+            got = ops.dequant_pages(cache, scale, pages.cuda(), 128, ops._FMT[fmt], ops._MODE[smode]).cpu()
+            sc = kv.k_scale if cache is g.key_cache else kv.v_scale
+            ref = O._dequant_pages(ocache, fmt, smode, sc, pages.long(), 128)   # [H, n*page, D]
+            ref = ref.view(4, n, 16, 128).permute(1, 0, 3, 2)
+            assert torch.equal(got, ref)
+
+
+def test_dequant_all_codes(ops):
+    """Every E4M3 byte and every E8M0 byte decodes exactly as the format tables say."""
+    codes = torch.arange(256, dtype=torch.uint8).repeat(8).view(1, 1, 128, 16).cuda()
+    one = torch.ones(1, dtype=torch.float32).cuda()
+    got = ops.dequant_pages(codes, one, torch.zeros(1, dtype=torch.int32).cuda(), 128,
+                            ops.L.KV_FP8_E4M3, ops.L.SCALE_PER_HEAD).cpu().view(-1)
+    ref = torch.from_numpy(O.E4M3_TABLE)[codes.cpu().view(-1).long()]
+    fin = torch.isfinite(ref)
+    assert torch.equal(got[fin], ref[fin]) and torch.isnan(got[~fin]).all()
+    # E8M0: payload 1.0 (0x38) times every scale byte
+    payload = torch.full((1, 1, 128, 16), 0x38, dtype=torch.uint8).cuda()
+    sc = torch.arange(256, dtype=torch.uint8)[:64].view(1, 1, 4, 16)
+    for base in range(0, 256, 64):
+        s = (sc + base).to(torch.uint8).cuda()
+        got = ops.dequant_pages(payload, s, torch.zeros(1, dtype=torch.int32).cuda(), 128,
+                                ops.L.KV_FP8_E4M3, ops.L.SCALE_MX_E8M0).cpu()
+        ref = torch.from_numpy(O.E8M0_TABLE)[(sc + base).long()].repeat_interleave(32, dim=2)
+        fin = torch.isfinite(ref)
+        assert torch.equal(got[fin], ref[fin]) and torch.isnan(got[~fin]).all()
+
+
+# ------------------------------------------------------------------------------------------
+# the reference's own E4M3 cases, against the golden outputs of the reference's ref_decode
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("case", list(cases.fp8_cases()), ids=lambda c: c[0])
+def test_reference_fp8_cases(ops, golden, case):
+    name, dtype, hd, lens = case
+    q, k, v, lens_t = cases.paged_inputs(dtype, hd, lens)
+    k8, v8, ks, vs, _, _ = cases.fp8_quantise(k, v)
+    bt = torch.from_numpy(golden[f"{name}/bt"])
+    perm = bt.reshape(-1).to(torch.int64)
+    kc = O.paged_layout_from_dense(k8, cases.PAGE, perm)
+    vc = O.paged_layout_from_dense(v8, cases.PAGE, perm)
+    out = ops.fp8_paged_attention_forward(q.cuda(), kc.cuda(), vc.cuda(), ks.cuda(), vs.cuda(),
+                                          bt.cuda(), lens_t.cuda(), check_status=True)
+    ref = torch.from_numpy(golden[f"{name}/out"])
+    # the reference's tolerance table (tests/_utils.py:23-27)
+    atol, rtol = {torch.float16: (2e-2, 2e-2), torch.bfloat16: (4e-2, 4e-2)}[dtype]
+    assert out.dtype == dtype and torch.isfinite(out).all()
+    assert torch.allclose(out.float().cpu(), ref, atol=atol, rtol=rtol)
+    assert_parity(out, ref, dtype, name)
+
+
+# ------------------------------------------------------------------------------------------
+# the five configurations, shrunk
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("cfg,batch,ctx_scale", [(1, 4, 1.0), (2, 6, 1 / 8), (3, 5, 1 / 16),
+                                                 (4, 2, 1 / 64), (5, 24, 1 / 8)])
+def test_configs_small(ops, cfg, batch, ctx_scale):
+    W = _W()
+    wl = W.make_config(cfg, batch=batch, ctx_scale=ctx_scale)
+    ref, ref_lse = oracle_out(wl, return_lse=True)
+    out, lse = ops.run_workload(wl.to("cuda"), return_lse=True, check_status=True)
+    assert_parity(out, ref, wl.query.dtype, wl.name)
+    assert (lse.cpu() - ref_lse).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("page", [16, 32, 64])
+@pytest.mark.parametrize("hkv,group", [(1, 1), (1, 8), (2, 4), (4, 1), (8, 4), (16, 2), (3, 1)])
+@pytest.mark.parametrize("mode,vfmt", [("per_token", "fp8_e4m3"), ("mx_e8m0", "fp8_e4m3"),
+                                       ("mx_e8m0", "fp4_e2m1"), ("per_head", "fp8_e4m3")])
+def test_head_and_page_shapes(ops, page, hkv, group, mode, vfmt):
+    W = _W()
+    d = 128 if hkv != 4 else 64
+    wl = W.build_workload("shapes", context_lens=[1, page, page + 1, 5 * page + 3, 0, 300], q_lens=None,
+                          num_q_heads=hkv * group, num_kv_heads=hkv, head_dim=d, page_size=page,
+                          q_dtype=torch.bfloat16, v_format=vfmt, scale_mode=mode, pool_factor=1.3,
+                          seed=page + hkv + group)
+    ref = oracle_out(wl)
+    out = ops.run_workload(wl.to("cuda"), check_status=True)
+    assert_parity(out, ref, torch.bfloat16, f"p{page} hkv{hkv} g{group} {mode} {vfmt}")
+    assert (out[4] == 0).all()          # empty context -> zeros
+
+
+@pytest.mark.parametrize("page", [16, 32, 64])
+def test_every_context_length(ops, page):
+    """ctx = 1 .. 3*page+1: every page-tail length, GQA group 4."""
+    W = _W()
+    lens = list(range(1, 3 * page + 2))
+    wl = W.build_workload("lens", context_lens=lens, q_lens=None, num_q_heads=8, num_kv_heads=2,
+                          head_dim=64, page_size=page, q_dtype=torch.float16,
+                          scale_mode="per_token", pool_factor=1.25, seed=5)
+    ref = oracle_out(wl)
+    out = ops.run_workload(wl.to("cuda"), check_status=True)
+    assert_parity(out, ref, torch.float16, f"lens page {page}")
+
+
+@pytest.mark.parametrize("mode,vfmt", [("per_token", "fp8_e4m3"), ("mx_e8m0", "fp4_e2m1")])
+@pytest.mark.parametrize("group", [1, 4])
+def test_q_len_causal(ops, mode, vfmt, group):
+    """q_len in {1..4}: bottom-right aligned causal mask inside the verify window."""
+    W = _W()
+    lens = [4, 5, 16, 17, 35, 64, 100, 3, 250]
+    qls = [4, 1, 2, 4, 3, 4, 1, 3, 4]
+    wl = W.build_workload("qlen", context_lens=lens, q_lens=qls, num_q_heads=2 * group, num_kv_heads=2,
+                          head_dim=128, page_size=16, q_dtype=torch.bfloat16, v_format=vfmt,
+                          scale_mode=mode, pool_factor=1.5, seed=9)
+    ref, ref_lse = oracle_out(wl, return_lse=True)
+    out, lse = ops.run_workload(wl.to("cuda"), return_lse=True, check_status=True)
+    assert_parity(out, ref, torch.bfloat16, "q_len causal")
+    assert (lse.cpu() - ref_lse).abs().max() < 2e-2
+
+
+def test_fp32_query_is_tight(ops):
+    """fp32 Q/out (the reference's <float,float> instantiation) uses split operands."""
+    W = _W()
+    wl = W.make_config(1)
+    ref = oracle_out(wl)
+    out = ops.run_workload(wl.to("cuda"), check_status=True)
+    assert out.dtype == torch.float32
+    assert (out.cpu() - ref).abs().max() < 2e-4
+
+
+def test_split_invariance_and_merge(ops):
+    """The result does not depend on how many CTAs the units are cut into."""
+    W = _W()
+    wl = W.make_config(2, batch=5, ctx_scale=1 / 4).to("cuda")
+    ref = oracle_out(wl)
+    outs = []
+    for n in (1, 3, 37, 148, 500):
+        ws = torch.zeros(ops.L.load().cuda_llm_paged_decode_workspace_bytes(5, 32, 8, 128, 16, 1, n),
+                         dtype=torch.uint8, device="cuda")
+        outs.append(ops.run_workload(wl, num_ctas=n, workspace=ws, check_status=True))
+        assert_parity(outs[-1], ref, torch.bfloat16, f"{n} CTAs")
+    for o in outs[1:]:
+        assert (o.float() - outs[0].float()).abs().max() <= 2e-2
+
+
+def test_merge_partials_matches_oracle(ops):
+    torch.manual_seed(1)
+    P, rows, d = 5, 37, 128
+    o = torch.randn(P, rows, d)
+    l = torch.randn(P, rows) * 3
+    l[2, :5] = float("-inf")
+    l[:, 7] = float("-inf")
+    ro, rl = O.merge_partials(o, l)
+    go, gl = ops.merge_partials(o.cuda(), l.cuda(), return_lse=True)
+    assert (go.cpu() - ro).abs().max() < 1e-5
+    fin = torch.isfinite(rl)
+    assert torch.equal(torch.isfinite(gl.cpu()), fin) and (gl.cpu()[fin] - rl[fin]).abs().max() < 1e-5
+    assert (go.cpu()[7] == 0).all()
+
+
+def test_bad_block_index_is_reported_not_faulted(ops):
+    W = _W()
+    wl = W.build_workload("bad", context_lens=[40, 40], q_lens=None, num_q_heads=8, num_kv_heads=8,
+                          head_dim=64, page_size=16, q_dtype=torch.float16, scale_mode="per_token", seed=2)
+    wl.block_tables[1, 1] = 10_000                 # outside the pool
+    g = wl.to("cuda")
+    ws = torch.zeros(16 << 20, dtype=torch.uint8, device="cuda")
+    ops.run_workload(g, workspace=ws)
+    st = ops.decode_status(ws)
+    assert st & ops.L.ST_BAD_BLOCK
+    assert ops.decode_status(ws) == 0              # cleared by the read
+
+
+def test_reference_error_messages(ops):
+    q = torch.zeros(2, 4, 64, device="cuda", dtype=torch.float16)
+    c = torch.zeros(4, 4, 64, 16, device="cuda", dtype=torch.uint8)
+    s = torch.ones(4, device="cuda")
+    bt = torch.zeros(2, 2, device="cuda", dtype=torch.int32)
+    cl = torch.ones(2, device="cuda", dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="Inputs must be on CUDA"):
+        ops.fp8_paged_attention_forward(q.cpu(), c, c, s, s, bt, cl)
+    with pytest.raises(RuntimeError, match="Query must be 3D"):
+        ops.fp8_paged_attention_forward(q[0], c, c, s, s, bt, cl)
+    with pytest.raises(RuntimeError, match="8-bit quantized"):
+        ops.fp8_paged_attention_forward(q, c.half(), c.half(), s, s, bt, cl)
+    with pytest.raises(RuntimeError, match="Only head_dim 64 and 128 supported"):
+        ops.fp8_paged_attention_forward(torch.zeros(2, 4, 32, device="cuda", dtype=torch.float16),
+                                        c[:, :, :32], c[:, :, :32], s, s, bt, cl)
