@@ -28,7 +28,7 @@ static int fail(int code, const char* msg) {
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct Layout {
-  int HG, TS, n_hg, NT, rows_max, PPS, n_stages, grid;
+  int HG, SUBS, tok_stage, n_hg, NT, rows_max, PPS, n_stages, grid;
   uint32_t stage_bytes, off_v, off_ks, off_vs;
   uint32_t k_page_stride, v_page_stride, ks_page_stride, vs_page_stride;
   uint32_t k_chunk, v_chunk, ks_chunk, vs_chunk;
@@ -64,13 +64,16 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   L.rows_max = 8 * L.NT;
   int HG = 8;
   while (Hkv % HG) HG >>= 1;
-  if (page == 64 && HG > 4) HG = 4;  // a stage must hold whole pages: 32*TS >= page
+  if (page == 64 && HG > 4) HG = 4;  // a stage must hold whole pages: 256/HG >= page
   L.HG = HG;
-  L.TS = 8 / HG;
+  // 16 consumer warps: NT == 1 -> (HG heads) x (16/HG sub-tiles of 16 tokens);
+  //                    NT == 2 -> 2 row halves x (HG heads) x (8/HG sub-tiles of 32 tokens)
+  L.SUBS = (L.NT == 1 ? 16 : 8) / HG;
+  L.tok_stage = 256 / HG;
   L.n_hg = Hkv / HG;
-  L.PPS = (32 * L.TS >= page) ? 32 * L.TS / page : 1;
+  L.PPS = (L.tok_stage >= page) ? L.tok_stage / page : 1;
   if (L.PPS > kMaxPagesPerStage) return fail(CUDA_LLM_EINVAL, "internal: too many pages per stage");
-  const uint32_t pad = (page == 16) ? 64u : 0u;  // keeps the two pages of a sub-tile on different banks
+  const uint32_t pad = 0;  // every 16-token m-tile lies inside one page: no padding between pages
   const int DV = (v_format == CUDA_LLM_KV_FP4_E2M1) ? D / 2 : D;
   L.k_chunk = (uint32_t)HG * D * page;
   L.v_chunk = (uint32_t)HG * DV * page;
@@ -85,7 +88,7 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   L.off_ks = L.off_v + L.PPS * L.v_page_stride;
   L.off_vs = L.off_ks + L.PPS * L.ks_page_stride;
   L.stage_bytes = (uint32_t)align_up(L.off_vs + L.PPS * L.vs_page_stride, 128);
-  const uint32_t stages_off = 256 + kMaxStages * sizeof(StageMeta);
+  const uint32_t stages_off = kStagesOff;
   int ns = (int)((kSmemBudget - stages_off) / L.stage_bytes);
   if (ns > kMaxStages) ns = kMaxStages;
   if (ns < 2) return fail(CUDA_LLM_EINVAL, "internal: stage does not fit in shared memory twice");
@@ -96,7 +99,7 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   if (num_ctas <= 0) return fail(CUDA_LLM_ECUDA, "cannot query the SM count");
   L.grid = num_ctas;
   const size_t n_slots = (size_t)S * L.n_hg + L.grid;
-  const size_t rows = n_slots * L.TS * L.HG * L.rows_max;
+  const size_t rows = n_slots * L.SUBS * L.HG * L.rows_max;
   L.ws_table = 256;
   L.ws_lse = align_up(L.ws_table + (size_t)S * L.n_hg * 16, 256);
   L.ws_o = align_up(L.ws_lse + rows * 4, 256);
@@ -200,7 +203,8 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   a.max_blocks = p->max_blocks_per_seq;
   a.num_blocks = p->num_blocks;
   a.HG = L.HG;
-  a.TS = L.TS;
+  a.SUBS = L.SUBS;
+  a.tok_stage = L.tok_stage;
   a.n_hg = L.n_hg;
   a.rows_max = L.rows_max;
   a.q_dtype = p->q_dtype;
@@ -208,6 +212,12 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   a.per_block = (p->scale_mode == CUDA_LLM_SCALE_PER_BLOCK);
   a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
   a.n_stages = L.n_stages;
+  if (p->flags & CUDA_LLM_FLAG_DIAG_NO_MATH) a.debug |= 1;
+  if (p->flags & CUDA_LLM_FLAG_DIAG_NO_COPY) a.debug |= 2;
+  {
+    const int ns_req = (p->flags >> 8) & 0xF;  // diagnostics: cap the ring depth
+    if (ns_req >= 2 && ns_req < a.n_stages) a.n_stages = ns_req;
+  }
   a.stage_bytes = L.stage_bytes;
   a.off_v = L.off_v;
   a.off_ks = L.off_ks;

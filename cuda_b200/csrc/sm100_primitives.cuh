@@ -34,20 +34,22 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// upper bound (ns) a single try_wait may sleep in hardware before it reports "not yet"
+constexpr uint32_t kSuspendHintNs = 2000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false after kMaxPolls unsuccessful polls (each poll may itself suspend for
-// a hardware-defined time, so the bound is of the order of a second).
-constexpr uint32_t kMaxPolls = 1u << 22;
+// Bounded wait: false after kMaxPolls unsuccessful polls (each poll may itself suspend for up
+// to kSuspendHintNs, so the bound is of the order of a few seconds at most).
+constexpr uint32_t kMaxPolls = 1u << 21;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -67,9 +69,34 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
       : "memory");
 }
 
+// 4-byte asynchronous copy global -> shared (no register in between), grouped and waited on
+// with commit / wait_group.
+__device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ----------------------------------------------------------------------------------------
-// Shared-memory loads
+// Shared-memory loads and stores
 // ----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {  // zero-extended
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, int v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts128(uint32_t addr, int x, int y, int z, int w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -127,6 +154,50 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ float e8m0_to_f32(uint32_t e) {
   uint32_t bits = (e == 0u) ? 0x00400000u : (e == 255u ? 0x7fc00000u : (e << 23));
   return __uint_as_float(bits);
+}
+
+// two fp32 -> two E4M3 bytes (round to nearest even, saturating): lo -> bits 7..0, hi -> 15..8
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
+  uint16_t d;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+// low / high half of an f16x2 as fp32
+__device__ __forceinline__ float f16x2_lo(uint32_t v) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xffffu)));
+}
+__device__ __forceinline__ float f16x2_hi(uint32_t v) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(v >> 16)));
+}
+
+// ----------------------------------------------------------------------------------------
+// ldmatrix: four 8x8 matrices of 16-bit elements; lane l supplies the address of row (l % 8)
+// of matrix (l / 8), rows are 16 bytes.  Plain: thread (g,t) gets, per matrix, the 4 bytes
+// 4t..4t+3 of row g.  Transposed: thread (g,t) gets {M[2t][g], M[2t+1][g]} as 16-bit elements,
+// i.e. bytes (2g, 2g+1) of row 2t in the low half and of row 2t+1 in the high half.
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// ----------------------------------------------------------------------------------------
+// Warp MMA m16n8k32, E4M3 inputs, fp32 accumulate:  D(16x8) += A(16x32) * B(32x8)
+//   a0:(row g, k 4t..4t+3) a1:(row g+8, k 4t..4t+3) a2:(row g, k 4t+16..19) a3:(row g+8, k 4t+16..19)
+//   b0:(k 4t..4t+3, col g) b1:(k 4t+16..19, col g)      c as for m16n8k16
+// Products of two E4M3 values are exact in the fp32 accumulator.
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // ----------------------------------------------------------------------------------------

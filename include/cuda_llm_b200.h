@@ -41,6 +41,12 @@ extern "C" {
 #define CUDA_LLM_FLAG_SKIP_MERGE 1 /* launch the attention kernel only (profiling: sequences
                                       that were split across CTAs are left unmerged)         */
 
+#define CUDA_LLM_FLAG_DIAG_NO_MATH 2 /* diagnostics: stream the pages but skip the attention math
+                                        (output is meaningless; measures the copy pipeline)   */
+#define CUDA_LLM_FLAG_DIAG_NO_COPY 4 /* diagnostics: do the attention math on stale shared memory,
+                                        no page copies (output is meaningless)                */
+/* bits 8..11: diagnostics: cap the shared-memory ring at this many stages (0 = as many as fit) */
+
 /* ---- enums ---------------------------------------------------------------------------- */
 enum CudaLlmDType { CUDA_LLM_F32 = 0, CUDA_LLM_F16 = 1, CUDA_LLM_BF16 = 2 };
 
