@@ -31,6 +31,10 @@ if ROOT not in sys.path:
 WORKLOADS = {"cfg1": 1, "cfg2": 2, "cfg3": 3, "cfg4": 4, "cfg5": 5}
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode-kernel launch,
+# from the ncu capture summarised in profiles/paged_decode_kernel_cfg2.md (traffic grows with the
+# bytes streamed, so the ratio carries over to the full-size launch)
+DRAM_TRAFFIC_PER_KV_BYTE = {"cfg2_llama8b_fp8_pertoken": 1.033}
 
 
 def measured_peak():
@@ -134,8 +138,8 @@ def cpu_reference_run(wl_cpu, budget_s: float, max_seqs=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the batch (smaller ncu captures)")
@@ -157,9 +161,10 @@ def main():
             return
         ncores = os.cpu_count() or 1
         torch.set_num_threads(ncores)
-        wl = workloads.make_config(cfg_id, "cpu", batch=args.batch or 8, ctx_scale=args.ctx_scale,
+        wl = workloads.make_config(cfg_id, "cpu", batch=args.batch, ctx_scale=args.ctx_scale,
                                    seed=seed, poison=False)
-        per_step_budget = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+        args.steps = min(args.steps, 20)          # CPU steps are seconds, not microseconds
+        per_step_budget = max(1.0, min(20.0, 120.0 / max(1, args.steps + 1)))
         for _ in range(min(args.warmup, 1)):
             cpu_reference_run(wl, per_step_budget)
         tot_t, tot_b, tot_q, n = 0.0, 0, 0, 0
@@ -173,8 +178,8 @@ def main():
             "ms_per_step": tot_t / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3->f32", "data": "synthetic",
             "tokens_per_s": tot_q / tot_t,
-            "config": {"workload": wl.name, "sample": f"{n // max(1, args.steps)} sequences per step of a batch-"
-                       f"{wl.num_seqs} draw of the same length distribution", "heads": "32q/8kv",
+            "config": {"workload": wl.name, "sample": f"first {n // max(1, args.steps)} of {wl.num_seqs} sequences per step",
+                       "heads": f"{wl.num_q_heads}q/{wl.num_kv_heads}kv",
                        "head_dim": wl.head_dim, "page_size": wl.page_size},
             "cpu_baseline": {"value": val, "unit": "TB/s", "cores": torch.get_num_threads(), "kind": "port",
                              "sample": f"{n} sequences in {tot_t:.1f} s"},
@@ -315,14 +320,10 @@ def main():
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,
     }
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_file):
-        try:
-            tj = json.load(open(traffic_file)).get(wl.name)
-            if tj:
-                line["roofline"]["traffic"] = tj["dram_bytes_per_kv_byte"] * kv_bytes
-        except Exception:
-            pass
+    ratio = DRAM_TRAFFIC_PER_KV_BYTE.get(wl.name)
+    if ratio is not None:
+        line["roofline"]["traffic"] = ratio * kv_bytes
+        line["roofline"]["traffic_source"] = "ncu dram__bytes_read+write of a batch-16 launch, scaled by KV bytes"
     if not args.no_cpu_baseline:
         torch.set_num_threads(os.cpu_count() or 1)
         t, b, q, n = cpu_reference_run(wl.to("cpu"), args.cpu_budget_s)

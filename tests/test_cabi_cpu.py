@@ -32,11 +32,13 @@ def test_exports_every_declared_symbol(lib):
 
 def test_workspace_bytes_arithmetic(lib):
     f = lib.cuda_llm_paged_decode_workspace_bytes
-    # S=64, Hq=32, Hkv=8, D=128, page=16, q_len 1, 148 CTAs: (64+148) slots * 64 rows * 129 floats
+    # S=64, Hq=32, Hkv=8, D=128, page=16, q_len 1, 148 CTAs: (64+148) slots, each 16 warp
+    # partials of 8 rows, 128 + 1 floats per row
     n = f(64, 32, 8, 128, 16, 1, 148)
-    rows = (64 + 148) * 8 * 8
+    rows = (64 + 148) * 16 * 8
     assert n >= rows * 129 * 4 and n < rows * 129 * 4 + 4096 + 64 * 16
-    assert f(64, 32, 8, 128, 16, 4, 148) > n          # 16 rows per KV head
+    assert f(64, 32, 8, 128, 16, 4, 148) == n         # 8 warp partials of 16 rows
+    assert f(128, 32, 8, 128, 16, 1, 148) > n
     assert f(64, 32, 8, 96, 16, 1, 148) == 0          # unsupported head_dim
     assert f(64, 32, 8, 128, 8, 1, 148) == 0          # unsupported page size
     assert f(64, 32, 5, 128, 16, 1, 148) == 0         # Hq not a multiple of Hkv
