@@ -132,6 +132,12 @@ static LaunchFn pick_d(int D, int page, int NT, bool precise) {
 
 using namespace b200;
 
+// Scratch for cuda_llm_paged_decode_static(): lives in the library image, one copy per GPU that
+// loads it, for the life of the process.  Host code may not pass this name to a kernel (on the
+// host it is only a handle for the symbol); its device address is looked up once per device.
+constexpr size_t kStaticScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
 extern "C" {
 
 const char* cuda_llm_last_cuda_error(void) { return g_err; }
@@ -253,6 +259,36 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   e = (D == 64) ? launch_merge_splits<64>(a, page, st) : launch_merge_splits<128>(a, page, st);
   if (e != cudaSuccess) return fail_cuda(e, "merge_splits_kernel launch");
   return CUDA_LLM_OK;
+}
+
+size_t cuda_llm_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int cuda_llm_paged_decode_static(const CudaLlmPagedDecodeParams* p, void* stream) {
+  if (!p) return fail(CUDA_LLM_EINVAL, "params is null");
+  static void* scratch_addr[64] = {nullptr};  // device address of g_static_scratch, per device
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(CUDA_LLM_EINVAL, "device ordinal out of range");
+  const size_t need = cuda_llm_paged_decode_workspace_bytes(p->num_seqs, p->num_q_heads, p->num_kv_heads,
+                                                            p->head_dim, p->page_size, p->max_q_len, p->num_ctas);
+  if (p->num_seqs > 0 && need == 0) return CUDA_LLM_EINVAL;  // message set by the layout check
+  if (need > kStaticScratchBytes)
+    return fail(CUDA_LLM_EWORKSPACE, "problem needs more scratch than the 16 MiB built into the library; "
+                                     "use cuda_llm_paged_decode with a caller-provided workspace");
+  if (!scratch_addr[dev]) {  // first call on this device: resolve the symbol with this device current
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
+    scratch_addr[dev] = ptr;
+  }
+  // the array keeps whatever the previous call left: the status word has to start at zero
+  e = cudaMemsetAsync(scratch_addr[dev], 0, 256, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(e, "clearing the static scratch header");
+  CudaLlmPagedDecodeParams q = *p;
+  q.workspace = scratch_addr[dev];
+  q.workspace_bytes = kStaticScratchBytes;
+  return cuda_llm_paged_decode(&q, stream);
 }
 
 int cuda_llm_decode_status(void* workspace, void* stream, uint32_t* status_out) {

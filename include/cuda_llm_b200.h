@@ -113,6 +113,21 @@ int cuda_llm_workspace_init(void* workspace, size_t workspace_bytes, void* strea
  * split-KV).  Launches the attention kernel and the split merge on `stream`. */
 int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* params, void* stream);
 
+/* No counterpart in the reference.  Same computation as cuda_llm_paged_decode, for callers that
+ * must not allocate device memory: a plugin called from a host runtime that owns the memory pool,
+ * or a serving thread where a cudaMalloc (which can synchronise the device or fail under memory
+ * pressure) is not acceptable.  params->workspace / workspace_bytes are ignored; the split
+ * partials go to a 16 MiB array built into the library (cuda_llm_static_scratch_bytes()), which
+ * every GPU that loads the library holds until the process exits.  Nothing is allocated or freed,
+ * here or in anything this calls.  Problems whose workspace exceeds the array (see
+ * cuda_llm_paged_decode_workspace_bytes) are refused with CUDA_LLM_EWORKSPACE.  The first call on
+ * a device looks up the array's device address; make that first call outside any stream capture.
+ * All calls on a device share the one array: two calls that overlap on the GPU (different
+ * streams) race on it, so keep them on one stream or order them with events.  The array keeps
+ * the previous call's contents; the status word is cleared on every call. */
+int cuda_llm_paged_decode_static(const CudaLlmPagedDecodeParams* params, void* stream);
+size_t cuda_llm_static_scratch_bytes(void);
+
 /* Read (and clear) the device status word of a workspace; synchronises `stream`. */
 int cuda_llm_decode_status(void* workspace, void* stream, uint32_t* status_out);
 
