@@ -40,6 +40,11 @@ SYMBOLS = {
     "cuda_llm_paged_decode": (C.c_int, [C.POINTER(PagedDecodeParams), C.c_void_p]),
     "cuda_llm_paged_decode_static": (C.c_int, [C.POINTER(PagedDecodeParams), C.c_void_p]),
     "cuda_llm_static_scratch_bytes": (C.c_size_t, []),
+    "cuda_llm_dense_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
+    "cuda_llm_paged_attention": (C.c_int, [C.c_void_p] * 6 + [C.c_int32] * 7 + [C.c_float, C.c_int32, C.c_void_p,
+                                                                            C.c_size_t, C.c_void_p]),
+    "cuda_llm_flash_decode": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 5 + [C.c_float, C.c_int32, C.c_void_p,
+                                                                         C.c_size_t, C.c_void_p]),
     "cuda_llm_decode_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]),
     "cuda_llm_merge_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
                                           C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),

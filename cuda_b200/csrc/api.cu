@@ -15,6 +15,12 @@ cudaError_t launch_merge_partials(const float*, const float*, int, long long, in
 cudaError_t launch_dequant_pages(const void*, const void*, const int32_t*, int, int, int, int, int,
                                  int, float*, cudaStream_t);
 
+size_t dense_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens);
+cudaError_t run_dense_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
+                             const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int page,
+                             int max_blocks, int num_blocks, int seq_len, float softmax_scale, int dtype,
+                             void* workspace, cudaStream_t st);
+
 static thread_local char g_err[256] = "";
 static int fail_cuda(cudaError_t e, const char* where) {
   snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));
@@ -322,6 +328,57 @@ int cuda_llm_dequant_pages(const void* cache, const void* scale, const int32_t* 
   cudaError_t e = launch_dequant_pages(cache, scale, pages, n_pages, num_kv_heads, head_dim, page_size,
                                        format, scale_mode, out, reinterpret_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "dequant_pages_kernel launch");
+}
+
+static int check_dense(int S, int Hq, int Hkv, int D, int dtype) {
+  if (S < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return fail(CUDA_LLM_EINVAL, "num_heads must be a positive multiple of num_kv_heads");
+  if (Hq / Hkv > 8) return fail(CUDA_LLM_EINVAL, "num_heads / num_kv_heads must be <= 8");
+  if (D != 64 && D != 128) return fail(CUDA_LLM_EINVAL, "Only head_dim 64 and 128 supported");
+  if (dtype < 0 || dtype > CUDA_LLM_BF16) return fail(CUDA_LLM_EINVAL, "unknown dtype");
+  return CUDA_LLM_OK;
+}
+
+size_t cuda_llm_dense_decode_workspace_bytes(int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads,
+                                             int32_t head_dim, int32_t max_tokens) {
+  if (check_dense(num_seqs, num_heads, num_kv_heads, head_dim, CUDA_LLM_F32) != CUDA_LLM_OK || max_tokens < 0) return 0;
+  return dense_decode_workspace_bytes(num_seqs, num_heads, num_kv_heads, head_dim, max_tokens);
+}
+
+int cuda_llm_paged_attention(const void* query, const void* key_cache, const void* value_cache,
+                             const int32_t* block_tables, const int32_t* context_lens, void* out,
+                             int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                             int32_t page_size, int32_t max_blocks_per_seq, int32_t num_blocks,
+                             float softmax_scale, int32_t dtype, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  if (num_seqs == 0) return CUDA_LLM_OK;
+  if (!query || !key_cache || !value_cache || !block_tables || !context_lens || !out)
+    return fail(CUDA_LLM_EINVAL, "a required tensor pointer is null");
+  int rc = check_dense(num_seqs, num_heads, num_kv_heads, head_dim, dtype);
+  if (rc != CUDA_LLM_OK) return rc;
+  if (page_size != 16 && page_size != 32 && page_size != 64) return fail(CUDA_LLM_EINVAL, "Only page_size 16, 32 and 64 supported");
+  if (max_blocks_per_seq <= 0 || num_blocks <= 0) return fail(CUDA_LLM_EINVAL, "max_blocks_per_seq and num_blocks must be positive");
+  const size_t need = dense_decode_workspace_bytes(num_seqs, num_heads, num_kv_heads, head_dim, max_blocks_per_seq * page_size);
+  if (!workspace || workspace_bytes < need) return fail(CUDA_LLM_EWORKSPACE, "workspace missing or smaller than cuda_llm_dense_decode_workspace_bytes()");
+  cudaError_t e = run_dense_decode(true, query, key_cache, value_cache, block_tables, context_lens, out, num_seqs,
+                                   num_heads, num_kv_heads, head_dim, page_size, max_blocks_per_seq, num_blocks, 0,
+                                   softmax_scale, dtype, workspace, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "paged_attention launch");
+}
+
+int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, int32_t batch_size,
+                          int32_t num_heads, int32_t num_kv_heads, int32_t seq_len, int32_t head_dim,
+                          float softmax_scale, int32_t dtype, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  if (batch_size == 0) return CUDA_LLM_OK;
+  if (!q || !k || !v || !o) return fail(CUDA_LLM_EINVAL, "a required tensor pointer is null");
+  int rc = check_dense(batch_size, num_heads, num_kv_heads, head_dim, dtype);
+  if (rc != CUDA_LLM_OK) return rc;
+  if (seq_len < 0) return fail(CUDA_LLM_EINVAL, "seq_len must be >= 0");
+  const size_t need = dense_decode_workspace_bytes(batch_size, num_heads, num_kv_heads, head_dim, seq_len);
+  if (!workspace || workspace_bytes < need) return fail(CUDA_LLM_EWORKSPACE, "workspace missing or smaller than cuda_llm_dense_decode_workspace_bytes()");
+  cudaError_t e = run_dense_decode(false, q, k, v, nullptr, nullptr, o, batch_size, num_heads, num_kv_heads, head_dim,
+                                   1, 1, 1, seq_len, softmax_scale, dtype, workspace, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "flash_decode launch");
 }
 
 int cuda_llm_merge_partials(const float* parts_out, const float* parts_lse, int32_t num_parts,

@@ -156,6 +156,83 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
     return (out, lse) if return_lse else out
 
 
+def paged_attention_forward(query, key_cache, value_cache, block_tables, context_lens, softmax_scale=None):
+    """Decode attention over a paged fp32 / fp16 / bf16 cache: signature of the reference binding
+    ``paged_attention_forward`` (``fused_softmax_binding.cpp:109-173`` in the reference project).
+    ``key_cache.shape[1]`` may be smaller than ``query.shape[1]`` (GQA)."""
+    if not (query.is_cuda and key_cache.is_cuda and value_cache.is_cuda):
+        raise RuntimeError("Inputs must be on CUDA")
+    if not (block_tables.is_cuda and context_lens.is_cuda):
+        raise RuntimeError("Metadata tensors must be on CUDA")
+    if query.dim() != 3:
+        raise RuntimeError("Query must be 3D [num_seqs, num_heads, head_dim]")
+    if key_cache.dim() != 4 or value_cache.dim() != 4:
+        raise RuntimeError("KV caches must be 4D [num_blocks, num_heads, head_dim, page_size]")
+    if query.dtype not in _DTYPE:
+        raise RuntimeError("Unsupported scalar type for PagedAttention. Supported: Float32, Float16, BFloat16.")
+    if key_cache.dtype != query.dtype or value_cache.dtype != query.dtype:
+        raise RuntimeError("query and KV caches must have the same dtype")
+    n, hq, d = query.shape
+    nb, hkv, dk, page = key_cache.shape
+    if d not in (64, 128) or dk != d:
+        raise RuntimeError("Only head_dim 64 and 128 supported")
+    if block_tables.dtype != torch.int32 or context_lens.dtype != torch.int32:
+        raise RuntimeError("block_tables and context_lens must be int32")
+    for t, name in ((query, "query"), (key_cache, "key_cache"), (value_cache, "value_cache"),
+                    (block_tables, "block_tables"), (context_lens, "context_lens")):
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    scale = 1.0 / math.sqrt(d) if softmax_scale is None else float(softmax_scale)
+    lib = L.load()
+    with torch.cuda.device(query.device):
+        out = torch.empty_like(query)
+        need = lib.cuda_llm_dense_decode_workspace_bytes(n, hq, hkv, d, block_tables.shape[1] * page)
+        if need == 0:
+            raise L.CudaLlmError(L.EINVAL, "cuda_llm_dense_decode_workspace_bytes")
+        ws = get_workspace(query.device, need)
+        L.check(lib.cuda_llm_paged_attention(query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+                                             block_tables.data_ptr(), context_lens.data_ptr(), out.data_ptr(),
+                                             n, hq, hkv, d, page, block_tables.shape[1], nb, scale,
+                                             _DTYPE[query.dtype], ws.data_ptr(), ws.numel(),
+                                             _stream_ptr(query.device)), "cuda_llm_paged_attention")
+    return out
+
+
+def async_flash_decode(q, k, v, softmax_scale=None):
+    """Decode attention over contiguous KV: signature of the reference binding ``async_flash_decode``
+    (``fused_softmax_binding.cpp:308-360``): q [B,H,1,D], k/v [B,Hkv,S,D] -> [B,H,1,D]."""
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("Inputs must be on CUDA")
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise RuntimeError("Inputs must be 4D [batch, heads, seq, dim]")
+    if q.size(2) != 1:
+        raise RuntimeError("Query sequence length must be 1 for Flash-Decoding")
+    if k.shape != v.shape:
+        raise RuntimeError("K and V must have identical shapes")
+    if q.dtype not in _DTYPE:
+        raise RuntimeError("Unsupported scalar type for Async Flash-Decode. Supported: Float32, Float16, BFloat16.")
+    b, h, _, d = q.shape
+    if d not in (64, 128):
+        raise RuntimeError("Only head_dim 64 and 128 supported")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    hkv, s = k.shape[1], k.shape[2]
+    scale = 1.0 / math.sqrt(d) if softmax_scale is None else float(softmax_scale)
+    lib = L.load()
+    with torch.cuda.device(q.device):
+        out = torch.empty_like(q)
+        need = lib.cuda_llm_dense_decode_workspace_bytes(b, h, hkv, d, s)
+        if need == 0:
+            raise L.CudaLlmError(L.EINVAL, "cuda_llm_dense_decode_workspace_bytes")
+        ws = get_workspace(q.device, need)
+        L.check(lib.cuda_llm_flash_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), b, h, hkv, s, d,
+                                          scale, _DTYPE[q.dtype], ws.data_ptr(), ws.numel(),
+                                          _stream_ptr(q.device)), "cuda_llm_flash_decode")
+    return out
+
+
+flash_decode = async_flash_decode      # the name the reference's README gives the Python-level call
+
+
 def decode_status(workspace: torch.Tensor, device=None) -> int:
     """Read and clear the device status word (synchronises the current stream)."""
     device = workspace.device if device is None else device

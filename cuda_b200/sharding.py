@@ -1,0 +1,152 @@
+"""Multi-GPU layer of the decode path: one process per GPU (torch.distributed).
+
+The reference has no distributed code at all; this layer exists because decode attention shards
+naturally in three ways:
+
+* by sequence   (batched decode): independent, no collective;
+* by KV head    (tensor-parallel style): every rank owns ``Hkv / world`` KV heads of every page and
+  the matching query heads; independent, the per-rank outputs are the final rows of their heads;
+* by KV range   (one long context): every rank owns a page-aligned token range, computes a
+  partial ``(out, lse)`` over it, the partials are all-gathered (NCCL over NVLink when the group
+  is an NCCL group) and merged with ``combine_softmax_state``'s algebra
+  (``fused_online_softmax_kernel.cuh:40-49`` in the reference project).
+
+The compute callables are parameters so that the host logic can be exercised on CPU ranks (gloo)
+with a stand-in; their defaults are the CUDA ops, and there is no CPU fallback inside them.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .workloads import DecodeWorkload, SCALE_NONE, SCALE_PER_HEAD
+
+
+# --------------------------------------------------------------------------------------
+# partition plans (pure integer logic)
+# --------------------------------------------------------------------------------------
+def shard_sequences(context_lens: Sequence[int], world: int) -> List[List[int]]:
+    """Deal sequences to ``world`` ranks, longest first onto the least loaded rank (LPT), so that
+    every rank streams about the same number of KV bytes.  Returns the sequence ids per rank, each
+    list in ascending order."""
+    loads = [0] * world
+    out: List[List[int]] = [[] for _ in range(world)]
+    for s in sorted(range(len(context_lens)), key=lambda i: (-int(context_lens[i]), i)):
+        r = min(range(world), key=lambda i: (loads[i], i))
+        out[r].append(s)
+        loads[r] += max(int(context_lens[s]), 0)
+    return [sorted(x) for x in out]
+
+
+def shard_kv_heads(num_kv_heads: int, world: int, rank: int) -> Tuple[int, int]:
+    """KV heads ``[lo, hi)`` of ``rank``; ``num_kv_heads`` must be a multiple of ``world``."""
+    if num_kv_heads % world:
+        raise ValueError("num_kv_heads must be a multiple of the number of ranks")
+    per = num_kv_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def split_context(ctx: int, world: int, rank: int, page_size: int) -> Tuple[int, int]:
+    """Token range ``[begin, end)`` of ``rank`` for a context of ``ctx`` tokens: whole pages,
+    spread as evenly as pages allow; ranks past the end get an empty range."""
+    pages = (max(ctx, 0) + page_size - 1) // page_size
+    lo = (pages * rank) // world
+    hi = (pages * (rank + 1)) // world
+    return min(lo * page_size, ctx), min(hi * page_size, ctx)
+
+
+# --------------------------------------------------------------------------------------
+# slicing a workload (tests and the benchmark build per-rank inputs with these)
+# --------------------------------------------------------------------------------------
+def slice_sequences(wl: DecodeWorkload, seq_ids: Sequence[int]) -> DecodeWorkload:
+    ids = torch.as_tensor(list(seq_ids), dtype=torch.long, device=wl.context_lens.device)
+    if wl.cu_q_lens is None:
+        q = wl.query[ids]
+        cu = None
+    else:
+        cu_all = wl.cu_q_lens.tolist()
+        rows = [r for s in seq_ids for r in range(cu_all[s], cu_all[s + 1])]
+        q = wl.query[torch.as_tensor(rows, dtype=torch.long, device=wl.query.device)]
+        lens = [cu_all[s + 1] - cu_all[s] for s in seq_ids]
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32,
+                          device=wl.context_lens.device)
+    return dataclasses.replace(wl, query=q.contiguous(), block_tables=wl.block_tables[ids].contiguous(),
+                               context_lens=wl.context_lens[ids].contiguous(), cu_q_lens=cu)
+
+
+def slice_kv_heads(wl: DecodeWorkload, lo: int, hi: int) -> DecodeWorkload:
+    g = wl.num_q_heads // wl.num_kv_heads
+
+    def sl(scale, mode):
+        if scale is None or mode == SCALE_NONE:
+            return scale
+        if mode == SCALE_PER_HEAD:
+            return scale[lo:hi].contiguous()
+        return scale[:, lo:hi].contiguous()
+
+    return dataclasses.replace(
+        wl, query=wl.query[:, lo * g:hi * g].contiguous(), key_cache=wl.key_cache[:, lo:hi].contiguous(),
+        value_cache=wl.value_cache[:, lo:hi].contiguous(), k_scale=sl(wl.k_scale, wl.k_scale_mode),
+        v_scale=sl(wl.v_scale, wl.v_scale_mode), num_q_heads=(hi - lo) * g, num_kv_heads=hi - lo)
+
+
+def slice_context(wl: DecodeWorkload, world: int, rank: int) -> DecodeWorkload:
+    """The page-aligned KV range of ``rank`` for every sequence (q_len 1 only: a verify window
+    would need absolute positions).  The page pool is shared; only tables and lengths change."""
+    if wl.cu_q_lens is not None:
+        raise ValueError("split-context mode supports q_len == 1")
+    ctx = wl.context_lens.tolist()
+    rng = [split_context(c, world, rank, wl.page_size) for c in ctx]
+    width = max(1, max((e - b + wl.page_size - 1) // wl.page_size for b, e in rng))
+    bt = torch.zeros(len(ctx), width, dtype=torch.int32, device=wl.block_tables.device)
+    for s, (b, e) in enumerate(rng):
+        n = (e - b + wl.page_size - 1) // wl.page_size
+        if n:
+            p0 = b // wl.page_size
+            bt[s, :n] = wl.block_tables[s, p0:p0 + n]
+    lens = torch.tensor([e - b for b, e in rng], dtype=torch.int32, device=wl.context_lens.device)
+    return dataclasses.replace(wl, block_tables=bt, context_lens=lens)
+
+
+# --------------------------------------------------------------------------------------
+# split-context decode: local partial -> all-gather -> merge
+# --------------------------------------------------------------------------------------
+def _cuda_partial(wl: DecodeWorkload):
+    from . import ops
+    out = torch.empty(wl.query.shape, dtype=torch.float32, device=wl.query.device)
+    return ops.run_workload(wl, return_lse=True, out=out)
+
+
+def _cuda_merge(parts_out, parts_lse, out_dtype):
+    from . import ops
+    return ops.merge_partials(parts_out, parts_lse, out_dtype=out_dtype)
+
+
+def decode_split_context(local: DecodeWorkload, group: Optional[dist.ProcessGroup] = None,
+                         partial_fn: Callable = _cuda_partial, merge_fn: Callable = _cuda_merge,
+                         out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Every rank calls this with the workload restricted to ITS KV range (``slice_context``).
+    Returns the full attention output on every rank.
+
+    One collective: an all-gather of ``[total_q, Hq, D + 1]`` fp32 per rank (the partial output
+    with its log-sum-exp in the last column), issued on the current stream right after the local
+    kernel; the merge kernel follows on the same stream."""
+    world = dist.get_world_size(group)
+    out, lse = partial_fn(local)                                   # [T,Hq,D] fp32, [T,Hq] natural log
+    packed = torch.cat((out.float(), lse.float().unsqueeze(-1)), dim=-1).contiguous()
+    gathered = torch.empty((world,) + tuple(packed.shape), dtype=packed.dtype, device=packed.device)
+    dist.all_gather(list(gathered.unbind(0)), packed, group=group)   # one slot per rank, written in place
+    dtype = out_dtype or local.query.dtype
+    return merge_fn(gathered[..., :-1].contiguous(), gathered[..., -1].contiguous(), dtype)
+
+
+def gather_head_shards(local_out: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """KV-head sharding produces final rows for a slice of the query heads; this concatenates the
+    slices (checking / a consumer that needs the full tensor).  Not on the attention data path."""
+    world = dist.get_world_size(group)
+    parts = [torch.empty_like(local_out) for _ in range(world)]
+    dist.all_gather(parts, local_out.contiguous(), group=group)
+    return torch.cat(parts, dim=1)

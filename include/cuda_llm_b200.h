@@ -131,6 +131,30 @@ size_t cuda_llm_static_scratch_bytes(void);
 /* Read (and clear) the device status word of a workspace; synchronises `stream`. */
 int cuda_llm_decode_status(void* workspace, void* stream, uint32_t* status_out);
 
+/* ---- unquantised KV ------------------------------------------------------------------- */
+/* Workspace for the two entry points below; max_tokens = max_blocks_per_seq * page_size (paged)
+ * or seq_len (contiguous). */
+size_t cuda_llm_dense_decode_workspace_bytes(int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads,
+                                             int32_t head_dim, int32_t max_tokens);
+
+/* Replaces dispatch_paged_attention<T> (kernels_api.h:35-41): decode attention over a paged
+ * fp32 / fp16 / bf16 cache [num_blocks, num_kv_heads, head_dim, page_size]; query and out
+ * [num_seqs, num_heads, head_dim] of the same dtype.  num_kv_heads < num_heads is GQA (the
+ * reference is MHA only); num_blocks bounds the block-table entries. */
+int cuda_llm_paged_attention(const void* query, const void* key_cache, const void* value_cache,
+                             const int32_t* block_tables, const int32_t* context_lens, void* out,
+                             int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                             int32_t page_size, int32_t max_blocks_per_seq, int32_t num_blocks,
+                             float softmax_scale, int32_t dtype, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
+/* Replaces dispatch_async_flash_decode<T> (kernels_api.h:58-62): q, o [batch, num_heads, 1, head_dim],
+ * k, v [batch, num_kv_heads, seq_len, head_dim], one dtype. */
+int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, int32_t batch_size,
+                          int32_t num_heads, int32_t num_kv_heads, int32_t seq_len, int32_t head_dim,
+                          float softmax_scale, int32_t dtype, void* workspace, size_t workspace_bytes,
+                          void* stream);
+
 /* Merge `num_parts` split-KV partials: parts_out [num_parts, rows, D] fp32 (each normalised
  * inside its own KV range), parts_lse [num_parts, rows] natural-log sum-exp (-inf = empty).
  * Writes out [rows, D] of out_dtype and, if not NULL, lse [rows].  Used after the all-gather

@@ -219,3 +219,63 @@ def test_reference_error_messages(ops):
     with pytest.raises(RuntimeError, match="Only head_dim 64 and 128 supported"):
         ops.fp8_paged_attention_forward(torch.zeros(2, 4, 32, device="cuda", dtype=torch.float16),
                                         c[:, :, :32], c[:, :, :32], s, s, bt, cl)
+
+
+# ------------------------------------------------------------------------------------------
+# unquantised entry points: the reference's own cases against its golden outputs
+# ------------------------------------------------------------------------------------------
+REF_TOL = {torch.float16: (2e-2, 2e-2), torch.bfloat16: (4e-2, 4e-2), torch.float32: (1e-4, 1e-4)}
+
+
+@pytest.mark.parametrize("case", list(cases.paged_cases()), ids=lambda c: c[0])
+def test_reference_paged_cases(ops, golden, case):
+    name, dtype, hd, lens = case
+    q, k, v, lens_t = cases.paged_inputs(dtype, hd, lens)
+    bt = torch.from_numpy(golden[f"{name}/bt"])
+    perm = bt.reshape(-1).to(torch.int64)
+    kc = O.paged_layout_from_dense(k, cases.PAGE, perm)
+    vc = O.paged_layout_from_dense(v, cases.PAGE, perm)
+    out = ops.paged_attention_forward(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), lens_t.cuda())
+    ref = torch.from_numpy(golden[f"{name}/out"])
+    atol, rtol = REF_TOL[dtype]
+    assert out.dtype == dtype and torch.isfinite(out).all()
+    assert torch.allclose(out.float().cpu(), ref, atol=atol, rtol=rtol)
+
+
+@pytest.mark.parametrize("case", list(cases.decode_cases()), ids=lambda c: c[0])
+def test_reference_decode_cases(ops, golden, case):
+    name, dtype, hd, kv_len = case
+    q, k, v = cases.decode_inputs(dtype, hd, kv_len)
+    out = ops.async_flash_decode(q.cuda(), k.cuda(), v.cuda())
+    ref = torch.from_numpy(golden[f"{name}/out"])
+    atol, rtol = REF_TOL[dtype]
+    assert out.shape == q.shape and torch.isfinite(out).all()
+    assert torch.allclose(out.float().cpu(), ref, atol=atol, rtol=rtol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("hkv,group,page", [(2, 4, 16), (8, 1, 32), (1, 8, 64)])
+def test_paged_attention_gqa_long(ops, dtype, hkv, group, page):
+    """GQA, page sizes 32/64, several splits, an empty sequence."""
+    W = _W()
+    wl = W.build_workload("pa", context_lens=[1000, 0, 37, 2049], q_lens=None, num_q_heads=hkv * group,
+                          num_kv_heads=hkv, head_dim=128, page_size=page, q_dtype=dtype, scale_mode="none",
+                          pool_factor=1.2, seed=3, cache_dtype=dtype)
+    kv = O.PagedKV(wl.key_cache, wl.value_cache, wl.block_tables, wl.context_lens, page, 128,
+                   O.KV_F32, O.KV_F32, O.SCALE_NONE, O.SCALE_NONE)
+    ref = O.ref_paged_decode(wl.query, kv, wl.softmax_scale)
+    g = wl.to("cuda")
+    out = ops.paged_attention_forward(g.query, g.key_cache, g.value_cache, g.block_tables, g.context_lens)
+    atol, rtol = REF_TOL[dtype]
+    assert torch.allclose(out.float().cpu(), ref, atol=atol, rtol=rtol)
+    assert (out[1] == 0).all()
+
+
+def test_flash_decode_gqa(ops):
+    torch.manual_seed(4)
+    q = torch.randn(3, 8, 1, 128, dtype=torch.bfloat16)
+    k = torch.randn(3, 2, 777, 128, dtype=torch.bfloat16)
+    v = torch.randn(3, 2, 777, 128, dtype=torch.bfloat16)
+    ref = O.ref_flash_decode(q, k.repeat_interleave(4, dim=1), v.repeat_interleave(4, dim=1))
+    out = ops.flash_decode(q.cuda(), k.cuda(), v.cuda())
+    assert torch.allclose(out.float().cpu(), ref, atol=4e-2, rtol=4e-2)
