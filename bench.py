@@ -199,16 +199,36 @@ def main():
     from cuda_b200 import ops
     ops.L.load()
 
-    wl = workloads.make_config(cfg_id, dev, batch=args.batch, ctx_scale=args.ctx_scale, seed=seed,
-                               poison=False)
+    # How the workload spreads over N GPUs (north star): cfg2 one batch per rank (weak scaling);
+    # cfg3 KV-head shards, cfg5 the batch dealt over the ranks, cfg4 KV ranges of the same
+    # contexts with an all-gather + merge (strong scaling: total work fixed).
+    scaling, parallelism = "weak", f"sequence-sharded x{world}, one batch per rank"
+    kw = dict(batch=args.batch, ctx_scale=args.ctx_scale, seed=seed, poison=False)
+    split_ctx = False
+    if cfg_id == 3:
+        scaling, parallelism = "strong", f"KV-head-sharded x{world}"
+        kw.update(head_shards=world, len_seed=1003)
+    elif cfg_id == 4:
+        scaling, parallelism = "strong", f"KV-range-sharded x{world}, all-gather + merge"
+        kw.update(ctx_scale=args.ctx_scale / world)
+        split_ctx = world > 1
+    elif cfg_id == 5:
+        scaling, parallelism = "strong", f"sequence-sharded x{world}"
+        kw.update(batch=(args.batch or 256) // world)
+    wl = workloads.make_config(cfg_id, dev, **kw)
     kv_bytes = wl.kv_bytes()
     q_tokens = wl.query.shape[0]
     need = ops.L.load().cuda_llm_paged_decode_workspace_bytes(
         wl.num_seqs, wl.num_q_heads, wl.num_kv_heads, wl.head_dim, wl.page_size, wl.max_q_len, 0)
     ws = torch.zeros(need, dtype=torch.uint8, device=dev)
     out = torch.empty_like(wl.query)
+    from cuda_b200 import sharding
 
     def step(flags=0):
+        if split_ctx:
+            part = torch.empty(wl.query.shape, dtype=torch.float32, device=dev)
+            return sharding.decode_split_context(
+                wl, partial_fn=lambda w: ops.run_workload(w, return_lse=True, out=part, workspace=ws))
         return ops.run_workload(wl, out=out, workspace=ws, flags=flags)
 
     def barrier():
@@ -252,7 +272,8 @@ def main():
     # (1) whole step resident in HBM: attention kernel + split merge
     ms_total = timed(step, args.steps)
     # (2) the dominant kernel alone (roofline numerator / denominator)
-    ms_kernel = timed(lambda: step(ops.L.FLAG_SKIP_MERGE), args.steps) / args.steps
+    ms_kernel = timed(lambda: ops.run_workload(wl, out=out, workspace=ws, flags=ops.L.FLAG_SKIP_MERGE),
+                      args.steps) / args.steps
     step()
     # (3) end to end through the public op with host buffers: the step's inputs (query, block
     #     tables, context lengths, query offsets) come from pinned host memory, the result goes back
@@ -269,9 +290,16 @@ def main():
             d.copy_(h, non_blocking=True)
         if dev_cu is not None:
             dev_cu.copy_(host_cu, non_blocking=True)
-        o = ops.fp8_paged_attention_forward(dev_in[0], wl.key_cache, wl.value_cache, wl.k_scale, wl.v_scale,
-                                            dev_in[1], dev_in[2], wl.softmax_scale, cu_q_lens=dev_cu,
-                                            max_q_len=wl.max_q_len, workspace=ws)
+        if split_ctx:
+            import dataclasses
+            lw = dataclasses.replace(wl, query=dev_in[0], block_tables=dev_in[1], context_lens=dev_in[2])
+            part = torch.empty(wl.query.shape, dtype=torch.float32, device=dev)
+            o = sharding.decode_split_context(
+                lw, partial_fn=lambda w: ops.run_workload(w, return_lse=True, out=part, workspace=ws))
+        else:
+            o = ops.fp8_paged_attention_forward(dev_in[0], wl.key_cache, wl.value_cache, wl.k_scale, wl.v_scale,
+                                                dev_in[1], dev_in[2], wl.softmax_scale, cu_q_lens=dev_cu,
+                                                max_q_len=wl.max_q_len, workspace=ws)
         host_out.copy_(o, non_blocking=True)
 
     for _ in range(3):
@@ -301,14 +329,14 @@ def main():
     line = {
         "metric": "paged_fp8_decode_kv_hbm_throughput", "value": value, "unit": "TB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3->f16 mma, f32 acc",
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "fp8_e4m3->f16 mma, f32 acc",
         "data": "synthetic", "tokens_per_s": tot_q / (ms_step * 1e-3),
         "pct_of_nominal_8TBs": 100.0 * value * 1e3 / (NOMINAL_HBM_GBS * world),
         "pct_of_measured_copy_peak": 100.0 * value * 1e3 / (peak * world),
         "config": {"workload": wl.name, "batch_per_gpu": wl.num_seqs, "heads": f"{wl.num_q_heads}q/{wl.num_kv_heads}kv",
                    "head_dim": wl.head_dim, "page_size": wl.page_size,
                    "kv_tokens_per_gpu": int(wl.context_lens.sum().item()), "kv_bytes_per_gpu": kv_bytes,
-                   "pool_pages": wl.meta["pool_pages"], "parallelism": f"sequence-sharded x{world}",
+                   "pool_pages": wl.meta["pool_pages"], "parallelism": parallelism,
                    "l2": "inputs larger than L2 (KV working set per step >> 126 MB), no flush needed"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src, "kernel": "paged_decode_kernel", "kernel_ms": ms_kernel,
@@ -317,7 +345,7 @@ def main():
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps,
                 "note": "KV cache resident in HBM (it is decode state, like weights); per-step inputs "
                         "(query, block tables, context lengths) from pinned host memory, output read back"},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": (3 if split_ctx else 2) * args.steps,
         "clocks": clocks,
     }
     ratio = DRAM_TRAFFIC_PER_KV_BYTE.get(wl.name)

@@ -6,11 +6,19 @@ namespace b200 {
 
 template <int D>
 cudaError_t launch_merge_splits(const DecodeArgs& a, int page, cudaStream_t st) {
-  const long long warps = (long long)a.S * a.Hq;
-  if (warps == 0) return cudaSuccess;
-  const int grid = (int)((warps + 3) / 4);
-  merge_splits_kernel<D><<<grid, 128, 0, st>>>(a, page);
-  return cudaGetLastError();
+  const long long blocks = (long long)a.S * a.Hq;
+  if (blocks == 0) return cudaSuccess;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while the decode kernel drains
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, merge_splits_kernel<D>, a, page);
 }
 template cudaError_t launch_merge_splits<64>(const DecodeArgs&, int, cudaStream_t);
 template cudaError_t launch_merge_splits<128>(const DecodeArgs&, int, cudaStream_t);
@@ -34,11 +42,16 @@ merge_partials_kernel(const float* __restrict__ parts_out, const float* __restri
 #pragma unroll
   for (int v = 0; v < VPL; ++v) acc[v] = 0.f;
   float wsum = 0.f;
-  for (int p = 0; p < num_parts; ++p) {
-    const float w = fast_exp2((parts_lse[(size_t)p * rows + row] - mu) * LOG2E);
-    if (w > 0.f) {
+  // weights 32 parts at a time (one per lane), then independent row loads
+  for (int base = 0; base < num_parts; base += 32) {
+    const int mine = base + lane;
+    const float wl = mine < num_parts ? fast_exp2((parts_lse[(size_t)mine * rows + row] - mu) * LOG2E) : 0.f;
+    const int cnt = min(32, num_parts - base);
+#pragma unroll 4
+    for (int j = 0; j < cnt; ++j) {
+      const float w = __shfl_sync(0xffffffffu, wl, j);
       wsum += w;
-      const float* po = parts_out + ((size_t)p * rows + row) * D + lane * VPL;
+      const float* po = parts_out + ((size_t)(base + j) * rows + row) * D + lane * VPL;
 #pragma unroll
       for (int v = 0; v < VPL; ++v) acc[v] = fmaf(w, po[v], acc[v]);
     }

@@ -181,6 +181,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   const int NS = a.n_stages;
   const int TOK_STAGE = a.tok_stage;
 
+  asm volatile("griddepcontrol.launch_dependents;");  // the split merge may be scheduled behind this grid
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
       mbar_init(full_bar + 8 * i, 1);
@@ -744,69 +745,92 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------
-// Split merge: one warp per (sequence, query head); combines the partials of every CTA and
-// sub-tile warp that touched the sequence (algebra of combine_softmax_state,
-// fused_online_softmax_kernel.cuh:40-49 in the reference project, in base 2).
+// Split merge: one 4-warp block per (sequence, query head); the warps share the partials of every
+// CTA and sub-tile warp that touched the sequence and combine them (algebra of
+// combine_softmax_state, fused_online_softmax_kernel.cuh:40-49 in the reference project, in
+// base 2).  Launched as a programmatic dependent of the decode kernel: blocks may start early
+// and wait at griddepcontrol.wait until the decode kernel's results are visible.
 // ------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(128)
 merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
-  const int warp_global = blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (warp_global >= a.S * a.Hq) return;
-  const int s = warp_global / a.Hq, qh = warp_global - s * a.Hq;
+  constexpr float NEG_INF = -__builtin_huge_valf();
+  constexpr int VPL = D / 32;  // values per lane
+  __shared__ float s_max[4];
+  __shared__ float s_sum[4];
+  __shared__ float s_acc[4][D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int s = blockIdx.x / a.Hq, qh = blockIdx.x - s * a.Hq;
   int qbase, qlen;
   seq_q(a, s, qbase, qlen);
-  if (qlen <= 0) return;
   const int ctx = eff_ctx(a, s, page);
-  constexpr int VPL = D / 32;  // values per lane
-  if (ctx <= 0) {
-    for (int j = 0; j < qlen; ++j) {
-      const size_t row = (size_t)(qbase + j) * a.Hq + qh;
-#pragma unroll
-      for (int v = 0; v < VPL; ++v) store_out_elem(a.out, a.out_dtype, row * D + lane * VPL + v, 0.f);
-      if (a.lse && lane == 0) a.lse[row] = -__builtin_huge_valf();
-    }
-    return;
-  }
   const int kvh = qh / a.group, i = qh - kvh * a.group;
   const int hg = kvh / a.HG, h = kvh - hg * a.HG;
   const int sh = s * a.n_hg + hg;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (qlen <= 0) return;
+  if (ctx <= 0) {
+    for (int j = warp; j < qlen; j += 4) {
+      const size_t row = (size_t)(qbase + j) * a.Hq + qh;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) store_out_elem(a.out, a.out_dtype, row * D + lane * VPL + v, 0.f);
+      if (a.lse && lane == 0) a.lse[row] = NEG_INF;
+    }
+    return;
+  }
   const int32_t* tb = a.table + 4 * (size_t)sh;
   const int cta_first = tb[0], n_cta = tb[1], direct = tb[2];
   if (direct) return;
   const int n_parts = n_cta * a.SUBS;
+  const size_t pstride = (size_t)a.HG * a.rows_max;  // rows between consecutive parts
   for (int j = 0; j < qlen; ++j) {
     const int r = j * a.group + i;
     const size_t row = (size_t)(qbase + j) * a.Hq + qh;
-    float mx = -__builtin_huge_valf();
-    for (int p = lane; p < n_parts; p += 32) {
-      const size_t prow = (((size_t)(sh + cta_first) * a.SUBS + p) * a.HG + h) * a.rows_max + r;
-      mx = fmaxf(mx, a.part_lse[prow]);
-    }
+    const size_t row0 = (((size_t)(sh + cta_first) * a.SUBS) * a.HG + h) * a.rows_max + r;
+    float mx = NEG_INF;
+    for (int p = threadIdx.x; p < n_parts; p += 128) mx = fmaxf(mx, a.part_lse[row0 + p * pstride]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    const float mu = (mx == -__builtin_huge_valf()) ? 0.f : mx;
+    if (lane == 0) s_max[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
+    const float mu = (mx == NEG_INF) ? 0.f : mx;
     float acc[VPL];
 #pragma unroll
     for (int v = 0; v < VPL; ++v) acc[v] = 0.f;
     float wsum = 0.f;
-    for (int p = 0; p < n_parts; ++p) {
-      const size_t prow = (((size_t)(sh + cta_first) * a.SUBS + p) * a.HG + h) * a.rows_max + r;
-      const float w = fast_exp2(a.part_lse[prow] - mu);
-      if (w > 0.f) {
+    // warp w takes parts w, w+4, ...: weights 32 of its parts at a time (one per lane), then every
+    // lane walks the rows of those parts with independent loads
+    for (int base = 0; base < n_parts; base += 128) {
+      const int mine = base + 4 * lane + warp;
+      const float wl = mine < n_parts ? fast_exp2(a.part_lse[row0 + mine * pstride] - mu) : 0.f;
+      const int cnt = min(32, (n_parts - base - warp + 3) / 4);
+#pragma unroll 4
+      for (int jj = 0; jj < cnt; ++jj) {
+        const float w = __shfl_sync(0xffffffffu, wl, jj);
         wsum += w;
-        const float* po = a.part_o + prow * D + lane * VPL;
+        const float* po = a.part_o + (row0 + (size_t)(base + 4 * jj + warp) * pstride) * D + lane * VPL;
 #pragma unroll
         for (int v = 0; v < VPL; ++v) acc[v] = fmaf(w, po[v], acc[v]);
       }
     }
-    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
 #pragma unroll
-    for (int v = 0; v < VPL; ++v)
-      store_out_elem(a.out, a.out_dtype, row * D + lane * VPL + v, acc[v] * inv);
-    if (a.lse && lane == 0)
-      a.lse[row] = wsum > 0.f ? (mu + log2f(wsum)) * 0.69314718055994531f : -__builtin_huge_valf();
+    for (int v = 0; v < VPL; ++v) s_acc[warp][lane * VPL + v] = acc[v];
+    if (lane == 0) s_sum[warp] = wsum;
+    __syncthreads();
+    if (warp == 0) {
+      wsum = s_sum[0] + s_sum[1] + s_sum[2] + s_sum[3];
+      const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        const int d = lane * VPL + v;
+        store_out_elem(a.out, a.out_dtype, row * D + d,
+                       (s_acc[0][d] + s_acc[1][d] + s_acc[2][d] + s_acc[3][d]) * inv);
+      }
+      if (a.lse && lane == 0)
+        a.lse[row] = wsum > 0.f ? (mu + log2f(wsum)) * 0.69314718055994531f : NEG_INF;
+    }
+    __syncthreads();
   }
 }
 

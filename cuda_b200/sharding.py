@@ -131,16 +131,21 @@ def decode_split_context(local: DecodeWorkload, group: Optional[dist.ProcessGrou
     """Every rank calls this with the workload restricted to ITS KV range (``slice_context``).
     Returns the full attention output on every rank.
 
-    One collective: an all-gather of ``[total_q, Hq, D + 1]`` fp32 per rank (the partial output
-    with its log-sum-exp in the last column), issued on the current stream right after the local
-    kernel; the merge kernel follows on the same stream."""
+    The exchange is an all-gather of ``[total_q, Hq, D]`` fp32 plus ``[total_q, Hq]`` log-sum-exps
+    per rank, issued on the current stream right after the local kernel; the merge kernel follows
+    on the same stream and reads the gathered partials from local HBM."""
     world = dist.get_world_size(group)
     out, lse = partial_fn(local)                                   # [T,Hq,D] fp32, [T,Hq] natural log
-    packed = torch.cat((out.float(), lse.float().unsqueeze(-1)), dim=-1).contiguous()
-    gathered = torch.empty((world,) + tuple(packed.shape), dtype=packed.dtype, device=packed.device)
-    dist.all_gather(list(gathered.unbind(0)), packed, group=group)   # one slot per rank, written in place
-    dtype = out_dtype or local.query.dtype
-    return merge_fn(gathered[..., :-1].contiguous(), gathered[..., -1].contiguous(), dtype)
+    out, lse = out.float().contiguous(), lse.float().contiguous()
+    g_out = torch.empty((world,) + tuple(out.shape), dtype=torch.float32, device=out.device)
+    g_lse = torch.empty((world,) + tuple(lse.shape), dtype=torch.float32, device=out.device)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(g_out, out, group=group)
+        dist.all_gather_into_tensor(g_lse, lse, group=group)
+    else:                                                          # gloo (CPU ranks in the tests)
+        dist.all_gather(list(g_out.unbind(0)), out, group=group)
+        dist.all_gather(list(g_lse.unbind(0)), lse, group=group)
+    return merge_fn(g_out, g_lse, out_dtype or local.query.dtype)
 
 
 def gather_head_shards(local_out: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:

@@ -238,12 +238,16 @@ def _lognormal_lens(n, median, sigma, lo, hi, gen):
 
 def make_config(config_id: int, device="cpu", *, batch: Optional[int] = None,
                 ctx_scale: float = 1.0, seed: Optional[int] = None,
-                poison: bool = True) -> DecodeWorkload:
+                poison: bool = True, head_shards: int = 1, len_seed: Optional[int] = None) -> DecodeWorkload:
     """The benchmark configurations.  ``batch`` / ``ctx_scale`` shrink a configuration for
-    parity tests (same shapes and value distributions, fewer / shorter sequences)."""
+    parity tests (same shapes and value distributions, fewer / shorter sequences);
+    ``head_shards`` builds one KV-head shard (1/head_shards of the KV and query heads);
+    ``len_seed`` fixes the length draw independently of the data seed (ranks of a sharded run
+    share the lengths and differ in the data)."""
     seed = 1000 + config_id if seed is None else seed
     cg = torch.Generator()
-    cg.manual_seed(seed)
+    cg.manual_seed(seed if len_seed is None else len_seed)
+    hs = head_shards
     sc = lambda x: max(1, int(round(x * ctx_scale)))
     if config_id == 1:
         b = batch or 4
@@ -262,7 +266,7 @@ def make_config(config_id: int, device="cpu", *, batch: Optional[int] = None,
         b = batch or 128
         lens = _lognormal_lens(b, 4096 * ctx_scale, 1.0, sc(256), sc(32768), cg)
         return build_workload("cfg3_llama70b_mxfp8", context_lens=lens, q_lens=None,
-                              num_q_heads=64, num_kv_heads=8, head_dim=128, page_size=32,
+                              num_q_heads=64 // hs, num_kv_heads=8 // hs, head_dim=128, page_size=32,
                               q_dtype=torch.bfloat16, scale_mode=SCALE_MX_E8M0, pool_factor=1.0,
                               mx_exponent_range=(-4, 4), seed=seed, device=device, poison=poison)
     if config_id == 4:
