@@ -27,8 +27,17 @@ cudaError_t launch_merge_splits(const DecodeArgs& a, int page, cudaStream_t st);
       if (e != cudaSuccess) return e;                                                           \
       configured[dev] = 1;                                                                      \
     }                                                                                           \
-    kern<<<grid, kDecodeThreads, smem, st>>>(a);                                                \
-    return cudaGetLastError();                                                                  \
+    cudaLaunchConfig_t cfg = {};                                                                \
+    cfg.gridDim = dim3((unsigned)grid);                                                         \
+    cfg.blockDim = dim3(kDecodeThreads);                                                        \
+    cfg.dynamicSmemBytes = smem;                                                                \
+    cfg.stream = st;                                                                            \
+    cudaLaunchAttribute attr[1];                                                                \
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                            \
+    attr[0].val.programmaticStreamSerializationAllowed = 1;                                     \
+    cfg.attrs = attr;                                                                           \
+    cfg.numAttrs = 1;                                                                           \
+    return cudaLaunchKernelEx(&cfg, kern, a);                                                   \
   }
 
 // every page size and row-tile variant of one (MODE, D)

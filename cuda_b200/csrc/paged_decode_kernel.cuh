@@ -181,7 +181,11 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   const int NS = a.n_stages;
   const int TOK_STAGE = a.tok_stage;
 
-  asm volatile("griddepcontrol.launch_dependents;");  // the split merge may be scheduled behind this grid
+  // Launched as a programmatic dependent: nothing a previous kernel may still be writing (query,
+  // tables, the workspace the previous merge reads) is touched before this wait.  Our own dependent,
+  // the split merge, may be scheduled from here on.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
       mbar_init(full_bar + 8 * i, 1);
@@ -767,6 +771,7 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
   const int kvh = qh / a.group, i = qh - kvh * a.group;
   const int hg = kvh / a.HG, h = kvh - hg * a.HG;
   const int sh = s * a.n_hg + hg;
+  asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (qlen <= 0) return;
   if (ctx <= 0) {
