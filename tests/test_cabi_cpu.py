@@ -87,3 +87,23 @@ def test_ops_fail_loudly_without_library(monkeypatch):
     monkeypatch.setattr(L, "LIB_PATH", "/nonexistent/libcuda_llm_b200.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         L.load()
+
+
+CXX_SYMBOLS = {
+    ("paged", "f32"): "_Z24dispatch_paged_attentionIfEvPKT_S2_S2_PKiS4_PS0_iiiifP11CUstream_st",
+    ("paged", "f16"): "_Z24dispatch_paged_attentionI6__halfEvPKT_S3_S3_PKiS5_PS1_iiiifP11CUstream_st",
+    ("paged", "bf16"): "_Z24dispatch_paged_attentionI13__nv_bfloat16EvPKT_S3_S3_PKiS5_PS1_iiiifP11CUstream_st",
+    ("decode", "f32"): "_Z27dispatch_async_flash_decodeIfEvPKT_S2_S2_PS0_iiiifP11CUstream_st",
+    ("decode", "f16"): "_Z27dispatch_async_flash_decodeI6__halfEvPKT_S3_S3_PS1_iiiifP11CUstream_st",
+    ("decode", "bf16"): "_Z27dispatch_async_flash_decodeI13__nv_bfloat16EvPKT_S3_S3_PS1_iiiifP11CUstream_st",
+    ("fp8", "f32"): "_Z28dispatch_fp8_paged_attentionIffEvPKT0_PKaS4_PKfS6_PKiS8_PT_iiiiifbP11CUstream_st",
+    ("fp8", "f16"): "_Z28dispatch_fp8_paged_attentionI6__halfS0_EvPKT0_PKaS5_PKfS7_PKiS9_PT_iiiiifbP11CUstream_st",
+    ("fp8", "bf16"): "_Z28dispatch_fp8_paged_attentionI13__nv_bfloat16S0_EvPKT0_PKaS5_PKfS7_PKiS9_PT_iiiiifbP11CUstream_st",
+}
+
+
+def test_reference_cxx_dispatchers_are_exported(lib):
+    """The three templates of the reference's kernels_api.h, instantiated for its three dtypes, under
+    the names its binding's object file asks the linker for (Itanium mangling of those signatures)."""
+    for name in CXX_SYMBOLS.values():
+        assert hasattr(lib, name), name

@@ -279,3 +279,58 @@ def test_flash_decode_gqa(ops):
     ref = O.ref_flash_decode(q, k.repeat_interleave(4, dim=1), v.repeat_interleave(4, dim=1))
     out = ops.flash_decode(q.cuda(), k.cuda(), v.cuda())
     assert torch.allclose(out.float().cpu(), ref, atol=4e-2, rtol=4e-2)
+
+
+def test_reference_cxx_dispatcher_fp8(ops, golden):
+    """dispatch_fp8_paged_attention<__half,__half> called the way the reference binding calls it
+    (raw pointers, current stream), through its C++ symbol."""
+    import ctypes as C
+    from test_cabi_cpu import CXX_SYMBOLS
+    fn = getattr(ops.L.load(), CXX_SYMBOLS[("fp8", "f16")])
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 8 + [C.c_int] * 5 + [C.c_float, C.c_bool, C.c_void_p]
+    name, dtype, hd, lens = "fp8_f16_d128", torch.float16, 128, [300, 129, 64]
+    q, k, v, lens_t = cases.paged_inputs(dtype, hd, lens)
+    k8, v8, ks, vs, _, _ = cases.fp8_quantise(k, v)
+    bt = torch.from_numpy(golden[f"{name}/bt"])
+    perm = bt.reshape(-1).to(torch.int64)
+    kc = O.paged_layout_from_dense(k8, cases.PAGE, perm).cuda()
+    vc = O.paged_layout_from_dense(v8, cases.PAGE, perm).cuda()
+    qd, ksd, vsd, btd, ld = q.cuda(), ks.cuda(), vs.cuda(), bt.cuda(), lens_t.cuda()
+    out = torch.empty_like(qd)
+    fn(qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), ksd.data_ptr(), vsd.data_ptr(), btd.data_ptr(), ld.data_ptr(),
+       out.data_ptr(), 3, 4, hd, bt.shape[1], 16, 1.0 / hd ** 0.5, False, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    ref = torch.from_numpy(golden[f"{name}/out"])
+    assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+def test_reference_cxx_dispatcher_paged_and_decode(ops, golden):
+    import ctypes as C
+    from test_cabi_cpu import CXX_SYMBOLS
+    lib = ops.L.load()
+    st = torch.cuda.current_stream().cuda_stream
+    fn = getattr(lib, CXX_SYMBOLS[("paged", "bf16")])
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 6 + [C.c_int] * 4 + [C.c_float, C.c_void_p]
+    name, dtype, hd, lens = "paged_bf16_d64_l1", torch.bfloat16, 64, [300, 129, 64]
+    q, k, v, lens_t = cases.paged_inputs(dtype, hd, lens)
+    bt = torch.from_numpy(golden[f"{name}/bt"])
+    perm = bt.reshape(-1).to(torch.int64)
+    kc, vc = O.paged_layout_from_dense(k, 16, perm).cuda(), O.paged_layout_from_dense(v, 16, perm).cuda()
+    qd, btd, ld = q.cuda(), bt.cuda(), lens_t.cuda()
+    out = torch.empty_like(qd)
+    fn(qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), btd.data_ptr(), ld.data_ptr(), out.data_ptr(), 3, 4, hd,
+       bt.shape[1], 1.0 / hd ** 0.5, st)
+    torch.cuda.synchronize()
+    assert torch.allclose(out.float().cpu(), torch.from_numpy(golden[f"{name}/out"]), atol=4e-2, rtol=4e-2)
+    fn = getattr(lib, CXX_SYMBOLS[("decode", "f32")])
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float, C.c_void_p]
+    q = torch.randn(2, 4, 1, 128, device="cuda")
+    k = torch.randn(2, 4, 500, 128, device="cuda")
+    v = torch.randn(2, 4, 500, 128, device="cuda")
+    out = torch.empty_like(q)
+    fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 2, 4, 500, 128, 1.0 / 128 ** 0.5, st)
+    torch.cuda.synchronize()
+    assert torch.allclose(out.cpu(), O.ref_flash_decode(q.cpu(), k.cpu(), v.cpu()), atol=1e-4, rtol=1e-4)
