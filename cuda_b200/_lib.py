@@ -45,6 +45,7 @@ SYMBOLS = {
                                                                             C.c_size_t, C.c_void_p]),
     "cuda_llm_flash_decode": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 5 + [C.c_float, C.c_int32, C.c_void_p,
                                                                          C.c_size_t, C.c_void_p]),
+    "cuda_llm_kv_append": (C.c_int, [C.c_void_p] * 8 + [C.c_int32] * 8 + [C.c_void_p, C.c_void_p]),
     "cuda_llm_decode_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]),
     "cuda_llm_merge_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
                                           C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),

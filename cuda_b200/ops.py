@@ -233,6 +233,25 @@ def async_flash_decode(q, k, v, softmax_scale=None):
 flash_decode = async_flash_decode      # the name the reference's README gives the Python-level call
 
 
+def kv_cache_append(k_new, v_new, slot_block, slot_offset, key_cache, value_cache, k_scale, v_scale):
+    """Quantise and store new K/V tokens ``[n, Hkv, D]`` at pages ``slot_block`` / offsets
+    ``slot_offset`` (int32 ``[n]``).  Scale mode and V format are taken from the cache tensors as in
+    ``fp8_paged_attention_forward``; per-token and E8M0 scales are written, coarser scales are read."""
+    n, hkv, d = k_new.shape
+    nb, _, _, page = key_cache.shape
+    mode = _scale_mode(k_scale)
+    v_format = L.KV_FP8_E4M3 if value_cache.shape[2] == d else L.KV_FP4_E2M1
+    if k_new.dtype not in _DTYPE or v_new.dtype != k_new.dtype:
+        raise RuntimeError("new K/V must be float32, float16 or bfloat16 and of one dtype")
+    k_new, v_new = k_new.contiguous(), v_new.contiguous()
+    with torch.cuda.device(k_new.device):
+        L.check(L.load().cuda_llm_kv_append(k_new.data_ptr(), v_new.data_ptr(), slot_block.data_ptr(),
+                                            slot_offset.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+                                            k_scale.data_ptr(), v_scale.data_ptr(), n, hkv, d, page, nb,
+                                            _DTYPE[k_new.dtype], v_format, mode, None,
+                                            _stream_ptr(k_new.device)), "cuda_llm_kv_append")
+
+
 def decode_status(workspace: torch.Tensor, device=None) -> int:
     """Read and clear the device status word (synchronises the current stream)."""
     device = workspace.device if device is None else device

@@ -119,6 +119,29 @@ def _e8m0_to_float(b: torch.Tensor) -> torch.Tensor:
     return torch.exp2(b.float() - 127.0)
 
 
+def quantize_tokens(x: torch.Tensor, fmt: str, mode: str, scale: Optional[torch.Tensor] = None):
+    """Host statement of the cache write recipe for token-major input ``x [n, H, D]`` (fp32):
+    returns (codes uint8 ``[n, H, D]`` or packed ``[n, H, D/2]``, scale).  Per token:
+    ``scale = max(amax/448, 1e-8)``; E8M0: ``floor(log2(amax_block)) - emax`` per 32-element block;
+    per head: the given ``scale [H]``."""
+    n, h, d = x.shape
+    x = x.float()
+    if mode == SCALE_PER_TOKEN:
+        sc = (x.abs().amax(dim=2) / E4M3_MAX).clamp_min(1e-8)               # [n,H]
+        return quant_e4m3(x / sc.unsqueeze(-1)), sc
+    if mode == SCALE_PER_HEAD:
+        return quant_e4m3(x / scale.view(1, h, 1)), scale
+    if mode == SCALE_MX_E8M0:
+        xb = x.view(n, h, d // 32, 32)
+        eb = _mx_exponent(xb.abs().amax(dim=3), 8 if fmt == KV_FP8_E4M3 else 2)   # [n,H,D/32]
+        y = xb / _e8m0_to_float(eb).unsqueeze(-1)
+        if fmt == KV_FP8_E4M3:
+            return quant_e4m3(y.clamp(-E4M3_MAX, E4M3_MAX)).view(n, h, d), eb
+        c = quant_e2m1(y).view(n, h, d // 2, 2)
+        return (c[..., 0] | (c[..., 1] << 4)).contiguous(), eb
+    raise ValueError(mode)
+
+
 # --------------------------------------------------------------------------------------
 # Workload builder
 # --------------------------------------------------------------------------------------

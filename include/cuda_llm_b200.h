@@ -164,6 +164,17 @@ int cuda_llm_merge_partials(const float* parts_out, const float* parts_lse, int3
                             int64_t rows, int32_t head_dim, void* out, int32_t out_dtype,
                             float* lse, void* stream);
 
+/* Write n_tokens new K/V vectors ([n_tokens, Hkv, D] of in_dtype) into the paged quantised cache
+ * at (slot_block[i], slot_offset[i]), quantising on the fly with the reference test's recipe
+ * (tests/test_kernels_misc.py:51-55 extended to per-token and E8M0 block scales): per-token and
+ * E8M0 scales are computed and stored, per-head / per-block scales are read.  No counterpart kernel
+ * in the reference (it quantises with torch on the host).  `status` may be NULL. */
+int cuda_llm_kv_append(const void* k_new, const void* v_new, const int32_t* slot_block,
+                       const int32_t* slot_offset, void* key_cache, void* value_cache, void* k_scale,
+                       void* v_scale, int32_t n_tokens, int32_t num_kv_heads, int32_t head_dim,
+                       int32_t page_size, int32_t num_blocks, int32_t in_dtype, int32_t v_format,
+                       int32_t scale_mode, uint32_t* status, void* stream);
+
 /* Bit-exact dequantisation of whole pages to fp32 (test and debugging aid):
  * out [n_pages, Hkv, D, page] fp32 for the pages listed in `pages`. */
 int cuda_llm_dequant_pages(const void* cache, const void* scale, const int32_t* pages,

@@ -1,0 +1,81 @@
+"""The cache-append kernel writes exactly the bytes and scales of the host recipe, at the right
+place of the paged layout, and the decode kernel reads them back."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("mode,vfmt", [("per_token", "fp8_e4m3"), ("mx_e8m0", "fp8_e4m3"),
+                                       ("mx_e8m0", "fp4_e2m1"), ("per_head", "fp8_e4m3")])
+@pytest.mark.parametrize("d,page,dtype", [(128, 16, torch.bfloat16), (64, 32, torch.float32), (128, 64, torch.float16)])
+def test_append_is_bit_exact(mode, vfmt, d, page, dtype):
+    from cuda_b200 import ops, workloads as W
+    torch.manual_seed(3)
+    n, h, nb = 37, 4, 11
+    # magnitudes spread over many binades so that block exponents and subnormal codes are exercised
+    mag = torch.exp2(torch.randint(-12, 6, (n, h, d // 32, 1)).float()).expand(n, h, d // 32, 32).reshape(n, h, d)
+    k = (torch.randn(n, h, d) * mag).to(dtype)
+    v = (torch.randn(n, h, d) * mag).to(dtype)
+    k[3] = 0                                                   # an all-zero token
+    slots = torch.randperm(nb * page)[:n]
+    blk, off = (slots // page).to(torch.int32), (slots % page).to(torch.int32)
+    # per-head scales by the reference recipe (tests/test_kernels_misc.py:51-52): amax / 448 per head
+    k_head = (k.float().abs().amax(dim=(0, 2)) / 448.0).clamp_min(1e-8)
+    v_head = (v.float().abs().amax(dim=(0, 2)) / 448.0).clamp_min(1e-8)
+    kc_ref, ks_ref = W.quantize_tokens(k.float(), "fp8_e4m3", mode, k_head)
+    vc_ref, vs_ref = W.quantize_tokens(v.float(), vfmt, mode, v_head)
+    dv = d // 2 if vfmt == "fp4_e2m1" else d
+    kc = torch.full((nb, h, d, page), 0xAA, dtype=torch.uint8, device="cuda")
+    vc = torch.full((nb, h, dv, page), 0xAA, dtype=torch.uint8, device="cuda")
+    if mode == "per_token":
+        ks = torch.full((nb, h, page), -1.0, device="cuda"); vs = ks.clone()
+    elif mode == "mx_e8m0":
+        ks = torch.full((nb, h, d // 32, page), 0xAA, dtype=torch.uint8, device="cuda"); vs = ks.clone()
+    else:
+        ks = k_head.cuda(); vs = v_head.cuda()
+    ops.kv_cache_append(k.cuda(), v.cuda(), blk.cuda(), off.cuda(), kc, vc, ks, vs)
+    torch.cuda.synchronize()
+    b, o = blk.long(), off.long()
+    assert torch.equal(kc.cpu()[b, :, :, o], kc_ref)            # [n,h,d]
+    assert torch.equal(vc.cpu()[b, :, :, o], vc_ref)
+    if mode == "per_token":
+        assert torch.equal(ks.cpu()[b, :, o], ks_ref) and torch.equal(vs.cpu()[b, :, o], vs_ref)
+    elif mode == "mx_e8m0":
+        assert torch.equal(ks.cpu()[b, :, :, o], ks_ref) and torch.equal(vs.cpu()[b, :, :, o], vs_ref)
+    # untouched slots keep their fill
+    untouched = torch.ones(nb, page, dtype=torch.bool)
+    untouched[b, o] = False
+    assert (kc.cpu().permute(0, 3, 1, 2)[untouched] == 0xAA).all()
+
+
+def test_append_then_decode_round_trip():
+    """Fill a cache token by token with the append kernel, then attend over it: same result as the
+    oracle on the host-quantised cache."""
+    from cuda_b200 import ops, workloads as W
+    from helpers import assert_parity, oracle_out
+    wl = W.build_workload("rt", context_lens=[45, 130], q_lens=None, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                          page_size=16, q_dtype=torch.bfloat16, scale_mode="per_token", pool_factor=1.0, seed=8,
+                          poison=False)
+    torch.manual_seed(9)
+    g = wl.to("cuda")
+    kc, vc = torch.zeros_like(g.key_cache), torch.zeros_like(g.value_cache)
+    ks, vs = torch.ones_like(g.k_scale), torch.ones_like(g.v_scale)
+    import dataclasses
+    ref_wl = dataclasses.replace(wl, key_cache=wl.key_cache.clone(), value_cache=wl.value_cache.clone(),
+                                 k_scale=wl.k_scale.clone(), v_scale=wl.v_scale.clone())
+    for s, ctx in enumerate([45, 130]):
+        k = torch.randn(ctx, 2, 128)
+        v = torch.randn(ctx, 2, 128)
+        pos = torch.arange(ctx)
+        blk = wl.block_tables[s, pos // 16]
+        off = (pos % 16).to(torch.int32)
+        ops.kv_cache_append(k.cuda(), v.cuda(), blk.cuda(), off.cuda(), kc, vc, ks, vs)
+        kq, ksc = W.quantize_tokens(k, "fp8_e4m3", "per_token")
+        vq, vsc = W.quantize_tokens(v, "fp8_e4m3", "per_token")
+        ref_wl.key_cache[blk.long(), :, :, off.long()] = kq
+        ref_wl.value_cache[blk.long(), :, :, off.long()] = vq
+        ref_wl.k_scale[blk.long(), :, off.long()] = ksc
+        ref_wl.v_scale[blk.long(), :, off.long()] = vsc
+    out = ops.fp8_paged_attention_forward(g.query, kc, vc, ks, vs, g.block_tables, g.context_lens, check_status=True)
+    assert_parity(out, oracle_out(ref_wl), torch.bfloat16, "append + decode")
