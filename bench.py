@@ -277,19 +277,25 @@ def main():
     step()
     # (3) end to end through the public op with host buffers: the step's inputs (query, block
     #     tables, context lengths, query offsets) come from pinned host memory, the result goes back
-    host_in = [t.cpu().pin_memory() for t in (wl.query, wl.block_tables, wl.context_lens)]
-    host_cu = wl.cu_q_lens.cpu().pin_memory() if wl.cu_q_lens is not None else None
-    dev_in = [torch.empty_like(t, device=dev) for t in host_in]
-    dev_cu = torch.empty_like(host_cu, device=dev) if host_cu is not None else None
+    #     The inputs sit in ONE pinned staging buffer and go over in one copy per step (a serving
+    #     loop assembles its step inputs in such a buffer anyway); the device tensors are views.
+    srcs = [wl.query, wl.block_tables, wl.context_lens] + ([wl.cu_q_lens] if wl.cu_q_lens is not None else [])
+    sizes = [(t.numel() * t.element_size() + 255) // 256 * 256 for t in srcs]
+    h2d = sum(t.numel() * t.element_size() for t in srcs)
+    host_stage = torch.empty(sum(sizes), dtype=torch.uint8).pin_memory()
+    dev_stage = torch.empty(sum(sizes), dtype=torch.uint8, device=dev)
+    dev_in, off = [], 0
+    for t, n in zip(srcs, sizes):
+        nb = t.numel() * t.element_size()
+        host_stage[off:off + nb].copy_(t.cpu().contiguous().view(torch.uint8).view(-1))
+        dev_in.append(dev_stage[off:off + nb].view(t.dtype).view(t.shape))
+        off += n
+    dev_cu = dev_in[3] if wl.cu_q_lens is not None else None
     host_out = torch.empty(wl.query.shape, dtype=wl.query.dtype).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host_in) + (host_cu.numel() * 4 if host_cu is not None else 0)
     d2h = host_out.numel() * host_out.element_size()
 
     def e2e_step():
-        for d, h in zip(dev_in, host_in):
-            d.copy_(h, non_blocking=True)
-        if dev_cu is not None:
-            dev_cu.copy_(host_cu, non_blocking=True)
+        dev_stage.copy_(host_stage, non_blocking=True)
         if split_ctx:
             import dataclasses
             lw = dataclasses.replace(wl, query=dev_in[0], block_tables=dev_in[1], context_lens=dev_in[2])
