@@ -317,7 +317,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       if (seg_fresh || ic.tile == 0) {
         seg_cta_first = (int)(ic.seg_first / per_cta);
         seg_n_cta = (int)((ic.seg_first + ic.tiles - 1) / per_cta) - seg_cta_first + 1;
-        seg_direct = (a.SUBS == 1) && (seg_n_cta == 1);
+        // direct output needs one warp per (head, row): not when two warps share the rows of a
+        // short query (NT == 2 kernel, at most 8 live rows)
+        seg_direct = (a.SUBS == 1) && (seg_n_cta == 1) && !(NT == 2 && a.group * ic.qlen <= 8);
       }
       const int tok0 = ic.tile * TOK_STAGE;
       const int np = min(PPS, (ic.ctx - tok0 + PAGE - 1) / PAGE);
@@ -421,6 +423,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   float kscale_head = 1.f, vscale_head = 1.f;
   int kvh = 0, R = 0, qbase = 0, qlen = 0;
   bool live = false;  // this warp has query rows in the current segment
+  // NT == 2 kernels: a segment with at most 8 live rows does not need two row halves; the two
+  // warps of a pair then take one 16-token m-tile each (all rows) instead of idling one of them
+  bool helper = false;
+  int rb = 0, mt_lo = 0, mt_hi = MT;  // first query row of this warp; m-tiles it computes
 
   for (int it = 0; it < n_units; ++it) {
     const int slot = it % NS;
@@ -441,10 +447,14 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       qlen = (int)m1.w;
       kvh = hg * a.HG + h;
       R = a.group * qlen;  // live query rows of this KV head
-      live = nt_w * 8 < R;
+      helper = (NT == 2) && (R <= 8);
+      rb = helper ? 0 : nt_w * 8;
+      mt_lo = helper ? nt_w : 0;
+      mt_hi = helper ? nt_w + 1 : MT;
+      live = rb < R;
       // ---- Q fragments: B operand of S^T = K * Q^T, f16 pairs (d, d+1) with
       // b0: d = 16kt + 2t, b1: d = 16kt + 8 + 2t.  An fp32 Q keeps a second f16 word (PRECISE).
-      const int r = nt_w * 8 + g;
+      const int r = rb + g;
       const bool row_live = r < R;
       const int jq = row_live ? r / a.group : 0;
       const int iq = row_live ? r - jq * a.group : 0;
@@ -486,7 +496,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
 
     const int nv = min(SUB, ctx - tok0 - ts * SUB);  // valid tokens of this warp's sub-tile
     if (nv > 0 && live && !(a.debug & 1)) {
-      const bool tail = nv < SUB;
+      const bool tail = nv < SUB || helper;  // masking path (dead tokens, or an m-tile left to the partner)
       // causal limit: query row r = j*group + i sees positions < ctx - qlen + 1 + j
       const int pos0 = tok0 + ts * SUB;  // absolute position of sub-tile token 0
       const bool need_causal = (qlen > 1) && (pos0 + SUB > ctx - qlen + 1);
@@ -505,6 +515,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
+          if (NT == 2 && (mt < mt_lo || mt >= mt_hi)) continue;
           uint32_t r4[4];
           ldmatrix_x4_trans(r4, sb + k_lm[mt] + ks * 32 * PAGE);
           float tacc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -576,9 +587,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           float xx = fmaf(sacc[mt][c], ksc[mt][j] * a.scale_log2, vlg[mt][j]);
           if (tail || need_causal) {
             const int tok = 16 * mt + 2 * g + j;
-            bool vis = tok < nv;
+            bool vis = tok < nv && mt >= mt_lo && mt < mt_hi;
             if (need_causal) {
-              const int r = nt_w * 8 + 2 * t + (c & 1);
+              const int r = rb + 2 * t + (c & 1);
               const int jq = r / a.group;
               vis = vis && (pos0 + tok < ctx - qlen + 1 + jq);
             }
@@ -650,13 +661,21 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int dp = 0; dp < D / ROWS_PER_LDSM; ++dp) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
+          if (NT == 2 && (mt < mt_lo || mt >= mt_hi)) continue;
           uint32_t va[4];
           ldmatrix_x4(va, sb + v_lm[mt] + dp * 32 * PAGE);
           if (tail) {  // codes of dead slots may be NaN: 0 * NaN must not reach the accumulator
             va[0] &= vmask[mt]; va[1] &= vmask[mt]; va[2] &= vmask[mt]; va[3] &= vmask[mt];
           }
           if (!V4) {
-            // va[0], va[1]: rows g, g+8 of O m-tile 2dp; va[2], va[3]: of m-tile 2dp+1
+            // va[0], va[1]: rows g, g+8 of O m-tile 2dp; va[2], va[3]: of m-tile 2dp+1 (one scale block)
+            uint32_t s02 = 0u, s13 = 0u;
+            if (MX) {
+              uint32_t e = lds32(sb + vs_mx[mt] + dp * PAGE);  // E8M0 of tokens 4t..4t+3, block dp
+              if (tail) e = (e & vmask[mt]) | (0x7f7f7f7fu & ~vmask[mt]);
+              s02 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4240));  // tokens 4t, 4t+2
+              s13 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4341));  // tokens 4t+1, 4t+3
+            }
 #pragma unroll
             for (int kk = 0; kk < 2; ++kk) {
               const int mo = 2 * dp + kk;
@@ -664,10 +683,6 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
               uint32_t A0 = e4m3x2_to_f16x2_lo(x0), A1 = e4m3x2_to_f16x2_lo(x1);
               uint32_t A2 = e4m3x2_to_f16x2_hi(x0), A3 = e4m3x2_to_f16x2_hi(x1);
               if (MX) {
-                uint32_t e = lds32(sb + vs_mx[mt] + (mo / 2) * PAGE);  // E8M0 of tokens 4t..4t+3
-                if (tail) e = (e & vmask[mt]) | (0x7f7f7f7fu & ~vmask[mt]);
-                const uint32_t s02 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4240));
-                const uint32_t s13 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4341));
                 A0 = hmul2(A0, s02); A1 = hmul2(A1, s02); A2 = hmul2(A2, s13); A3 = hmul2(A3, s13);
               }
               mma_f16(oacc[mo], A0, A1, A2, A3, pb[mt][0], pb[mt][1]);
@@ -675,19 +690,22 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             }
           } else {
             // packed E2M1: matrix m holds byte rows 32dp + 8m + g, i.e. O m-tile 4dp + m:
-            // d = 16*mo + 2g in the low nibble (row g) and d + 1 in the high nibble (row g+8)
+            // d = 16*mo + 2g in the low nibble (row g) and d + 1 in the high nibble (row g+8);
+            // m-tiles 4dp, 4dp+1 share scale block 2dp, m-tiles 4dp+2, 4dp+3 share block 2dp+1
 #pragma unroll
-            for (int m = 0; m < 4; ++m) {
-              const int mo = 4 * dp + m;
-              const uint32_t ex = e2m1_lo_nibbles_to_f16_hi_bytes(va[m]), ox = e2m1_hi_nibbles_to_f16_hi_bytes(va[m]);
-              uint32_t A0 = prmt(ex, 0u, 0x2404), A1 = prmt(ox, 0u, 0x2404);  // tokens 4t, 4t+2
-              uint32_t A2 = prmt(ex, 0u, 0x3414), A3 = prmt(ox, 0u, 0x3414);  // tokens 4t+1, 4t+3
-              uint32_t e = lds32(sb + vs_mx[mt] + (mo / 2) * PAGE);
+            for (int bb = 0; bb < 2; ++bb) {
+              uint32_t e = lds32(sb + vs_mx[mt] + (2 * dp + bb) * PAGE);
               if (tail) e = (e & vmask[mt]) | (0x7f7f7f7fu & ~vmask[mt]);
               const uint32_t s02 = e8m0_pair_to_f16x2<kE2M1ScaleShift>(prmt(e, 0u, 0x4240));
               const uint32_t s13 = e8m0_pair_to_f16x2<kE2M1ScaleShift>(prmt(e, 0u, 0x4341));
-              A0 = hmul2(A0, s02); A1 = hmul2(A1, s02); A2 = hmul2(A2, s13); A3 = hmul2(A3, s13);
-              mma_f16(oacc[mo], A0, A1, A2, A3, pb[mt][0], pb[mt][1]);
+#pragma unroll
+              for (int mm = 0; mm < 2; ++mm) {
+                const int m = 2 * bb + mm, mo = 4 * dp + m;
+                const uint32_t ex = e2m1_lo_nibbles_to_f16_hi_bytes(va[m]), ox = e2m1_hi_nibbles_to_f16_hi_bytes(va[m]);
+                const uint32_t A0 = hmul2(prmt(ex, 0u, 0x2404), s02), A1 = hmul2(prmt(ox, 0u, 0x2404), s02);
+                const uint32_t A2 = hmul2(prmt(ex, 0u, 0x3414), s13), A3 = hmul2(prmt(ox, 0u, 0x3414), s13);
+                mma_f16(oacc[mo], A0, A1, A2, A3, pb[mt][0], pb[mt][1]);
+              }
             }
           }
         }
@@ -716,7 +734,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       const float lse1 = (l1 > 0.f) ? m_run[1] + log2f(l1) : NEG_INF;
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        const int r = nt_w * 8 + 2 * t + cc;
+        const int r = rb + 2 * t + cc;
         if (r >= R) continue;
         const float inv = cc ? inv1 : inv0;
         const float lse2 = cc ? lse1 : lse0;
@@ -732,7 +750,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           }
           if (a.lse && g == 0) a.lse[row] = lse2 * 0.69314718055994531f;
         } else {
-          const size_t prow = (((size_t)mslot * a.SUBS + ts) * a.HG + h) * a.rows_max + r;
+          // a helper pair stores its second result in the unused upper rows
+          const size_t prow = (((size_t)mslot * a.SUBS + ts) * a.HG + h) * a.rows_max + r + (helper ? nt_w * 8 : 0);
           float* po = a.part_o + prow * D;
 #pragma unroll
           for (int mt = 0; mt < KT; ++mt) {
@@ -786,14 +805,17 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
   const int32_t* tb = a.table + 4 * (size_t)sh;
   const int cta_first = tb[0], n_cta = tb[1], direct = tb[2];
   if (direct) return;
-  const int n_parts = n_cta * a.SUBS;
-  const size_t pstride = (size_t)a.HG * a.rows_max;  // rows between consecutive parts
+  // a 16-row kernel leaves two results per sub-tile for a query of at most 8 rows (rows r, r + 8)
+  const int dup = (a.rows_max == 16 && a.group * qlen <= 8) ? 2 : 1;
+  const int n_parts = n_cta * a.SUBS * dup;
+  const size_t pstride = (size_t)a.HG * a.rows_max;  // rows between consecutive sub-tile results
+  auto part_row = [&](size_t row0, int p) -> size_t { return row0 + (size_t)(p / dup) * pstride + (size_t)(p % dup) * 8; };
   for (int j = 0; j < qlen; ++j) {
     const int r = j * a.group + i;
     const size_t row = (size_t)(qbase + j) * a.Hq + qh;
     const size_t row0 = (((size_t)(sh + cta_first) * a.SUBS) * a.HG + h) * a.rows_max + r;
     float mx = NEG_INF;
-    for (int p = threadIdx.x; p < n_parts; p += 128) mx = fmaxf(mx, a.part_lse[row0 + p * pstride]);
+    for (int p = threadIdx.x; p < n_parts; p += 128) mx = fmaxf(mx, a.part_lse[part_row(row0, p)]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) s_max[warp] = mx;
@@ -808,13 +830,13 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
     // lane walks the rows of those parts with independent loads
     for (int base = 0; base < n_parts; base += 128) {
       const int mine = base + 4 * lane + warp;
-      const float wl = mine < n_parts ? fast_exp2(a.part_lse[row0 + mine * pstride] - mu) : 0.f;
+      const float wl = mine < n_parts ? fast_exp2(a.part_lse[part_row(row0, mine)] - mu) : 0.f;
       const int cnt = min(32, (n_parts - base - warp + 3) / 4);
 #pragma unroll 4
       for (int jj = 0; jj < cnt; ++jj) {
         const float w = __shfl_sync(0xffffffffu, wl, jj);
         wsum += w;
-        const float* po = a.part_o + (row0 + (size_t)(base + 4 * jj + warp) * pstride) * D + lane * VPL;
+        const float* po = a.part_o + part_row(row0, base + 4 * jj + warp) * D + lane * VPL;
 #pragma unroll
         for (int v = 0; v < VPL; ++v) acc[v] = fmaf(w, po[v], acc[v]);
       }
