@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "lib", "libcuda_llm_b200.so")
 OK, EINVAL, EALIGN, EWORKSPACE, ECUDA, EDEVICE = 0, -1, -2, -3, -4, -5
 ST_BAD_BLOCK, ST_BAD_CTX, ST_TIMEOUT, ST_BAD_QLEN = 1, 2, 4, 8
 F32, F16, BF16 = 0, 1, 2
-KV_FP8_E4M3, KV_FP4_E2M1, KV_INT8 = 0, 1, 2
+KV_FP8_E4M3, KV_FP4_E2M1, KV_INT8, KV_F16, KV_BF16 = 0, 1, 2, 3, 4
 SCALE_PER_HEAD, SCALE_PER_BLOCK, SCALE_PER_TOKEN, SCALE_MX_E8M0 = 0, 1, 2, 3
 FLAG_SKIP_MERGE = 1
 

@@ -58,7 +58,7 @@ static int sm_count_cached() {
 
 // Pure arithmetic (no device access when num_ctas > 0): shared-memory stage layout and
 // workspace carving for one problem shape.
-static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, int v_format,
+static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, int k_format, int v_format,
                        int scale_mode, int num_ctas, Layout& L) {
   if (S < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return fail(CUDA_LLM_EINVAL, "num_q_heads must be a positive multiple of num_kv_heads");
   if (D != 64 && D != 128) return fail(CUDA_LLM_EINVAL, "Only head_dim 64 and 128 supported");
@@ -68,22 +68,30 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   if (group * max_q_len > 16) return fail(CUDA_LLM_EINVAL, "(num_q_heads/num_kv_heads) * max_q_len must be <= 16");
   L.NT = (group * max_q_len <= 8) ? 1 : 2;
   L.rows_max = 8 * L.NT;
+  // An 8-bit stage holds 256 (token, head) pairs, a 16-bit stage 128: the same bytes.
+  const bool kv16 = (k_format == CUDA_LLM_KV_F16 || k_format == CUDA_LLM_KV_BF16);
+  const int eb = kv16 ? 2 : 1;
+  const int pairs = 256 / eb;
   int HG = 8;
   while (Hkv % HG) HG >>= 1;
-  if (page == 64 && HG > 4) HG = 4;  // a stage must hold whole pages: 256/HG >= page
+  while (pairs / HG < page) HG >>= 1;  // a stage must hold whole pages
   L.HG = HG;
-  // 16 consumer warps: NT == 1 -> (HG heads) x (16/HG sub-tiles of 16 tokens);
-  //                    NT == 2 -> 2 row halves x (HG heads) x (8/HG sub-tiles of 32 tokens)
+  // 16 consumer warps, 8 bit: NT == 1 -> (HG heads) x (16/HG sub-tiles of 16 tokens);
+  //                           NT == 2 -> 2 row halves x (HG heads) x (8/HG sub-tiles of 32 tokens)
+  //                    16 bit: NT == 1 -> 2 stage parities x (HG heads) x (8/HG sub-tiles of 16 tokens)
+  //                           NT == 2 -> 2 row halves x the same
+  // either way a (CTA, head) leaves SUBS results of rows_max rows
   L.SUBS = (L.NT == 1 ? 16 : 8) / HG;
-  L.tok_stage = 256 / HG;
+  L.tok_stage = pairs / HG;
   L.n_hg = Hkv / HG;
   L.PPS = (L.tok_stage >= page) ? L.tok_stage / page : 1;
   if (L.PPS > kMaxPagesPerStage) return fail(CUDA_LLM_EINVAL, "internal: too many pages per stage");
   const uint32_t pad = 0;  // every 16-token m-tile lies inside one page: no padding between pages
   const int DV = (v_format == CUDA_LLM_KV_FP4_E2M1) ? D / 2 : D;
-  L.k_chunk = (uint32_t)HG * D * page;
-  L.v_chunk = (uint32_t)HG * DV * page;
-  if (scale_mode == CUDA_LLM_SCALE_PER_TOKEN) L.ks_chunk = L.vs_chunk = (uint32_t)HG * page * 4;
+  L.k_chunk = (uint32_t)HG * D * page * eb;
+  L.v_chunk = (uint32_t)HG * DV * page * eb;
+  if (kv16) L.ks_chunk = L.vs_chunk = 0;
+  else if (scale_mode == CUDA_LLM_SCALE_PER_TOKEN) L.ks_chunk = L.vs_chunk = (uint32_t)HG * page * 4;
   else if (scale_mode == CUDA_LLM_SCALE_MX_E8M0) L.ks_chunk = L.vs_chunk = (uint32_t)HG * (D / 32) * page;
   else L.ks_chunk = L.vs_chunk = 0;
   L.k_page_stride = L.k_chunk + pad;
@@ -133,6 +141,17 @@ template <int MODE>
 static LaunchFn pick_d(int D, int page, int NT, bool precise) {
   return D == 64 ? pick_page_nt<64, MODE>(page, NT, precise) : pick_page_nt<128, MODE>(page, NT, precise);
 }
+template <int D, int MODE>
+static LaunchFn pick_kv16_page(int page, int NT) {
+  if (page == 16) return NT == 2 ? launch_paged_decode<D, 16, MODE, 2, false> : launch_paged_decode<D, 16, MODE, 1, false>;
+  if (page == 32) return NT == 2 ? launch_paged_decode<D, 32, MODE, 2, false> : launch_paged_decode<D, 32, MODE, 1, false>;
+  if (page == 64) return NT == 2 ? launch_paged_decode<D, 64, MODE, 2, false> : launch_paged_decode<D, 64, MODE, 1, false>;
+  return nullptr;
+}
+static LaunchFn pick_kv16(bool bf16, int D, int page, int NT) {
+  if (bf16) return D == 64 ? pick_kv16_page<64, MODE_KV_BF16>(page, NT) : pick_kv16_page<128, MODE_KV_BF16>(page, NT);
+  return D == 64 ? pick_kv16_page<64, MODE_KV_F16>(page, NT) : pick_kv16_page<128, MODE_KV_F16>(page, NT);
+}
 
 }  // namespace b200
 
@@ -155,10 +174,14 @@ size_t cuda_llm_paged_decode_workspace_bytes(int32_t num_seqs, int32_t num_q_hea
                                              int32_t num_ctas) {
   Layout L;
   // the workspace does not depend on the formats
-  if (make_layout(num_seqs, num_q_heads, num_kv_heads, head_dim, page_size, max_q_len,
+  if (make_layout(num_seqs, num_q_heads, num_kv_heads, head_dim, page_size, max_q_len, CUDA_LLM_KV_FP8_E4M3,
                   CUDA_LLM_KV_FP8_E4M3, CUDA_LLM_SCALE_PER_TOKEN, num_ctas, L) != CUDA_LLM_OK)
     return 0;
-  return L.ws_total;
+  size_t need = L.ws_total;  // a 16-bit cache may group fewer heads per stage: cover it too
+  if (make_layout(num_seqs, num_q_heads, num_kv_heads, head_dim, page_size, max_q_len, CUDA_LLM_KV_BF16,
+                  CUDA_LLM_KV_BF16, CUDA_LLM_SCALE_PER_HEAD, num_ctas, L) == CUDA_LLM_OK && L.ws_total > need)
+    need = L.ws_total;
+  return need;
 }
 
 int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
@@ -167,24 +190,29 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   if (p->num_seqs == 0) return CUDA_LLM_OK;
   if (!p->query || !p->key_cache || !p->value_cache || !p->block_tables || !p->context_lens || !p->out)
     return fail(CUDA_LLM_EINVAL, "a required tensor pointer is null");
-  if (!p->k_scale || !p->v_scale) return fail(CUDA_LLM_EINVAL, "scale tensors are required for a quantised cache");
-  if (p->k_format != CUDA_LLM_KV_FP8_E4M3)
-    return fail(CUDA_LLM_EINVAL, "K must be FP8-E4M3 (the int8 reading of the reference kernel is not provided)");
-  if (p->v_format != CUDA_LLM_KV_FP8_E4M3 && p->v_format != CUDA_LLM_KV_FP4_E2M1)
-    return fail(CUDA_LLM_EINVAL, "V must be FP8-E4M3 or FP4-E2M1");
-  if (p->v_format == CUDA_LLM_KV_FP4_E2M1 && p->scale_mode != CUDA_LLM_SCALE_MX_E8M0)
-    return fail(CUDA_LLM_EINVAL, "FP4 V needs E8M0 block scales");
-  if (p->scale_mode < 0 || p->scale_mode > CUDA_LLM_SCALE_MX_E8M0) return fail(CUDA_LLM_EINVAL, "unknown scale_mode");
+  const bool kv16 = (p->k_format == CUDA_LLM_KV_F16 || p->k_format == CUDA_LLM_KV_BF16);
+  if (kv16) {
+    if (p->v_format != p->k_format) return fail(CUDA_LLM_EINVAL, "a 16-bit cache needs K and V of the same format");
+  } else {
+    if (!p->k_scale || !p->v_scale) return fail(CUDA_LLM_EINVAL, "scale tensors are required for a quantised cache");
+    if (p->k_format != CUDA_LLM_KV_FP8_E4M3)
+      return fail(CUDA_LLM_EINVAL, "K must be FP8-E4M3, fp16 or bf16 (the int8 reading of the reference kernel is not provided)");
+    if (p->v_format != CUDA_LLM_KV_FP8_E4M3 && p->v_format != CUDA_LLM_KV_FP4_E2M1)
+      return fail(CUDA_LLM_EINVAL, "V must be FP8-E4M3 or FP4-E2M1");
+    if (p->v_format == CUDA_LLM_KV_FP4_E2M1 && p->scale_mode != CUDA_LLM_SCALE_MX_E8M0)
+      return fail(CUDA_LLM_EINVAL, "FP4 V needs E8M0 block scales");
+    if (p->scale_mode < 0 || p->scale_mode > CUDA_LLM_SCALE_MX_E8M0) return fail(CUDA_LLM_EINVAL, "unknown scale_mode");
+  }
   if (p->q_dtype < 0 || p->q_dtype > CUDA_LLM_BF16 || p->out_dtype < 0 || p->out_dtype > CUDA_LLM_BF16)
     return fail(CUDA_LLM_EINVAL, "unknown dtype");
   if (p->max_blocks_per_seq <= 0 || p->num_blocks <= 0) return fail(CUDA_LLM_EINVAL, "max_blocks_per_seq and num_blocks must be positive");
-  const uintptr_t al = (uintptr_t)p->key_cache | (uintptr_t)p->value_cache | (uintptr_t)p->k_scale |
-                       (uintptr_t)p->v_scale | (uintptr_t)p->workspace;
+  const uintptr_t al = (uintptr_t)p->key_cache | (uintptr_t)p->value_cache | (kv16 ? 0 : (uintptr_t)p->k_scale) |
+                       (kv16 ? 0 : (uintptr_t)p->v_scale) | (uintptr_t)p->workspace;
   if (al & 15) return fail(CUDA_LLM_EALIGN, "caches, scales and workspace must be 16-byte aligned");
 
   Layout L;
   int rc = make_layout(p->num_seqs, p->num_q_heads, p->num_kv_heads, p->head_dim, p->page_size,
-                       p->max_q_len, p->v_format, p->scale_mode, p->num_ctas, L);
+                       p->max_q_len, p->k_format, p->v_format, p->scale_mode, p->num_ctas, L);
   if (rc != CUDA_LLM_OK) return rc;
   if (!p->workspace || p->workspace_bytes < L.ws_total)
     return fail(CUDA_LLM_EWORKSPACE, "workspace missing or smaller than cuda_llm_paged_decode_workspace_bytes()");
@@ -221,11 +249,17 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   a.rows_max = L.rows_max;
   a.q_dtype = p->q_dtype;
   a.out_dtype = p->out_dtype;
-  a.per_block = (p->scale_mode == CUDA_LLM_SCALE_PER_BLOCK);
+  a.per_block = !kv16 && (p->scale_mode == CUDA_LLM_SCALE_PER_BLOCK);
+  a.helper_pairs = kv16 ? 0 : 1;
   a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
   a.n_stages = L.n_stages;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_MATH) a.debug |= 1;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_COPY) a.debug |= 2;
+  if (p->flags & CUDA_LLM_FLAG_DIAG_TRACE) {  // per-CTA timestamps go where the lse would go
+    a.debug |= 4;
+    a.trace = reinterpret_cast<unsigned long long*>(p->lse);
+    a.lse = nullptr;
+  }
   {
     const int ns_req = (p->flags >> 8) & 0xF;  // diagnostics: cap the ring depth
     if (ns_req >= 2 && ns_req < a.n_stages) a.n_stages = ns_req;
@@ -242,14 +276,17 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   a.v_chunk = L.v_chunk;
   a.ks_chunk = L.ks_chunk;
   a.vs_chunk = L.vs_chunk;
-  a.k_blk_stride = (uint64_t)Hkv * D * page;
-  a.v_blk_stride = (uint64_t)Hkv * DV * page;
-  if (p->scale_mode == CUDA_LLM_SCALE_PER_TOKEN) a.ks_blk_stride = a.vs_blk_stride = (uint64_t)Hkv * page * 4;
+  a.k_blk_stride = (uint64_t)Hkv * D * page * (kv16 ? 2 : 1);
+  a.v_blk_stride = (uint64_t)Hkv * DV * page * (kv16 ? 2 : 1);
+  if (kv16) a.ks_blk_stride = a.vs_blk_stride = 0;
+  else if (p->scale_mode == CUDA_LLM_SCALE_PER_TOKEN) a.ks_blk_stride = a.vs_blk_stride = (uint64_t)Hkv * page * 4;
   else if (p->scale_mode == CUDA_LLM_SCALE_MX_E8M0) a.ks_blk_stride = a.vs_blk_stride = (uint64_t)Hkv * (D / 32) * page;
 
   const bool precise = (p->q_dtype == CUDA_LLM_F32) && L.NT == 1;
   LaunchFn fn = nullptr;
-  if (p->scale_mode == CUDA_LLM_SCALE_PER_HEAD || p->scale_mode == CUDA_LLM_SCALE_PER_BLOCK)
+  if (kv16)
+    fn = pick_kv16(p->k_format == CUDA_LLM_KV_BF16, D, page, L.NT);
+  else if (p->scale_mode == CUDA_LLM_SCALE_PER_HEAD || p->scale_mode == CUDA_LLM_SCALE_PER_BLOCK)
     fn = pick_d<MODE_PAGE_SCALE>(D, page, L.NT, precise);
   else if (p->scale_mode == CUDA_LLM_SCALE_PER_TOKEN)
     fn = pick_d<MODE_TOKEN_SCALE>(D, page, L.NT, precise);
@@ -341,7 +378,15 @@ static int check_dense(int S, int Hq, int Hkv, int D, int dtype) {
 size_t cuda_llm_dense_decode_workspace_bytes(int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads,
                                              int32_t head_dim, int32_t max_tokens) {
   if (check_dense(num_seqs, num_heads, num_kv_heads, head_dim, CUDA_LLM_F32) != CUDA_LLM_OK || max_tokens < 0) return 0;
-  return dense_decode_workspace_bytes(num_seqs, num_heads, num_kv_heads, head_dim, max_tokens);
+  size_t need = dense_decode_workspace_bytes(num_seqs, num_heads, num_kv_heads, head_dim, max_tokens);
+  // a 16-bit paged cache runs on the persistent kernel: cover its split partials for every page size
+  for (int page = 16; page <= 64; page *= 2) {
+    Layout L;
+    if (make_layout(num_seqs, num_heads, num_kv_heads, head_dim, page, 1, CUDA_LLM_KV_BF16, CUDA_LLM_KV_BF16,
+                    CUDA_LLM_SCALE_PER_HEAD, 0, L) == CUDA_LLM_OK && L.ws_total > need)
+      need = L.ws_total;
+  }
+  return need;
 }
 
 int cuda_llm_paged_attention(const void* query, const void* key_cache, const void* value_cache,
@@ -357,8 +402,23 @@ int cuda_llm_paged_attention(const void* query, const void* key_cache, const voi
   if (rc != CUDA_LLM_OK) return rc;
   if (page_size != 16 && page_size != 32 && page_size != 64) return fail(CUDA_LLM_EINVAL, "Only page_size 16, 32 and 64 supported");
   if (max_blocks_per_seq <= 0 || num_blocks <= 0) return fail(CUDA_LLM_EINVAL, "max_blocks_per_seq and num_blocks must be positive");
-  const size_t need = dense_decode_workspace_bytes(num_seqs, num_heads, num_kv_heads, head_dim, max_blocks_per_seq * page_size);
+  const size_t need = cuda_llm_dense_decode_workspace_bytes(num_seqs, num_heads, num_kv_heads, head_dim, max_blocks_per_seq * page_size);
   if (!workspace || workspace_bytes < need) return fail(CUDA_LLM_EWORKSPACE, "workspace missing or smaller than cuda_llm_dense_decode_workspace_bytes()");
+  if (dtype != CUDA_LLM_F32 && !(((uintptr_t)key_cache | (uintptr_t)value_cache | (uintptr_t)workspace) & 15)) {
+    // 16-bit cache: the persistent tensor-core kernel (an fp32 cache stays on the SIMT kernel)
+    CudaLlmPagedDecodeParams p;
+    memset(&p, 0, sizeof(p));
+    p.query = query; p.key_cache = key_cache; p.value_cache = value_cache;
+    p.block_tables = block_tables; p.context_lens = context_lens; p.out = out;
+    p.workspace = workspace; p.workspace_bytes = workspace_bytes;
+    p.num_seqs = num_seqs; p.num_q_heads = num_heads; p.num_kv_heads = num_kv_heads;
+    p.head_dim = head_dim; p.page_size = page_size; p.max_blocks_per_seq = max_blocks_per_seq;
+    p.num_blocks = num_blocks; p.max_q_len = 1;
+    p.q_dtype = p.out_dtype = dtype;
+    p.k_format = p.v_format = (dtype == CUDA_LLM_F16) ? CUDA_LLM_KV_F16 : CUDA_LLM_KV_BF16;
+    p.softmax_scale = softmax_scale;
+    return cuda_llm_paged_decode(&p, stream);
+  }
   cudaError_t e = run_dense_decode(true, query, key_cache, value_cache, block_tables, context_lens, out, num_seqs,
                                    num_heads, num_kv_heads, head_dim, page_size, max_blocks_per_seq, num_blocks, 0,
                                    softmax_scale, dtype, workspace, reinterpret_cast<cudaStream_t>(stream));

@@ -46,7 +46,10 @@ constexpr uint32_t kSmemBudget = 232448;  // 227 KB opt-in maximum per CTA
 constexpr int kBtAhead = 8;               // block-table prefetch distance, in stages
 constexpr int kBtRing = 16;               // ring slots for prefetched block-table entries
 
-enum : int { MODE_PAGE_SCALE = 0, MODE_TOKEN_SCALE = 1, MODE_MX8 = 2, MODE_MX8K_MX4V = 3 };
+enum : int {
+  MODE_PAGE_SCALE = 0, MODE_TOKEN_SCALE = 1, MODE_MX8 = 2, MODE_MX8K_MX4V = 3,
+  MODE_KV_F16 = 4, MODE_KV_BF16 = 5  // unquantised 16-bit cache (no scales)
+};
 
 enum : int { FLAG_NEW = 1, FLAG_LAST = 2, FLAG_DIRECT = 4 };
 
@@ -78,7 +81,11 @@ struct DecodeArgs {
   int S, Hq, Hkv, group, max_blocks, num_blocks;
   int HG, SUBS, n_hg, rows_max, tok_stage;
   int q_dtype, out_dtype, per_block;
-  int debug;  // diagnostics: bit 0 = consumers skip the math, bit 1 = producer skips the copies
+  int helper_pairs;  // 16-row kernels of the 8-bit modes pair two warps on a short query (two results per sub-tile)
+  int debug;  // diagnostics: bit 0 = consumers skip the math, bit 1 = producer skips the copies,
+              // bit 2 = per-CTA timestamps into `trace`
+  unsigned long long* trace;  // [grid][8] ns: kernel entry, first stage landed, last stage consumed, exit,
+                              // plan done, table prefetches issued, first table entry landed, first copy issued
   float scale_log2;
   int n_stages;
   uint32_t stage_bytes, off_v, off_ks, off_vs;
@@ -161,7 +168,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   constexpr bool MX = (MODE == MODE_MX8 || MODE == MODE_MX8K_MX4V);
   constexpr int DV = V4 ? D / 2 : D;             // byte rows per head in the V slab
   constexpr int NB = D / 32;                     // scale blocks along head_dim
-  constexpr int SUB = (NT == 1) ? 16 : 32;       // tokens per warp sub-tile
+  constexpr bool KV16 = (MODE == MODE_KV_F16 || MODE == MODE_KV_BF16);  // 2-byte elements, no scales
+  constexpr int SUB = (KV16 || NT == 1) ? 16 : 32;  // tokens per warp sub-tile
   constexpr int MT = SUB / 16;                   // m-tiles of S^T == k-tiles of PV per sub-tile
   constexpr float NEG_INF = -__builtin_huge_valf();
 
@@ -186,6 +194,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   // the split merge, may be scheduled from here on.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;");
+  const bool tracing = (a.debug & 4) && a.trace != nullptr;
+  if (tracing && threadIdx.x == 0) a.trace[blockIdx.x * 8 + 0] = globaltimer_ns();
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
       mbar_init(full_bar + 8 * i, 1);
@@ -221,7 +231,11 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     total_units += v;
   }
   const long long my_prefix = warp_base + incl - my_units;
-  const long long per_cta = (total_units + gridDim.x - 1) / gridDim.x;
+  // unit counts fit 32 bits in practice (a unit moves at least 2 KB); 64-bit division is kept as
+  // the fallback only
+  const bool small_units = total_units < (1ll << 31) - (long long)gridDim.x;
+  const long long per_cta = small_units ? (long long)(((unsigned)total_units + gridDim.x - 1) / gridDim.x)
+                                        : (total_units + gridDim.x - 1) / gridDim.x;
   const long long u_begin = min(total_units, (long long)blockIdx.x * per_cta);
   const long long u_end = min(total_units, u_begin + per_cta);
   if (u_begin < u_end && my_units > 0 && u_begin >= my_prefix && u_begin < my_prefix + my_units) {
@@ -240,6 +254,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     }
   }
   __syncthreads();
+  if (tracing && tid == 0) a.trace[blockIdx.x * 8 + 4] = globaltimer_ns();
   if (u_begin >= u_end) return;
   const int n_units = (int)(u_end - u_begin);
 
@@ -250,7 +265,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     // small shared-memory ring with 4-byte cp.async.  The block-table read is the one dependent
     // global load on the copy path; fetching it several stages early keeps it off the critical
     // path of every stage.
-    constexpr int NTYPES = (MODE == MODE_PAGE_SCALE) ? 2 : 4;
+    constexpr int NTYPES = (MODE == MODE_PAGE_SCALE || KV16) ? 2 : 4;
     const int PPS = (TOK_STAGE >= PAGE) ? TOK_STAGE / PAGE : 1;  // pages per stage
     auto load_seq = [&](UnitCursor& c) {
       c.ctx = eff_ctx(a, c.s, PAGE);
@@ -302,6 +317,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       cp_async_commit();
     };
     for (int j = 0; j < kBtAhead; ++j) prefetch();
+    if (tracing && lane == 0) a.trace[blockIdx.x * 8 + 5] = globaltimer_ns();
 
     // per-segment constants of the issue cursor
     int seg_cta_first = 0, seg_n_cta = 1;
@@ -314,12 +330,18 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       prefetch();
       cp_async_wait<kBtAhead>();  // the group of unit `it` has landed
       __syncwarp();
+      if (tracing && it == 0 && lane == 0) a.trace[blockIdx.x * 8 + 6] = globaltimer_ns();
       if (seg_fresh || ic.tile == 0) {
-        seg_cta_first = (int)(ic.seg_first / per_cta);
-        seg_n_cta = (int)((ic.seg_first + ic.tiles - 1) / per_cta) - seg_cta_first + 1;
+        if (small_units) {
+          seg_cta_first = (int)((unsigned)ic.seg_first / (unsigned)per_cta);
+          seg_n_cta = (int)((unsigned)(ic.seg_first + ic.tiles - 1) / (unsigned)per_cta) - seg_cta_first + 1;
+        } else {
+          seg_cta_first = (int)(ic.seg_first / per_cta);
+          seg_n_cta = (int)((ic.seg_first + ic.tiles - 1) / per_cta) - seg_cta_first + 1;
+        }
         // direct output needs one warp per (head, row): not when two warps share the rows of a
         // short query (NT == 2 kernel, at most 8 live rows)
-        seg_direct = (a.SUBS == 1) && (seg_n_cta == 1) && !(NT == 2 && a.group * ic.qlen <= 8);
+        seg_direct = (a.SUBS == 1) && (seg_n_cta == 1) && !(!KV16 && NT == 2 && a.group * ic.qlen <= 8);
       }
       const int tok0 = ic.tile * TOK_STAGE;
       const int np = min(PPS, (ic.ctx - tok0 + PAGE - 1) / PAGE);
@@ -378,6 +400,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           }
         }
       }
+      if (tracing && it == 0 && lane == 0) a.trace[blockIdx.x * 8 + 7] = globaltimer_ns();
       issued = it + 1;
       if (it + 1 < n_units) advance(ic);
     }
@@ -393,10 +416,15 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
 
   // ================================================================= consumer warps
   const int g = lane >> 2, t = lane & 3;
-  const int wl = (NT == 1) ? warp : (warp & 7);  // index among the warps that share one row half
-  const int nt_w = (NT == 1) ? 0 : (warp >> 3);  // which 8 query rows this warp owns
+  // 16-bit cache: a stage holds 128 (token, head) pairs, half of the 8-bit stage.  With up to 8
+  // query rows the two groups of 8 warps take alternate stages (`par`); with 9..16 rows every
+  // stage is computed by both groups, one row half each.
+  const int wl = (NT == 1 && !KV16) ? warp : (warp & 7);  // index among the warps that share a stage's rows
+  const int nt_w = (NT == 1) ? 0 : (warp >> 3);           // which 8 query rows this warp owns
+  const int par = (KV16 && NT == 1) ? (warp >> 3) : -1;   // stage parity this warp computes (-1: all)
   const int h = wl % a.HG;                       // head within the CTA's head group
   const int ts = wl / a.HG;                      // sub-tile within the stage
+  const int psub = (NT == 1) ? warp / a.HG : ts;  // index of this warp's result among those of a (CTA, head)
   // Every m-tile is 16 consecutive tokens of one page: token 16*mt + 2g (+1) sits on S^T rows
   // g (g+8) of m-tile mt.  Shared-memory offsets of this thread, per m-tile:
   uint32_t k_lm[MT];   // K ldmatrix row address: lane l <-> row (32*ks + l) of the head slab
@@ -413,6 +441,16 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     vs_t[mt] = a.off_vs + pi * a.vs_page_stride + (h * PAGE + po + 2 * g) * 4;
     ks_mx[mt] = a.off_ks + pi * a.ks_page_stride + h * (NB * PAGE) + po + 2 * g;
     vs_mx[mt] = a.off_vs + pi * a.vs_page_stride + h * (NB * PAGE) + po + 4 * t;
+    if (KV16) {
+      // row = head_dim index, 2*PAGE bytes; a 16-token m-tile is 32 bytes of a row.  Four 8x8
+      // matrices per ldmatrix.x4 -- K (transposed on load): lanes 8..15 the upper 8 tokens, lanes
+      // 16..31 the upper 8 head_dim rows; V: lanes 8..15 the upper 8 rows, lanes 16..31 the upper
+      // 8 tokens -- so the four registers are the A fragment of mma.m16n8k16 in order.
+      k_lm[mt] = pi * a.k_page_stride + h * (D * PAGE * 2) + (((lane >> 4) * 8 + (lane & 7)) * PAGE + po) * 2 +
+                 ((lane >> 3) & 1) * 16;
+      v_lm[mt] = a.off_v + pi * a.v_page_stride + h * (D * PAGE * 2) +
+                 ((((lane >> 3) & 1) * 8 + (lane & 7)) * PAGE + po) * 2 + (lane >> 4) * 16;
+    }
   }
 
   constexpr int KS = D / 32;   // ldmatrix.x4 steps over head_dim (32 rows each)
@@ -435,6 +473,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       if (lane == 0) atomicOr(a.status, CUDA_LLM_ST_TIMEOUT);
       return;
     }
+    if (tracing && it == 0 && warp == 0 && lane == 0) a.trace[blockIdx.x * 8 + 1] = globaltimer_ns();
     const uint32_t meta = smem_base + kMetaOff + slot * (uint32_t)sizeof(StageMeta);
     const uint4 m0 = lds128(meta);
     const uint4 m1 = lds128(meta + 16);
@@ -447,7 +486,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       qlen = (int)m1.w;
       kvh = hg * a.HG + h;
       R = a.group * qlen;  // live query rows of this KV head
-      helper = (NT == 2) && (R <= 8);
+      helper = !KV16 && (NT == 2) && (R <= 8);
       rb = helper ? 0 : nt_w * 8;
       mt_lo = helper ? nt_w : 0;
       mt_hi = helper ? nt_w + 1 : MT;
@@ -478,7 +517,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
               lo = __low2float(v); hi = __high2float(v);
             }
           }
-          const uint32_t pk = pack_f16x2(lo, hi);
+          const uint32_t pk = (MODE == MODE_KV_BF16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
           qf[kt][hf] = pk;
           if (PRECISE) ql[PRECISE ? kt : 0][hf] = pack_f16x2(lo - f16x2_lo(pk), hi - f16x2_hi(pk));
         }
@@ -495,7 +534,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     }
 
     const int nv = min(SUB, ctx - tok0 - ts * SUB);  // valid tokens of this warp's sub-tile
-    if (nv > 0 && live && !(a.debug & 1)) {
+    if (nv > 0 && live && !(a.debug & 1) && (par < 0 || (it & 1) == par)) {
       const bool tail = nv < SUB || helper;  // masking path (dead tokens, or an m-tile left to the partner)
       // causal limit: query row r = j*group + i sees positions < ctx - qlen + 1 + j
       const int pos0 = tok0 + ts * SUB;  // absolute position of sub-tile token 0
@@ -511,8 +550,18 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) sacc[mt][c] = 0.f;
+      if (KV16) {
+        // 16-bit K: token g (g+8) of the sub-tile on S^T rows g (g+8)
 #pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
+        for (int kt = 0; kt < KT; ++kt) {
+          uint32_t r4[4];
+          ldmatrix_x4_trans(r4, sb + k_lm[0] + kt * 16 * PAGE * 2);
+          if (MODE == MODE_KV_BF16) mma_bf16(sacc[0], r4[0], r4[1], r4[2], r4[3], qf[kt][0], qf[kt][1]);
+          else mma_f16(sacc[0], r4[0], r4[1], r4[2], r4[3], qf[kt][0], qf[kt][1]);
+        }
+      }
+#pragma unroll
+      for (int ks = 0; ks < (KV16 ? 0 : KS); ++ks) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           if (NT == 2 && (mt < mt_lo || mt >= mt_hi)) continue;
@@ -586,7 +635,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           const int j = c >> 1;  // token 16*mt + 2g + j
           float xx = fmaf(sacc[mt][c], ksc[mt][j] * a.scale_log2, vlg[mt][j]);
           if (tail || need_causal) {
-            const int tok = 16 * mt + 2 * g + j;
+            const int tok = KV16 ? g + 8 * j : 16 * mt + 2 * g + j;
             bool vis = tok < nv && mt >= mt_lo && mt < mt_hi;
             if (need_causal) {
               const int r = rb + 2 * t + (c & 1);
@@ -644,7 +693,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          const uint32_t pk = pack_f16x2(pv[mt][2 * hf], pv[mt][2 * hf + 1]);
+          const uint32_t pk = (MODE == MODE_KV_BF16) ? pack_bf16x2(pv[mt][2 * hf], pv[mt][2 * hf + 1])
+                                                     : pack_f16x2(pv[mt][2 * hf], pv[mt][2 * hf + 1]);
           pb[mt][hf] = movmatrix_trans(pk);
           if (PRECISE)
             pbl[PRECISE ? mt : 0][hf] = movmatrix_trans(
@@ -656,9 +706,25 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         const int kc = max(0, min(4, nv - 16 * mt - 4 * t));
         vmask[mt] = kc >= 4 ? 0xffffffffu : ((1u << (8 * kc)) - 1u);
       }
+      if (KV16) {
+        // 16-bit V: registers 0,1 hold tokens 2t, 2t+1 (rows g, g+8), registers 2,3 tokens 2t+8, 2t+9;
+        // P^T after the transpose: b0 = tokens 2t, 2t+1, b1 = tokens 2t+8, 2t+9
+        const uint32_t m_lo = (2 * t < nv ? 0xffffu : 0u) | (2 * t + 1 < nv ? 0xffff0000u : 0u);
+        const uint32_t m_hi = (2 * t + 8 < nv ? 0xffffu : 0u) | (2 * t + 9 < nv ? 0xffff0000u : 0u);
+#pragma unroll
+        for (int mo = 0; mo < KT; ++mo) {
+          uint32_t va[4];
+          ldmatrix_x4(va, sb + v_lm[0] + mo * 16 * PAGE * 2);
+          if (tail) {  // a dead slot may hold a NaN pattern: 0 * NaN must not reach the accumulator
+            va[0] &= m_lo; va[1] &= m_lo; va[2] &= m_hi; va[3] &= m_hi;
+          }
+          if (MODE == MODE_KV_BF16) mma_bf16(oacc[mo], va[0], va[1], va[2], va[3], pb[0][0], pb[0][1]);
+          else mma_f16(oacc[mo], va[0], va[1], va[2], va[3], pb[0][0], pb[0][1]);
+        }
+      }
       constexpr int ROWS_PER_LDSM = V4 ? 64 : 32;  // head_dim rows one ldmatrix.x4 covers
 #pragma unroll
-      for (int dp = 0; dp < D / ROWS_PER_LDSM; ++dp) {
+      for (int dp = 0; dp < (KV16 ? 0 : D / ROWS_PER_LDSM); ++dp) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           if (NT == 2 && (mt < mt_lo || mt >= mt_hi)) continue;
@@ -715,6 +781,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     // stage consumed: hand the slot back before the epilogue
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
+    if (tracing && it == n_units - 1 && warp == 0 && lane == 0) a.trace[blockIdx.x * 8 + 2] = globaltimer_ns();
 
     if (flags & FLAG_LAST) {
       // ------------------------------------------------------------ epilogue of the segment
@@ -751,7 +818,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           if (a.lse && g == 0) a.lse[row] = lse2 * 0.69314718055994531f;
         } else {
           // a helper pair stores its second result in the unused upper rows
-          const size_t prow = (((size_t)mslot * a.SUBS + ts) * a.HG + h) * a.rows_max + r + (helper ? nt_w * 8 : 0);
+          const size_t prow = (((size_t)mslot * a.SUBS + psub) * a.HG + h) * a.rows_max + r + (helper ? nt_w * 8 : 0);
           float* po = a.part_o + prow * D;
 #pragma unroll
           for (int mt = 0; mt < KT; ++mt) {
@@ -765,6 +832,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       }
     }
   }
+  if (tracing && warp == 0 && lane == 0) a.trace[blockIdx.x * 8 + 3] = globaltimer_ns();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -806,7 +874,7 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
   const int cta_first = tb[0], n_cta = tb[1], direct = tb[2];
   if (direct) return;
   // a 16-row kernel leaves two results per sub-tile for a query of at most 8 rows (rows r, r + 8)
-  const int dup = (a.rows_max == 16 && a.group * qlen <= 8) ? 2 : 1;
+  const int dup = (a.helper_pairs && a.rows_max == 16 && a.group * qlen <= 8) ? 2 : 1;
   const int n_parts = n_cta * a.SUBS * dup;
   const size_t pstride = (size_t)a.HG * a.rows_max;  // rows between consecutive sub-tile results
   auto part_row = [&](size_t row0, int p) -> size_t { return row0 + (size_t)(p / dup) * pstride + (size_t)(p % dup) * 8; };

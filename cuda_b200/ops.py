@@ -156,10 +156,14 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
     return (out, lse) if return_lse else out
 
 
-def paged_attention_forward(query, key_cache, value_cache, block_tables, context_lens, softmax_scale=None):
+def paged_attention_forward(query, key_cache, value_cache, block_tables, context_lens, softmax_scale=None, *,
+                            cu_q_lens: Optional[torch.Tensor] = None, max_q_len: int = 1,
+                            return_lse: bool = False, num_ctas: int = 0, check_status: bool = False,
+                            flags: int = 0):
     """Decode attention over a paged fp32 / fp16 / bf16 cache: signature of the reference binding
     ``paged_attention_forward`` (``fused_softmax_binding.cpp:109-173`` in the reference project).
-    ``key_cache.shape[1]`` may be smaller than ``query.shape[1]`` (GQA)."""
+    ``key_cache.shape[1]`` may be smaller than ``query.shape[1]`` (GQA).  The keyword-only extensions
+    (several query rows per sequence, log-sum-exp output) exist for a 16-bit cache only."""
     if not (query.is_cuda and key_cache.is_cuda and value_cache.is_cuda):
         raise RuntimeError("Inputs must be on CUDA")
     if not (block_tables.is_cuda and context_lens.is_cuda):
@@ -184,6 +188,36 @@ def paged_attention_forward(query, key_cache, value_cache, block_tables, context
             raise RuntimeError(f"{name} must be contiguous")
     scale = 1.0 / math.sqrt(d) if softmax_scale is None else float(softmax_scale)
     lib = L.load()
+    extended = cu_q_lens is not None or return_lse or num_ctas or check_status or flags
+    if extended:
+        if query.dtype == torch.float32:
+            raise RuntimeError("cu_q_lens / return_lse need a float16 or bfloat16 cache")
+        if page not in (16, 32, 64):
+            raise RuntimeError("Only page_size 16, 32 and 64 are supported")
+        num_seqs = context_lens.shape[0]
+        fmt = L.KV_F16 if query.dtype == torch.float16 else L.KV_BF16
+        with torch.cuda.device(query.device):
+            out = torch.empty_like(query)
+            lse = torch.empty(n, hq, dtype=torch.float32, device=query.device) if return_lse else None
+            need = lib.cuda_llm_paged_decode_workspace_bytes(num_seqs, hq, hkv, d, page, max_q_len, num_ctas)
+            if need == 0:
+                raise L.CudaLlmError(L.EINVAL, "cuda_llm_paged_decode_workspace_bytes")
+            ws = get_workspace(query.device, need)
+            p = L.PagedDecodeParams(
+                query=query.data_ptr(), key_cache=key_cache.data_ptr(), value_cache=value_cache.data_ptr(),
+                k_scale=None, v_scale=None, block_tables=block_tables.data_ptr(),
+                context_lens=context_lens.data_ptr(), cu_q_lens=_ptr(cu_q_lens), out=out.data_ptr(),
+                lse=_ptr(lse), workspace=ws.data_ptr(), workspace_bytes=ws.numel(),
+                num_seqs=num_seqs, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page,
+                max_blocks_per_seq=block_tables.shape[1], num_blocks=nb, max_q_len=max_q_len,
+                q_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[out.dtype], k_format=fmt, v_format=fmt,
+                scale_mode=0, softmax_scale=scale, num_ctas=num_ctas, flags=flags)
+            L.check(lib.cuda_llm_paged_decode(C.byref(p), _stream_ptr(query.device)), "cuda_llm_paged_decode")
+            if check_status:
+                st = decode_status(ws, query.device)
+                if st:
+                    raise RuntimeError(f"paged decode reported device status 0x{st:x}")
+        return (out, lse) if return_lse else out
     with torch.cuda.device(query.device):
         out = torch.empty_like(query)
         need = lib.cuda_llm_dense_decode_workspace_bytes(n, hq, hkv, d, block_tables.shape[1] * page)

@@ -45,6 +45,10 @@ extern "C" {
                                         (output is meaningless; measures the copy pipeline)   */
 #define CUDA_LLM_FLAG_DIAG_NO_COPY 4 /* diagnostics: do the attention math on stale shared memory,
                                         no page copies (output is meaningless)                */
+#define CUDA_LLM_FLAG_DIAG_TRACE 8   /* diagnostics: `lse` receives, per CTA, eight 64-bit nanosecond
+                                        timestamps (entry, first stage landed, last stage consumed,
+                                        exit, four prologue marks) instead of log-sum-exps; needs
+                                        grid*64 bytes         */
 /* bits 8..11: diagnostics: cap the shared-memory ring at this many stages (0 = as many as fit) */
 
 /* ---- enums ---------------------------------------------------------------------------- */
@@ -53,7 +57,9 @@ enum CudaLlmDType { CUDA_LLM_F32 = 0, CUDA_LLM_F16 = 1, CUDA_LLM_BF16 = 2 };
 enum CudaLlmKvFormat {
   CUDA_LLM_KV_FP8_E4M3 = 0, /* uint8 [num_blocks, Hkv, D,   page]                            */
   CUDA_LLM_KV_FP4_E2M1 = 1, /* uint8 [num_blocks, Hkv, D/2, page], low nibble = even d (V only) */
-  CUDA_LLM_KV_INT8 = 2      /* reference's integer reading of the byte (fp8_paged_attention_kernel.cuh:102) */
+  CUDA_LLM_KV_INT8 = 2,     /* reference's integer reading of the byte (fp8_paged_attention_kernel.cuh:102) */
+  CUDA_LLM_KV_F16 = 3,      /* fp16 [num_blocks, Hkv, D, page], no scales (K and V alike)    */
+  CUDA_LLM_KV_BF16 = 4      /* bf16 [num_blocks, Hkv, D, page], no scales (K and V alike)    */
 };
 
 enum CudaLlmScaleMode {
