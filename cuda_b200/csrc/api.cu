@@ -299,7 +299,7 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   cudaError_t e = fn(a, L.grid, L.smem_bytes, st);
   if (e != cudaSuccess) return fail_cuda(e, "paged_decode_kernel launch");
   if (p->flags & CUDA_LLM_FLAG_SKIP_MERGE) return CUDA_LLM_OK;
-  e = (D == 64) ? launch_merge_splits<64>(a, page, st) : launch_merge_splits<128>(a, page, st);
+  e = (D == 64) ? launch_merge_splits<64>(a, page, L.grid, st) : launch_merge_splits<128>(a, page, L.grid, st);
   if (e != cudaSuccess) return fail_cuda(e, "merge_splits_kernel launch");
   return CUDA_LLM_OK;
 }

@@ -10,7 +10,7 @@ template <int D, int PAGE, int MODE, int NT, bool PRECISE>
 cudaError_t launch_paged_decode(const DecodeArgs& a, int grid, size_t smem, cudaStream_t st);
 
 template <int D>
-cudaError_t launch_merge_splits(const DecodeArgs& a, int page, cudaStream_t st);
+cudaError_t launch_merge_splits(const DecodeArgs& a, int page, int decode_grid, cudaStream_t st);
 
 #define B200_DEFINE_DECODE_LAUNCH(D, PAGE, MODE, NT, PRECISE)                                   \
   template <>                                                                                   \

@@ -5,12 +5,14 @@
 namespace b200 {
 
 template <int D>
-cudaError_t launch_merge_splits(const DecodeArgs& a, int page, cudaStream_t st) {
+cudaError_t launch_merge_splits(const DecodeArgs& a, int page, int decode_grid, cudaStream_t st) {
   const long long blocks = (long long)a.S * a.Hq;
   if (blocks == 0) return cudaSuccess;
+  // few sequences cut across many CTAs leave many results per row: more warps per block then
+  const bool many_parts = (long long)decode_grid >= 4LL * a.S * a.n_hg;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
-  cfg.blockDim = dim3(128);
+  cfg.blockDim = dim3(many_parts ? 512 : 128);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -18,10 +20,11 @@ cudaError_t launch_merge_splits(const DecodeArgs& a, int page, cudaStream_t st) 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, merge_splits_kernel<D>, a, page);
+  if (many_parts) return cudaLaunchKernelEx(&cfg, merge_splits_kernel<D, 16>, a, page);
+  return cudaLaunchKernelEx(&cfg, merge_splits_kernel<D, 4>, a, page);
 }
-template cudaError_t launch_merge_splits<64>(const DecodeArgs&, int, cudaStream_t);
-template cudaError_t launch_merge_splits<128>(const DecodeArgs&, int, cudaStream_t);
+template cudaError_t launch_merge_splits<64>(const DecodeArgs&, int, int, cudaStream_t);
+template cudaError_t launch_merge_splits<128>(const DecodeArgs&, int, int, cudaStream_t);
 
 // parts_out [P, rows, D] fp32, parts_lse [P, rows] natural log.  One warp per row.
 template <int D>

@@ -316,7 +316,26 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       }
       cp_async_commit();
     };
-    for (int j = 0; j < kBtAhead; ++j) prefetch();
+    if (n_units >= kBtAhead && pc.tile + kBtAhead <= pc.tiles) {
+      // common start: the first kBtAhead units are consecutive tiles of one (sequence, head group),
+      // so their table entries are fetched by the lanes in parallel instead of unit by unit
+      for (int idx = lane; idx < kBtAhead * PPS; idx += 32) {
+        const int j = idx / PPS, pg = idx - j * PPS;
+        const int tok0 = (pc.tile + j) * TOK_STAGE;
+        const int np = min(PPS, (pc.ctx - tok0 + PAGE - 1) / PAGE);
+        if (pg < np) {
+          const int32_t* src = a.bt + (size_t)pc.s * a.max_blocks + min(tok0 / PAGE + pg, a.max_blocks - 1);
+          cp_async_4(ring + ((j % kBtRing) * kMaxPagesPerStage + pg) * 4, src);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kBtAhead; ++j) cp_async_commit();
+      pf_done = kBtAhead;
+      pc.tile += kBtAhead - 1;
+      if (pf_done < n_units) advance(pc);
+    } else {
+      for (int j = 0; j < kBtAhead; ++j) prefetch();
+    }
     if (tracing && lane == 0) a.trace[blockIdx.x * 8 + 5] = globaltimer_ns();
 
     // per-segment constants of the issue cursor
@@ -327,8 +346,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     for (int it = 0; it < n_units; ++it) {
       const int slot = it % NS;
       const uint32_t phase = (it / NS) & 1;
-      prefetch();
-      cp_async_wait<kBtAhead>();  // the group of unit `it` has landed
+      cp_async_wait<kBtAhead - 1>();  // the group of unit `it` has landed
       __syncwarp();
       if (tracing && it == 0 && lane == 0) a.trace[blockIdx.x * 8 + 6] = globaltimer_ns();
       if (seg_fresh || ic.tile == 0) {
@@ -402,6 +420,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       }
       if (tracing && it == 0 && lane == 0) a.trace[blockIdx.x * 8 + 7] = globaltimer_ns();
       issued = it + 1;
+      prefetch();  // table entries of unit it + kBtAhead
       if (it + 1 < n_units) advance(ic);
     }
     cp_async_wait<0>();
@@ -462,9 +481,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   int kvh = 0, R = 0, qbase = 0, qlen = 0;
   bool live = false;  // this warp has query rows in the current segment
   // NT == 2 kernels: a segment with at most 8 live rows does not need two row halves; the two
-  // warps of a pair then take one 16-token m-tile each (all rows) instead of idling one of them
+  // warps of a pair then take alternate stages (all rows) instead of idling one of them
   bool helper = false;
-  int rb = 0, mt_lo = 0, mt_hi = MT;  // first query row of this warp; m-tiles it computes
+  int rb = 0;  // first query row of this warp
 
   for (int it = 0; it < n_units; ++it) {
     const int slot = it % NS;
@@ -488,8 +507,6 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       R = a.group * qlen;  // live query rows of this KV head
       helper = !KV16 && (NT == 2) && (R <= 8);
       rb = helper ? 0 : nt_w * 8;
-      mt_lo = helper ? nt_w : 0;
-      mt_hi = helper ? nt_w + 1 : MT;
       live = rb < R;
       // ---- Q fragments: B operand of S^T = K * Q^T, f16 pairs (d, d+1) with
       // b0: d = 16kt + 2t, b1: d = 16kt + 8 + 2t.  An fp32 Q keeps a second f16 word (PRECISE).
@@ -534,8 +551,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     }
 
     const int nv = min(SUB, ctx - tok0 - ts * SUB);  // valid tokens of this warp's sub-tile
-    if (nv > 0 && live && !(a.debug & 1) && (par < 0 || (it & 1) == par)) {
-      const bool tail = nv < SUB || helper;  // masking path (dead tokens, or an m-tile left to the partner)
+    if (nv > 0 && live && !(a.debug & 1) && (par < 0 || (it & 1) == par) && (!helper || (it & 1) == nt_w)) {
+      const bool tail = nv < SUB;  // masking path (dead tokens)
       // causal limit: query row r = j*group + i sees positions < ctx - qlen + 1 + j
       const int pos0 = tok0 + ts * SUB;  // absolute position of sub-tile token 0
       const bool need_causal = (qlen > 1) && (pos0 + SUB > ctx - qlen + 1);
@@ -564,7 +581,6 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int ks = 0; ks < (KV16 ? 0 : KS); ++ks) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-          if (NT == 2 && (mt < mt_lo || mt >= mt_hi)) continue;
           uint32_t r4[4];
           ldmatrix_x4_trans(r4, sb + k_lm[mt] + ks * 32 * PAGE);
           float tacc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -636,7 +652,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           float xx = fmaf(sacc[mt][c], ksc[mt][j] * a.scale_log2, vlg[mt][j]);
           if (tail || need_causal) {
             const int tok = KV16 ? g + 8 * j : 16 * mt + 2 * g + j;
-            bool vis = tok < nv && mt >= mt_lo && mt < mt_hi;
+            bool vis = tok < nv;
             if (need_causal) {
               const int r = rb + 2 * t + (c & 1);
               const int jq = r / a.group;
@@ -727,7 +743,6 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int dp = 0; dp < (KV16 ? 0 : D / ROWS_PER_LDSM); ++dp) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-          if (NT == 2 && (mt < mt_lo || mt >= mt_hi)) continue;
           uint32_t va[4];
           ldmatrix_x4(va, sb + v_lm[mt] + dp * 32 * PAGE);
           if (tail) {  // codes of dead slots may be NaN: 0 * NaN must not reach the accumulator
@@ -836,20 +851,20 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------
-// Split merge: one 4-warp block per (sequence, query head); the warps share the partials of every
+// Split merge: one block of W warps per (sequence, query head); the warps share the partials of every
 // CTA and sub-tile warp that touched the sequence and combine them (algebra of
 // combine_softmax_state, fused_online_softmax_kernel.cuh:40-49 in the reference project, in
 // base 2).  Launched as a programmatic dependent of the decode kernel: blocks may start early
 // and wait at griddepcontrol.wait until the decode kernel's results are visible.
 // ------------------------------------------------------------------------------------------
-template <int D>
-__global__ void __launch_bounds__(128)
+template <int D, int W>
+__global__ void __launch_bounds__(32 * W)
 merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
   constexpr float NEG_INF = -__builtin_huge_valf();
   constexpr int VPL = D / 32;  // values per lane
-  __shared__ float s_max[4];
-  __shared__ float s_sum[4];
-  __shared__ float s_acc[4][D];
+  __shared__ float s_max[W];
+  __shared__ float s_sum[W];
+  __shared__ float s_acc[W][D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int s = blockIdx.x / a.Hq, qh = blockIdx.x - s * a.Hq;
   int qbase, qlen;
@@ -862,7 +877,7 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (qlen <= 0) return;
   if (ctx <= 0) {
-    for (int j = warp; j < qlen; j += 4) {
+    for (int j = warp; j < qlen; j += W) {
       const size_t row = (size_t)(qbase + j) * a.Hq + qh;
 #pragma unroll
       for (int v = 0; v < VPL; ++v) store_out_elem(a.out, a.out_dtype, row * D + lane * VPL + v, 0.f);
@@ -883,28 +898,30 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
     const size_t row = (size_t)(qbase + j) * a.Hq + qh;
     const size_t row0 = (((size_t)(sh + cta_first) * a.SUBS) * a.HG + h) * a.rows_max + r;
     float mx = NEG_INF;
-    for (int p = threadIdx.x; p < n_parts; p += 128) mx = fmaxf(mx, a.part_lse[part_row(row0, p)]);
+    for (int p = threadIdx.x; p < n_parts; p += 32 * W) mx = fmaxf(mx, a.part_lse[part_row(row0, p)]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) s_max[warp] = mx;
     __syncthreads();
-    mx = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
+    mx = s_max[0];
+#pragma unroll
+    for (int w = 1; w < W; ++w) mx = fmaxf(mx, s_max[w]);
     const float mu = (mx == NEG_INF) ? 0.f : mx;
     float acc[VPL];
 #pragma unroll
     for (int v = 0; v < VPL; ++v) acc[v] = 0.f;
     float wsum = 0.f;
-    // warp w takes parts w, w+4, ...: weights 32 of its parts at a time (one per lane), then every
+    // warp w takes parts w, w+W, ...: weights 32 of its parts at a time (one per lane), then every
     // lane walks the rows of those parts with independent loads
-    for (int base = 0; base < n_parts; base += 128) {
-      const int mine = base + 4 * lane + warp;
+    for (int base = 0; base < n_parts; base += 32 * W) {
+      const int mine = base + W * lane + warp;
       const float wl = mine < n_parts ? fast_exp2(a.part_lse[part_row(row0, mine)] - mu) : 0.f;
-      const int cnt = min(32, (n_parts - base - warp + 3) / 4);
+      const int cnt = min(32, (n_parts - base - warp + W - 1) / W);
 #pragma unroll 4
       for (int jj = 0; jj < cnt; ++jj) {
         const float w = __shfl_sync(0xffffffffu, wl, jj);
         wsum += w;
-        const float* po = a.part_o + part_row(row0, base + 4 * jj + warp) * D + lane * VPL;
+        const float* po = a.part_o + part_row(row0, base + W * jj + warp) * D + lane * VPL;
 #pragma unroll
         for (int v = 0; v < VPL; ++v) acc[v] = fmaf(w, po[v], acc[v]);
       }
@@ -914,13 +931,17 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
     if (lane == 0) s_sum[warp] = wsum;
     __syncthreads();
     if (warp == 0) {
-      wsum = s_sum[0] + s_sum[1] + s_sum[2] + s_sum[3];
+      wsum = 0.f;
+#pragma unroll
+      for (int w = 0; w < W; ++w) wsum += s_sum[w];
       const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
         const int d = lane * VPL + v;
-        store_out_elem(a.out, a.out_dtype, row * D + d,
-                       (s_acc[0][d] + s_acc[1][d] + s_acc[2][d] + s_acc[3][d]) * inv);
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < W; ++w) sum += s_acc[w][d];
+        store_out_elem(a.out, a.out_dtype, row * D + d, sum * inv);
       }
       if (a.lse && lane == 0)
         a.lse[row] = wsum > 0.f ? (mu + log2f(wsum)) * 0.69314718055994531f : NEG_INF;
