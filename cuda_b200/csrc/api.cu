@@ -59,7 +59,7 @@ static int sm_count_cached() {
 // Pure arithmetic (no device access when num_ctas > 0): shared-memory stage layout and
 // workspace carving for one problem shape.
 static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, int k_format, int v_format,
-                       int scale_mode, int num_ctas, Layout& L) {
+                       int scale_mode, int num_ctas, Layout& L, bool token_major = false) {
   if (S < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return fail(CUDA_LLM_EINVAL, "num_q_heads must be a positive multiple of num_kv_heads");
   if (D != 64 && D != 128) return fail(CUDA_LLM_EINVAL, "Only head_dim 64 and 128 supported");
   if (page != 16 && page != 32 && page != 64) return fail(CUDA_LLM_EINVAL, "Only page_size 16, 32 and 64 supported");
@@ -75,6 +75,7 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   int HG = 8;
   while (Hkv % HG) HG >>= 1;
   while (pairs / HG < page) HG >>= 1;  // a stage must hold whole pages
+  if (token_major) HG = 1;             // contiguous K/V: a stage is 128 consecutive tokens of one head
   L.HG = HG;
   // 16 consumer warps, 8 bit: NT == 1 -> (HG heads) x (16/HG sub-tiles of 16 tokens);
   //                           NT == 2 -> 2 row halves x (HG heads) x (8/HG sub-tiles of 32 tokens)
@@ -84,12 +85,12 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   L.SUBS = (L.NT == 1 ? 16 : 8) / HG;
   L.tok_stage = pairs / HG;
   L.n_hg = Hkv / HG;
-  L.PPS = (L.tok_stage >= page) ? L.tok_stage / page : 1;
+  L.PPS = token_major ? 1 : (L.tok_stage >= page) ? L.tok_stage / page : 1;
   if (L.PPS > kMaxPagesPerStage) return fail(CUDA_LLM_EINVAL, "internal: too many pages per stage");
   const uint32_t pad = 0;  // every 16-token m-tile lies inside one page: no padding between pages
   const int DV = (v_format == CUDA_LLM_KV_FP4_E2M1) ? D / 2 : D;
-  L.k_chunk = (uint32_t)HG * D * page * eb;
-  L.v_chunk = (uint32_t)HG * DV * page * eb;
+  L.k_chunk = token_major ? (uint32_t)L.tok_stage * D * eb : (uint32_t)HG * D * page * eb;
+  L.v_chunk = token_major ? L.k_chunk : (uint32_t)HG * DV * page * eb;
   if (kv16) L.ks_chunk = L.vs_chunk = 0;
   else if (scale_mode == CUDA_LLM_SCALE_PER_TOKEN) L.ks_chunk = L.vs_chunk = (uint32_t)HG * page * 4;
   else if (scale_mode == CUDA_LLM_SCALE_MX_E8M0) L.ks_chunk = L.vs_chunk = (uint32_t)HG * (D / 32) * page;
@@ -386,6 +387,12 @@ size_t cuda_llm_dense_decode_workspace_bytes(int32_t num_seqs, int32_t num_heads
                     CUDA_LLM_SCALE_PER_HEAD, 0, L) == CUDA_LLM_OK && L.ws_total > need)
       need = L.ws_total;
   }
+  {  // contiguous 16-bit K/V: one head per stage
+    Layout L;
+    if (make_layout(num_seqs, num_heads, num_kv_heads, head_dim, 16, 1, CUDA_LLM_KV_BF16, CUDA_LLM_KV_BF16,
+                    CUDA_LLM_SCALE_PER_HEAD, 0, L, true) == CUDA_LLM_OK && L.ws_total > need)
+      need = L.ws_total;
+  }
   return need;
 }
 
@@ -434,8 +441,41 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
   int rc = check_dense(batch_size, num_heads, num_kv_heads, head_dim, dtype);
   if (rc != CUDA_LLM_OK) return rc;
   if (seq_len < 0) return fail(CUDA_LLM_EINVAL, "seq_len must be >= 0");
-  const size_t need = dense_decode_workspace_bytes(batch_size, num_heads, num_kv_heads, head_dim, seq_len);
+  const size_t need = cuda_llm_dense_decode_workspace_bytes(batch_size, num_heads, num_kv_heads, head_dim, seq_len);
   if (!workspace || workspace_bytes < need) return fail(CUDA_LLM_EWORKSPACE, "workspace missing or smaller than cuda_llm_dense_decode_workspace_bytes()");
+  if (dtype != CUDA_LLM_F32 && seq_len > 0 && !(((uintptr_t)k | (uintptr_t)v | (uintptr_t)workspace) & 15)) {
+    // 16-bit K/V: the persistent tensor-core kernel reading token-major rows (fp32 stays on the SIMT kernel)
+    Layout L;
+    int lrc = make_layout(batch_size, num_heads, num_kv_heads, head_dim, 16, 1, CUDA_LLM_KV_BF16, CUDA_LLM_KV_BF16,
+                          CUDA_LLM_SCALE_PER_HEAD, 0, L, true);
+    if (lrc != CUDA_LLM_OK) return lrc;
+    if (workspace_bytes < L.ws_total) return fail(CUDA_LLM_EWORKSPACE, "workspace missing or smaller than cuda_llm_dense_decode_workspace_bytes()");
+    DecodeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.q = q; a.kc = (const uint8_t*)k; a.vc = (const uint8_t*)v; a.out = o;
+    uint8_t* ws = (uint8_t*)workspace;
+    a.status = (uint32_t*)ws;
+    a.table = (int32_t*)(ws + L.ws_table);
+    a.part_lse = (float*)(ws + L.ws_lse);
+    a.part_o = (float*)(ws + L.ws_o);
+    a.S = batch_size; a.Hq = num_heads; a.Hkv = num_kv_heads; a.group = num_heads / num_kv_heads;
+    a.max_blocks = 1; a.num_blocks = 1; a.fixed_ctx = seq_len;
+    a.HG = L.HG; a.SUBS = L.SUBS; a.tok_stage = L.tok_stage; a.n_hg = L.n_hg; a.rows_max = L.rows_max;
+    a.q_dtype = a.out_dtype = dtype;
+    a.scale_log2 = softmax_scale * 1.4426950408889634f;
+    a.n_stages = L.n_stages;
+    a.stage_bytes = L.stage_bytes; a.off_v = L.off_v; a.off_ks = L.off_ks; a.off_vs = L.off_vs;
+    a.k_page_stride = L.k_page_stride; a.v_page_stride = L.v_page_stride;
+    a.k_chunk = L.k_chunk; a.v_chunk = L.v_chunk;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    LaunchFn fn;
+    if (dtype == CUDA_LLM_BF16) fn = head_dim == 64 ? launch_paged_decode<64, 16, MODE_KV_BF16_TM, 1, false> : launch_paged_decode<128, 16, MODE_KV_BF16_TM, 1, false>;
+    else fn = head_dim == 64 ? launch_paged_decode<64, 16, MODE_KV_F16_TM, 1, false> : launch_paged_decode<128, 16, MODE_KV_F16_TM, 1, false>;
+    cudaError_t e = fn(a, L.grid, L.smem_bytes, st);
+    if (e != cudaSuccess) return fail_cuda(e, "paged_decode_kernel launch");
+    e = (head_dim == 64) ? launch_merge_splits<64>(a, 16, L.grid, st) : launch_merge_splits<128>(a, 16, L.grid, st);
+    return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "merge_splits_kernel launch");
+  }
   cudaError_t e = run_dense_decode(false, q, k, v, nullptr, nullptr, o, batch_size, num_heads, num_kv_heads, head_dim,
                                    1, 1, 1, seq_len, softmax_scale, dtype, workspace, reinterpret_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "flash_decode launch");

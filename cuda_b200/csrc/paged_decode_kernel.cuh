@@ -48,7 +48,8 @@ constexpr int kBtRing = 16;               // ring slots for prefetched block-tab
 
 enum : int {
   MODE_PAGE_SCALE = 0, MODE_TOKEN_SCALE = 1, MODE_MX8 = 2, MODE_MX8K_MX4V = 3,
-  MODE_KV_F16 = 4, MODE_KV_BF16 = 5  // unquantised 16-bit cache (no scales)
+  MODE_KV_F16 = 4, MODE_KV_BF16 = 5,       // unquantised 16-bit paged cache (no scales)
+  MODE_KV_F16_TM = 6, MODE_KV_BF16_TM = 7  // unquantised 16-bit contiguous K/V [batch, heads, seq, head_dim]
 };
 
 enum : int { FLAG_NEW = 1, FLAG_LAST = 2, FLAG_DIRECT = 4 };
@@ -81,6 +82,7 @@ struct DecodeArgs {
   int S, Hq, Hkv, group, max_blocks, num_blocks;
   int HG, SUBS, n_hg, rows_max, tok_stage;
   int q_dtype, out_dtype, per_block;
+  int fixed_ctx;     // context length of every sequence when `ctx` is null (contiguous K/V)
   int helper_pairs;  // 16-row kernels of the 8-bit modes pair two warps on a short query (two results per sub-tile)
   int debug;  // diagnostics: bit 0 = consumers skip the math, bit 1 = producer skips the copies,
               // bit 2 = per-CTA timestamps into `trace`
@@ -95,6 +97,7 @@ struct DecodeArgs {
 };
 
 __device__ __forceinline__ int eff_ctx(const DecodeArgs& a, int s, int page) {
+  if (!a.ctx) return a.fixed_ctx;
   int c = a.ctx[s];
   long long cap = (long long)a.max_blocks * page;
   if (c > cap) {
@@ -168,7 +171,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   constexpr bool MX = (MODE == MODE_MX8 || MODE == MODE_MX8K_MX4V);
   constexpr int DV = V4 ? D / 2 : D;             // byte rows per head in the V slab
   constexpr int NB = D / 32;                     // scale blocks along head_dim
-  constexpr bool KV16 = (MODE == MODE_KV_F16 || MODE == MODE_KV_BF16);  // 2-byte elements, no scales
+  constexpr bool KV16 = (MODE >= MODE_KV_F16);  // 2-byte elements, no scales
+  constexpr bool TM = (MODE >= MODE_KV_F16_TM);  // token-major rows [token][head_dim] instead of pages [head_dim][token]
+  constexpr bool BF = (MODE == MODE_KV_BF16 || MODE == MODE_KV_BF16_TM);
   constexpr int SUB = (KV16 || NT == 1) ? 16 : 32;  // tokens per warp sub-tile
   constexpr int MT = SUB / 16;                   // m-tiles of S^T == k-tiles of PV per sub-tile
   constexpr float NEG_INF = -__builtin_huge_valf();
@@ -304,6 +309,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     const uint32_t ring = smem_base + kBtRingOff;
     int pf_done = 0;  // units whose block-table entries have been requested
     auto prefetch = [&]() {
+      if (TM) return;  // contiguous K/V: no block table
       if (pf_done < n_units) {
         const int tok0 = pc.tile * TOK_STAGE;
         const int np = min(PPS, (pc.ctx - tok0 + PAGE - 1) / PAGE);
@@ -316,7 +322,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       }
       cp_async_commit();
     };
-    if (n_units >= kBtAhead && pc.tile + kBtAhead <= pc.tiles) {
+    if (!TM && n_units >= kBtAhead && pc.tile + kBtAhead <= pc.tiles) {
       // common start: the first kBtAhead units are consecutive tiles of one (sequence, head group),
       // so their table entries are fetched by the lanes in parallel instead of unit by unit
       for (int idx = lane; idx < kBtAhead * PPS; idx += 32) {
@@ -362,9 +368,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         seg_direct = (a.SUBS == 1) && (seg_n_cta == 1) && !(!KV16 && NT == 2 && a.group * ic.qlen <= 8);
       }
       const int tok0 = ic.tile * TOK_STAGE;
-      const int np = min(PPS, (ic.ctx - tok0 + PAGE - 1) / PAGE);
+      const int np = TM ? 1 : min(PPS, (ic.ctx - tok0 + PAGE - 1) / PAGE);
       int c_blk = 0;
-      if (lane < np) {
+      if (!TM && lane < np) {
         c_blk = (int)lds32(ring + ((it % kBtRing) * kMaxPagesPerStage + lane) * 4);
         if (c_blk < 0 || c_blk >= a.num_blocks) {
           atomicOr(a.status, CUDA_LLM_ST_BAD_BLOCK);
@@ -395,13 +401,26 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       seg_fresh = false;
       const uint32_t fb = full_bar + 8 * slot;
       const bool no_copy = (a.debug & 2) != 0;  // diagnostics: math on whatever shared memory holds
-      if (lane == 0) {
+      if (TM) {
+        // one copy each for the K and the V rows of the live tokens of this (batch, head) tile
+        if (lane == 0) {
+          const uint32_t bytes = (uint32_t)min(TOK_STAGE, ic.ctx - tok0) * (D * 2);
+          mbar_arrive_expect_tx(fb, no_copy ? 0u : 2u * bytes);
+          if (!no_copy) {
+            const uint32_t sb = stage0 + slot * a.stage_bytes;
+            const uint64_t off = (((uint64_t)ic.s * a.Hkv + ic.hg) * a.fixed_ctx + tok0) * (D * 2);
+            bulk_g2s(sb, a.kc + off, bytes, fb);
+            bulk_g2s(sb + a.off_v, a.vc + off, bytes, fb);
+          }
+        }
+        __syncwarp();
+      } else if (lane == 0) {
         uint32_t bytes = (uint32_t)np * (a.k_chunk + a.v_chunk);
         if (NTYPES == 4) bytes += (uint32_t)np * (a.ks_chunk + a.vs_chunk);
         mbar_arrive_expect_tx(fb, no_copy ? 0u : bytes);
       }
       __syncwarp();
-      if (!no_copy) {
+      if (!TM && !no_copy) {
         const uint32_t sb = stage0 + slot * a.stage_bytes;
         // lane pi issues the copies of page pi
         if (lane < np) {
@@ -460,7 +479,13 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     vs_t[mt] = a.off_vs + pi * a.vs_page_stride + (h * PAGE + po + 2 * g) * 4;
     ks_mx[mt] = a.off_ks + pi * a.ks_page_stride + h * (NB * PAGE) + po + 2 * g;
     vs_mx[mt] = a.off_vs + pi * a.vs_page_stride + h * (NB * PAGE) + po + 4 * t;
-    if (KV16) {
+    if (TM) {
+      // row = token, 2*D bytes.  Thread (g,t) reads 16-byte chunks t, t+4, ... of token rows g and
+      // g+8 of its sub-tile: eight consecutive head_dim values each, used as two k-tile column
+      // pairs (Q.K) or, after an 8x8 transpose across the warp, as rows of O^T (P.V).
+      k_lm[mt] = (ts * 16 + g) * (D * 2) + t * 16;
+      v_lm[mt] = a.off_v + (ts * 16 + g) * (D * 2) + t * 16;
+    } else if (KV16) {
       // row = head_dim index, 2*PAGE bytes; a 16-token m-tile is 32 bytes of a row.  Four 8x8
       // matrices per ldmatrix.x4 -- K (transposed on load): lanes 8..15 the upper 8 tokens, lanes
       // 16..31 the upper 8 head_dim rows; V: lanes 8..15 the upper 8 rows, lanes 16..31 the upper
@@ -519,7 +544,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int kt = 0; kt < KT; ++kt)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          const int d = 16 * kt + 8 * hf + 2 * t;
+          // token-major K: the thread's 16-byte chunk (t + 4*(kt/2)) holds the columns of two k-tiles
+          const int d = TM ? 8 * (t + 4 * (kt >> 1)) + 4 * (kt & 1) + 2 * hf : 16 * kt + 8 * hf + 2 * t;
           float lo = 0.f, hi = 0.f;
           if (row_live) {
             if (a.q_dtype == CUDA_LLM_F32) {
@@ -534,7 +560,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
               lo = __low2float(v); hi = __high2float(v);
             }
           }
-          const uint32_t pk = (MODE == MODE_KV_BF16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+          const uint32_t pk = BF ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
           qf[kt][hf] = pk;
           if (PRECISE) ql[PRECISE ? kt : 0][hf] = pack_f16x2(lo - f16x2_lo(pk), hi - f16x2_hi(pk));
         }
@@ -567,13 +593,25 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) sacc[mt][c] = 0.f;
-      if (KV16) {
+      if (TM) {
+#pragma unroll
+        for (int j = 0; j < D / 32; ++j) {
+          const uint4 lo = lds128(sb + k_lm[0] + j * 64), hi = lds128(sb + k_lm[0] + 8 * (D * 2) + j * 64);
+          if (BF) {
+            mma_bf16(sacc[0], lo.x, hi.x, lo.y, hi.y, qf[2 * j][0], qf[2 * j][1]);
+            mma_bf16(sacc[0], lo.z, hi.z, lo.w, hi.w, qf[2 * j + 1][0], qf[2 * j + 1][1]);
+          } else {
+            mma_f16(sacc[0], lo.x, hi.x, lo.y, hi.y, qf[2 * j][0], qf[2 * j][1]);
+            mma_f16(sacc[0], lo.z, hi.z, lo.w, hi.w, qf[2 * j + 1][0], qf[2 * j + 1][1]);
+          }
+        }
+      } else if (KV16) {
         // 16-bit K: token g (g+8) of the sub-tile on S^T rows g (g+8)
 #pragma unroll
         for (int kt = 0; kt < KT; ++kt) {
           uint32_t r4[4];
           ldmatrix_x4_trans(r4, sb + k_lm[0] + kt * 16 * PAGE * 2);
-          if (MODE == MODE_KV_BF16) mma_bf16(sacc[0], r4[0], r4[1], r4[2], r4[3], qf[kt][0], qf[kt][1]);
+          if (BF) mma_bf16(sacc[0], r4[0], r4[1], r4[2], r4[3], qf[kt][0], qf[kt][1]);
           else mma_f16(sacc[0], r4[0], r4[1], r4[2], r4[3], qf[kt][0], qf[kt][1]);
         }
       }
@@ -709,7 +747,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          const uint32_t pk = (MODE == MODE_KV_BF16) ? pack_bf16x2(pv[mt][2 * hf], pv[mt][2 * hf + 1])
+          const uint32_t pk = BF ? pack_bf16x2(pv[mt][2 * hf], pv[mt][2 * hf + 1])
                                                      : pack_f16x2(pv[mt][2 * hf], pv[mt][2 * hf + 1]);
           pb[mt][hf] = movmatrix_trans(pk);
           if (PRECISE)
@@ -727,14 +765,36 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         // P^T after the transpose: b0 = tokens 2t, 2t+1, b1 = tokens 2t+8, 2t+9
         const uint32_t m_lo = (2 * t < nv ? 0xffffu : 0u) | (2 * t + 1 < nv ? 0xffff0000u : 0u);
         const uint32_t m_hi = (2 * t + 8 < nv ? 0xffffu : 0u) | (2 * t + 9 < nv ? 0xffff0000u : 0u);
+        if (TM) {
+          // a register of token row g holds two head_dim values; the transpose turns the 8x8 block
+          // (token g, value pair of thread t) into (value, token pair 2t, 2t+1): O^T row g of m-tile
+          // 2j+rp is head_dim 8*((g>>1) + 4j) + 4rp + (g&1), row g+8 that + 2
 #pragma unroll
-        for (int mo = 0; mo < KT; ++mo) {
+          for (int j = 0; j < D / 32; ++j) {
+            const uint4 lo = lds128(sb + v_lm[0] + j * 64), hi = lds128(sb + v_lm[0] + 8 * (D * 2) + j * 64);
+#pragma unroll
+            for (int rp = 0; rp < 2; ++rp) {
+              uint32_t va[4];
+              va[0] = movmatrix_trans(rp ? lo.z : lo.x);
+              va[1] = movmatrix_trans(rp ? lo.w : lo.y);
+              va[2] = movmatrix_trans(rp ? hi.z : hi.x);
+              va[3] = movmatrix_trans(rp ? hi.w : hi.y);
+              if (tail) {
+                va[0] &= m_lo; va[1] &= m_lo; va[2] &= m_hi; va[3] &= m_hi;
+              }
+              if (BF) mma_bf16(oacc[2 * j + rp], va[0], va[1], va[2], va[3], pb[0][0], pb[0][1]);
+              else mma_f16(oacc[2 * j + rp], va[0], va[1], va[2], va[3], pb[0][0], pb[0][1]);
+            }
+          }
+        }
+#pragma unroll
+        for (int mo = 0; mo < (TM ? 0 : KT); ++mo) {
           uint32_t va[4];
           ldmatrix_x4(va, sb + v_lm[0] + mo * 16 * PAGE * 2);
           if (tail) {  // a dead slot may hold a NaN pattern: 0 * NaN must not reach the accumulator
             va[0] &= m_lo; va[1] &= m_lo; va[2] &= m_hi; va[3] &= m_hi;
           }
-          if (MODE == MODE_KV_BF16) mma_bf16(oacc[mo], va[0], va[1], va[2], va[3], pb[0][0], pb[0][1]);
+          if (BF) mma_bf16(oacc[mo], va[0], va[1], va[2], va[3], pb[0][0], pb[0][1]);
           else mma_f16(oacc[mo], va[0], va[1], va[2], va[3], pb[0][0], pb[0][1]);
         }
       }
@@ -825,8 +885,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           const size_t row = (size_t)(qbase + j) * a.Hq + (size_t)kvh * a.group + i;
 #pragma unroll
           for (int mt = 0; mt < KT; ++mt) {
-            const int d0 = V4 ? mt * 16 + 2 * g : mt * 16 + g;
-            const int d1 = V4 ? d0 + 1 : d0 + 8;
+            const int d0 = TM ? 8 * ((g >> 1) + 4 * (mt >> 1)) + 4 * (mt & 1) + (g & 1) : V4 ? mt * 16 + 2 * g : mt * 16 + g;
+            const int d1 = TM ? d0 + 2 : V4 ? d0 + 1 : d0 + 8;
             store_out_elem(a.out, a.out_dtype, row * D + d0, oacc[mt][cc] * inv);
             store_out_elem(a.out, a.out_dtype, row * D + d1, oacc[mt][2 + cc] * inv);
           }
@@ -837,8 +897,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           float* po = a.part_o + prow * D;
 #pragma unroll
           for (int mt = 0; mt < KT; ++mt) {
-            const int d0 = V4 ? mt * 16 + 2 * g : mt * 16 + g;
-            const int d1 = V4 ? d0 + 1 : d0 + 8;
+            const int d0 = TM ? 8 * ((g >> 1) + 4 * (mt >> 1)) + 4 * (mt & 1) + (g & 1) : V4 ? mt * 16 + 2 * g : mt * 16 + g;
+            const int d1 = TM ? d0 + 2 : V4 ? d0 + 1 : d0 + 8;
             po[d0] = oacc[mt][cc] * inv;
             po[d1] = oacc[mt][2 + cc] * inv;
           }

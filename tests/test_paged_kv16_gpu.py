@@ -103,3 +103,32 @@ def test_llama_shape_batch(ops):
     g = wl.to("cuda")
     out = ops.paged_attention_forward(g.query, g.key_cache, g.value_cache, g.block_tables, g.context_lens)
     _check(out, _oracle(wl), torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------------------
+# contiguous K/V [batch, kv_heads, seq, head_dim] (the reference's async_flash_decode)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("seq_len", [1, 15, 16, 17, 127, 128, 129, 1000, 4100])
+@pytest.mark.parametrize("hkv,group,d", [(4, 1, 128), (2, 4, 128), (1, 8, 128), (3, 2, 64)])
+def test_flash_decode_shapes(ops, dtype, seq_len, hkv, group, d):
+    g = torch.Generator().manual_seed(seq_len * 31 + hkv)
+    b = 3
+    q = torch.randn(b, hkv * group, 1, d, generator=g).to(dtype)
+    k = torch.randn(b, hkv, seq_len, d, generator=g).to(dtype)
+    v = torch.randn(b, hkv, seq_len, d, generator=g).to(dtype)
+    ref = O.ref_flash_decode(q, k.repeat_interleave(group, dim=1), v.repeat_interleave(group, dim=1))
+    out = ops.async_flash_decode(q.cuda(), k.cuda(), v.cuda())
+    assert out.shape == q.shape and out.dtype == dtype
+    _check(out, ref, dtype, f"seq {seq_len} hkv {hkv} group {group} d {d}")
+
+
+def test_flash_decode_many_heads_few_ctas_worth_of_work(ops):
+    """More (batch, head) segments than CTAs and fewer: both partitions of the unit range."""
+    g = torch.Generator().manual_seed(77)
+    for b, h, s in ((40, 8, 300), (1, 2, 9000)):
+        q = torch.randn(b, h, 1, 128, generator=g).to(torch.bfloat16)
+        k = torch.randn(b, h, s, 128, generator=g).to(torch.bfloat16)
+        v = torch.randn(b, h, s, 128, generator=g).to(torch.bfloat16)
+        out = ops.async_flash_decode(q.cuda(), k.cuda(), v.cuda())
+        _check(out, O.ref_flash_decode(q, k, v), torch.bfloat16, f"b {b} h {h} s {s}")
