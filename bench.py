@@ -29,6 +29,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {"cfg1": 1, "cfg2": 2, "cfg3": 3, "cfg4": 4, "cfg5": 5}
+# secondary lines for the unquantised entry points (same Llama-3-8B head shape, bf16 K/V)
+AUX_WORKLOADS = ("pa16", "fd16")
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode-kernel launch,
@@ -135,13 +137,68 @@ def cpu_reference_run(wl_cpu, budget_s: float, max_seqs=None):
     return time.perf_counter() - t0, nbytes, qtok, done
 
 
+def aux_workload(args, rank, world, local):
+    """paged_attention (pa16) / async_flash_decode (fd16) over a bf16 cache, 32 query / 8 KV heads,
+    head_dim 128, batch 64 per GPU: kernel + merge timed with CUDA events, one JSON line."""
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU reference arm covers the FP8 configurations only"}))
+        return
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    from cuda_b200 import ops, workloads
+    batch = args.batch or 64
+    g = torch.Generator().manual_seed(2000 + rank)
+    if args.workload == "pa16":
+        ctx = torch.randint(int(1024 * args.ctx_scale), int(4096 * args.ctx_scale) + 1, (batch,), generator=g).tolist()
+        wl = workloads.build_workload("pa16_llama8b_bf16", context_lens=ctx, q_lens=None, num_q_heads=32,
+                                      num_kv_heads=8, head_dim=128, page_size=16, q_dtype=torch.bfloat16,
+                                      scale_mode="none", pool_factor=1.25, seed=2000 + rank,
+                                      cache_dtype=torch.bfloat16).to(dev)
+        kv_bytes = sum(ctx) * 8 * 128 * 2 * 2
+        fn = lambda: ops.paged_attention_forward(wl.query, wl.key_cache, wl.value_cache, wl.block_tables,
+                                                 wl.context_lens)
+        cfg = {"workload": wl.name, "batch_per_gpu": batch, "kv_tokens_per_gpu": sum(ctx), "page_size": 16}
+    else:
+        seq = int(2560 * args.ctx_scale)
+        q = torch.randn(batch, 32, 1, 128, generator=g).to(torch.bfloat16).to(dev)
+        k = torch.randn(batch, 8, seq, 128, generator=g).to(torch.bfloat16).to(dev)
+        v = torch.randn(batch, 8, seq, 128, generator=g).to(torch.bfloat16).to(dev)
+        kv_bytes = 2 * k.numel() * 2
+        fn = lambda: ops.async_flash_decode(q, k, v)
+        cfg = {"workload": "fd16_llama8b_bf16", "batch_per_gpu": batch, "seq_len": seq}
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    peak, peak_src = measured_peak()
+    cfg.update({"heads": "32q/8kv", "head_dim": 128, "kv_bytes_per_gpu": kv_bytes,
+                "l2": "inputs larger than L2, no flush needed"})
+    if rank != 0:
+        return
+    print(json.dumps({"metric": "bf16_decode_kv_hbm_throughput", "value": kv_bytes / (ms * 1e-3) / 1e12, "unit": "TB/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                      "higher_is_better": True, "dtype": "bf16 mma, f32 acc", "data": "synthetic", "config": cfg,
+                      "roofline": {"bound": "hbm", "achieved": kv_bytes / (ms * 1e-3) / 1e9, "peak": peak,
+                                   "unit": "GB/s", "frac": kv_bytes / (ms * 1e-3) / 1e9 / peak,
+                                   "peak_source": peak_src, "kernel": "paged_decode_kernel + merge_splits_kernel"},
+                      "gpu_launches": 2 * args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + list(AUX_WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the batch (smaller ncu captures)")
     ap.add_argument("--ctx-scale", type=float, default=1.0)
     ap.add_argument("--cpu-budget-s", type=float, default=15.0)
@@ -152,6 +209,8 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     from cuda_b200 import workloads
+    if args.workload in AUX_WORKLOADS:
+        return aux_workload(args, rank, world, local)
     cfg_id = WORKLOADS[args.workload]
     seed = 1000 + cfg_id + 7919 * rank
 

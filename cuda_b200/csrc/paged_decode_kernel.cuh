@@ -23,15 +23,17 @@
 //    accumulate).  Tokens sit on the M side (always a full 16-row tile); the query rows (GQA
 //    group x q_len) sit on the 8-wide N side.  E4M3 / E2M1 bytes are widened to f16 in
 //    registers (exact), fp32 per-token scales are applied to the fp32 logits and folded into P,
-//    E8M0 block scales are applied to the fp32 partial logits (K) or to the f16 operand (V).
+//    E8M0 block scales are applied to the fp32 partial logits (K), to P (E4M3 V) or to the f16
+//    V operand (packed E2M1 V).
 //  * Online softmax state (m, l) per query row lives in registers; every warp writes its
 //    result normalised, with a base-2 log-sum-exp, and merge_splits_kernel combines them.
 //
 // Numerical notes.  E4M3 -> f16 and E2M1 -> f16 are exact.  Q is used in f16 (bf16 -> f16 is
 // exact for |q| in [2^-14, 65504]); an fp32 Q is split into an f16 high and low part when
-// PRECISE.  P is rounded to f16 (again hi+lo when PRECISE).  V * 2^e is formed in f16 and is
-// exact for e in [-14, 7] (E4M3) or [-16, 8] (E2M1); smaller exponents flush to zero, larger
-// ones overflow to inf.
+// PRECISE.  P is rounded to f16 (again hi+lo when PRECISE).  An E8M0 scale 2^e of an E4M3 V block
+// multiplies P in f16 (exact up to e = 15; below about e = -10 the product loses bits to f16
+// subnormals); for packed E2M1 V the product V * 2^e is formed in f16 and is exact for e in
+// [-16, 8]; smaller exponents flush to zero, larger ones overflow to inf.
 #pragma once
 #include "sm100_primitives.cuh"
 #include "cuda_llm_b200.h"
@@ -241,7 +243,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   const bool small_units = total_units < (1ll << 31) - (long long)gridDim.x;
   const long long per_cta = small_units ? (long long)(((unsigned)total_units + gridDim.x - 1) / gridDim.x)
                                         : (total_units + gridDim.x - 1) / gridDim.x;
-  const long long u_begin = min(total_units, (long long)blockIdx.x * per_cta);
+  const int vb = (a.debug & 32) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // diagnostics: reversed ranges
+  const long long u_begin = min(total_units, (long long)vb * per_cta);
   const long long u_end = min(total_units, u_begin + per_cta);
   if (u_begin < u_end && my_units > 0 && u_begin >= my_prefix && u_begin < my_prefix + my_units) {
     long long U = my_prefix;
@@ -259,7 +262,11 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     }
   }
   __syncthreads();
-  if (tracing && tid == 0) a.trace[blockIdx.x * 8 + 4] = globaltimer_ns();
+  if (tracing && tid == 0) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    a.trace[blockIdx.x * 8 + 4] = smid;
+  }
   if (u_begin >= u_end) return;
   const int n_units = (int)(u_end - u_begin);
 
@@ -389,7 +396,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       if (lane == 0) {
         const int flags = (is_new ? FLAG_NEW : 0) | (is_last ? FLAG_LAST : 0) | (seg_direct ? FLAG_DIRECT : 0);
         sts128(meta, ic.s, ic.hg, tok0, ic.ctx);
-        sts128(meta + 16, flags, ic.s * a.n_hg + ic.hg + (int)blockIdx.x, ic.qbase, ic.qlen);
+        sts128(meta + 16, flags, ic.s * a.n_hg + ic.hg + vb, ic.qbase, ic.qlen);
         if (ic.tile == 0) {
           int32_t* t = a.table + 4 * (size_t)(ic.s * a.n_hg + ic.hg);
           t[0] = seg_cta_first;
@@ -416,7 +423,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         __syncwarp();
       } else if (lane == 0) {
         uint32_t bytes = (uint32_t)np * (a.k_chunk + a.v_chunk);
-        if (NTYPES == 4) bytes += (uint32_t)np * (a.ks_chunk + a.vs_chunk);
+        if (NTYPES == 4 && !(a.debug & 16)) bytes += (uint32_t)np * (a.ks_chunk + a.vs_chunk);
         mbar_arrive_expect_tx(fb, no_copy ? 0u : bytes);
       }
       __syncwarp();
@@ -429,7 +436,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
                    a.k_chunk, fb);
           bulk_g2s(sb + a.off_v + lane * a.v_page_stride,
                    a.vc + b * a.v_blk_stride + (uint64_t)ic.hg * a.v_chunk, a.v_chunk, fb);
-          if (NTYPES == 4) {
+          if (NTYPES == 4 && !(a.debug & 16)) {
             bulk_g2s(sb + a.off_ks + lane * a.ks_page_stride,
                      a.ks + b * a.ks_blk_stride + (uint64_t)ic.hg * a.ks_chunk, a.ks_chunk, fb);
             bulk_g2s(sb + a.off_vs + lane * a.vs_page_stride,
@@ -817,17 +824,21 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
               s02 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4240));  // tokens 4t, 4t+2
               s13 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4341));  // tokens 4t+1, 4t+3
             }
+            // a block scale multiplies P (two registers per 32 head_dim rows), not the V operand
+            uint32_t b0 = pb[mt][0], b1 = pb[mt][1];
+            uint32_t bl0 = pbl[PRECISE ? mt : 0][0], bl1 = pbl[PRECISE ? mt : 0][1];
+            if (MX) {
+              b0 = hmul2(b0, s02); b1 = hmul2(b1, s13);
+              if (PRECISE) { bl0 = hmul2(bl0, s02); bl1 = hmul2(bl1, s13); }
+            }
 #pragma unroll
             for (int kk = 0; kk < 2; ++kk) {
               const int mo = 2 * dp + kk;
               const uint32_t x0 = prmt(va[2 * kk], 0u, 0x3120), x1 = prmt(va[2 * kk + 1], 0u, 0x3120);
-              uint32_t A0 = e4m3x2_to_f16x2_lo(x0), A1 = e4m3x2_to_f16x2_lo(x1);
-              uint32_t A2 = e4m3x2_to_f16x2_hi(x0), A3 = e4m3x2_to_f16x2_hi(x1);
-              if (MX) {
-                A0 = hmul2(A0, s02); A1 = hmul2(A1, s02); A2 = hmul2(A2, s13); A3 = hmul2(A3, s13);
-              }
-              mma_f16(oacc[mo], A0, A1, A2, A3, pb[mt][0], pb[mt][1]);
-              if (PRECISE) mma_f16(oacc[mo], A0, A1, A2, A3, pbl[PRECISE ? mt : 0][0], pbl[PRECISE ? mt : 0][1]);
+              const uint32_t A0 = e4m3x2_to_f16x2_lo(x0), A1 = e4m3x2_to_f16x2_lo(x1);
+              const uint32_t A2 = e4m3x2_to_f16x2_hi(x0), A3 = e4m3x2_to_f16x2_hi(x1);
+              mma_f16(oacc[mo], A0, A1, A2, A3, b0, b1);
+              if (PRECISE) mma_f16(oacc[mo], A0, A1, A2, A3, bl0, bl1);
             }
           } else {
             // packed E2M1: matrix m holds byte rows 32dp + 8m + g, i.e. O m-tile 4dp + m:
