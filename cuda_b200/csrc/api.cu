@@ -256,8 +256,8 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   a.n_stages = L.n_stages;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_MATH) a.debug |= 1;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_COPY) a.debug |= 2;
-  if (p->flags & 16) a.debug |= 16;
-  if (p->flags & 32) a.debug |= 32;
+  if (p->flags & CUDA_LLM_FLAG_DIAG_NO_SCALE_COPY) a.debug |= 16;
+  if (p->flags & CUDA_LLM_FLAG_DIAG_REVERSED) a.debug |= 32;
   if (p->flags & CUDA_LLM_FLAG_DIAG_TRACE) {  // per-CTA timestamps go where the lse would go
     a.debug |= 4;
     a.trace = reinterpret_cast<unsigned long long*>(p->lse);

@@ -87,9 +87,9 @@ struct DecodeArgs {
   int fixed_ctx;     // context length of every sequence when `ctx` is null (contiguous K/V)
   int helper_pairs;  // 16-row kernels of the 8-bit modes pair two warps on a short query (two results per sub-tile)
   int debug;  // diagnostics: bit 0 = consumers skip the math, bit 1 = producer skips the copies,
-              // bit 2 = per-CTA timestamps into `trace`
-  unsigned long long* trace;  // [grid][8] ns: kernel entry, first stage landed, last stage consumed, exit,
-                              // plan done, table prefetches issued, first table entry landed, first copy issued
+              // bit 2 = per-CTA timestamps into `trace`, bit 4 = no scale copies, bit 5 = reversed ranges
+  unsigned long long* trace;  // [grid][8]: ns of kernel entry, first stage landed, last stage consumed, exit;
+                              // SM id; ns of table prefetches issued, first table entry landed, first copy issued
   float scale_log2;
   int n_stages;
   uint32_t stage_bytes, off_v, off_ks, off_vs;
@@ -277,6 +277,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     // small shared-memory ring with 4-byte cp.async.  The block-table read is the one dependent
     // global load on the copy path; fetching it several stages early keeps it off the critical
     // path of every stage.
+    const uint64_t stream_policy = l2_policy_evict_first();  // K/V bytes are read once
     constexpr int NTYPES = (MODE == MODE_PAGE_SCALE || KV16) ? 2 : 4;
     const int PPS = (TOK_STAGE >= PAGE) ? TOK_STAGE / PAGE : 1;  // pages per stage
     auto load_seq = [&](UnitCursor& c) {
@@ -416,8 +417,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           if (!no_copy) {
             const uint32_t sb = stage0 + slot * a.stage_bytes;
             const uint64_t off = (((uint64_t)ic.s * a.Hkv + ic.hg) * a.fixed_ctx + tok0) * (D * 2);
-            bulk_g2s(sb, a.kc + off, bytes, fb);
-            bulk_g2s(sb + a.off_v, a.vc + off, bytes, fb);
+            bulk_g2s_hint(sb, a.kc + off, bytes, fb, stream_policy);
+            bulk_g2s_hint(sb + a.off_v, a.vc + off, bytes, fb, stream_policy);
           }
         }
         __syncwarp();
@@ -432,15 +433,15 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         // lane pi issues the copies of page pi
         if (lane < np) {
           const uint64_t b = (uint64_t)c_blk;
-          bulk_g2s(sb + lane * a.k_page_stride, a.kc + b * a.k_blk_stride + (uint64_t)ic.hg * a.k_chunk,
-                   a.k_chunk, fb);
-          bulk_g2s(sb + a.off_v + lane * a.v_page_stride,
-                   a.vc + b * a.v_blk_stride + (uint64_t)ic.hg * a.v_chunk, a.v_chunk, fb);
+          bulk_g2s_hint(sb + lane * a.k_page_stride, a.kc + b * a.k_blk_stride + (uint64_t)ic.hg * a.k_chunk,
+                   a.k_chunk, fb, stream_policy);
+          bulk_g2s_hint(sb + a.off_v + lane * a.v_page_stride,
+                   a.vc + b * a.v_blk_stride + (uint64_t)ic.hg * a.v_chunk, a.v_chunk, fb, stream_policy);
           if (NTYPES == 4 && !(a.debug & 16)) {
-            bulk_g2s(sb + a.off_ks + lane * a.ks_page_stride,
-                     a.ks + b * a.ks_blk_stride + (uint64_t)ic.hg * a.ks_chunk, a.ks_chunk, fb);
-            bulk_g2s(sb + a.off_vs + lane * a.vs_page_stride,
-                     a.vs + b * a.vs_blk_stride + (uint64_t)ic.hg * a.vs_chunk, a.vs_chunk, fb);
+            bulk_g2s_hint(sb + a.off_ks + lane * a.ks_page_stride,
+                     a.ks + b * a.ks_blk_stride + (uint64_t)ic.hg * a.ks_chunk, a.ks_chunk, fb, stream_policy);
+            bulk_g2s_hint(sb + a.off_vs + lane * a.vs_page_stride,
+                     a.vs + b * a.vs_blk_stride + (uint64_t)ic.hg * a.vs_chunk, a.vs_chunk, fb, stream_policy);
           }
         }
       }

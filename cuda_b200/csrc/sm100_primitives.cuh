@@ -68,6 +68,20 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
       ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
+// The same copy with an L2 eviction policy (createpolicy): data that is read once should not push
+// the small, re-read tensors (tables, lengths, partial results) out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                              uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
 
 // 4-byte asynchronous copy global -> shared (no register in between), grouped and waited on
 // with commit / wait_group.

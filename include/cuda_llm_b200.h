@@ -46,9 +46,13 @@ extern "C" {
 #define CUDA_LLM_FLAG_DIAG_NO_COPY 4 /* diagnostics: do the attention math on stale shared memory,
                                         no page copies (output is meaningless)                */
 #define CUDA_LLM_FLAG_DIAG_TRACE 8   /* diagnostics: `lse` receives, per CTA, eight 64-bit nanosecond
-                                        timestamps (entry, first stage landed, last stage consumed,
-                                        exit, four prologue marks) instead of log-sum-exps; needs
-                                        grid*64 bytes         */
+                                        words (ns of entry, first stage landed, last stage consumed,
+                                        exit; SM id; three prologue marks) instead of log-sum-exps;
+                                        needs grid*64 bytes         */
+#define CUDA_LLM_FLAG_DIAG_NO_SCALE_COPY 16 /* diagnostics: do not copy the per-token / block scales
+                                              (output is meaningless)                          */
+#define CUDA_LLM_FLAG_DIAG_REVERSED 32      /* diagnostics: CTA i takes the unit range of CTA grid-1-i
+                                              (same result; separates SM effects from data effects) */
 /* bits 8..11: diagnostics: cap the shared-memory ring at this many stages (0 = as many as fit) */
 
 /* ---- enums ---------------------------------------------------------------------------- */
