@@ -1,0 +1,8 @@
+"""Stand-in for the reference's ``cuda_llm`` package (decode path only).  The reference documents
+``cuda_llm.flash_decode(q_single, k_cache, v_cache)`` (``README.md:75`` in the reference project);
+``paged_attention`` and ``fp8_paged_attention`` mirror the pybind signatures of the same path."""
+from cuda_b200.ops import async_flash_decode as flash_decode  # noqa: F401
+from cuda_b200.ops import fp8_paged_attention_forward as fp8_paged_attention  # noqa: F401
+from cuda_b200.ops import paged_attention_forward as paged_attention  # noqa: F401
+
+__all__ = ["flash_decode", "paged_attention", "fp8_paged_attention"]

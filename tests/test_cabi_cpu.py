@@ -107,3 +107,24 @@ def test_reference_cxx_dispatchers_are_exported(lib):
     the names its binding's object file asks the linker for (Itanium mangling of those signatures)."""
     for name in CXX_SYMBOLS.values():
         assert hasattr(lib, name), name
+
+
+def test_reference_module_names_import():
+    """The shims under the reference's module names expose the decode entry points (no compute)."""
+    import importlib
+    import sys
+    from cuda_b200 import compat, ops
+    sys.path.insert(0, compat.PATH)
+    try:
+        ext = importlib.import_module("fused_online_softmax_cuda")
+        pkg = importlib.import_module("cuda_llm")
+    finally:
+        sys.path.remove(compat.PATH)
+    assert ext.paged_attention_forward is ops.paged_attention_forward
+    assert ext.fp8_paged_attention_forward is ops.fp8_paged_attention_forward
+    assert ext.async_flash_decode is ops.async_flash_decode
+    assert pkg.flash_decode is ops.async_flash_decode
+    assert pkg.paged_attention is ops.paged_attention_forward
+    assert pkg.fp8_paged_attention is ops.fp8_paged_attention_forward
+    for mod in ("fused_online_softmax_cuda", "cuda_llm"):
+        sys.modules.pop(mod, None)
