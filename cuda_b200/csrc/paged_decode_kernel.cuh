@@ -7,9 +7,10 @@
 //
 //  * Work unit = one *stage*: TOK_STAGE consecutive tokens of one sequence for HG adjacent KV
 //    heads (HG * TOK_STAGE/32 = 8).  All units of the launch, in (sequence, head-group, tile)
-//    order, are cut into equal contiguous ranges, one per CTA, so every SM streams the same
-//    number of bytes whatever the context-length distribution is.  A sequence that straddles
-//    a cut is finished by the split merge kernel.
+//    order, are cut into contiguous ranges of equal cost, one per CTA, so every SM streams the
+//    same number of bytes whatever the context-length distribution is (a unit costs 1, or 2
+//    where a query of 9..16 rows makes both warps of a pair compute it).  A sequence that
+//    straddles a cut is finished by the split merge kernel.
 //  * One producer warp walks the CTA's range.  It prefetches block-table entries several
 //    stages ahead into shared memory with 4-byte cp.async, and for every stage issues 1-D bulk
 //    (TMA) copies: per page one copy each for the K bytes, the V bytes and their scales of all
@@ -54,7 +55,7 @@ enum : int {
   MODE_KV_F16_TM = 6, MODE_KV_BF16_TM = 7  // unquantised 16-bit contiguous K/V [batch, heads, seq, head_dim]
 };
 
-enum : int { FLAG_NEW = 1, FLAG_LAST = 2, FLAG_DIRECT = 4 };
+enum : int { FLAG_NEW = 1, FLAG_LAST = 2, FLAG_DIRECT = 4, FLAG_END = 8 };
 
 struct StageMeta {  // 32 ints
   int s, hg, tok0, ctx, flags, slot, qbase, qlen;
@@ -159,10 +160,13 @@ __device__ __forceinline__ uint32_t e2m1_hi_nibbles_to_f16_hi_bytes(uint32_t w) 
   return (w & 0x80808080u) | ((w >> 3) & 0x0E0E0E0Eu);
 }
 
-// Walks the (sequence, head-group, tile) units of a CTA's range in order.
+// Walks the (sequence, head-group, tile) units of a CTA's range in order.  Positions are in cost
+// units: a unit advances the position by its weight `w` (1, or 2 where both row halves of a 16-row
+// kernel have to compute it), and the launch is cut into ranges of equal cost.
 struct UnitCursor {
-  int s, hg, tile, tiles, ctx, qbase, qlen;
-  long long seg_first;  // global unit index of (s, hg, tile 0)
+  int s, hg, tile, tiles, ctx, qbase, qlen, w;
+  long long pos;        // cost position of the current unit
+  long long seg_first;  // cost position of (s, hg, tile 0)
 };
 
 template <int D, int PAGE, int MODE, int NT, bool PRECISE>
@@ -214,13 +218,19 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   // ---------------------------------------------------------------- plan: equal unit ranges
   const int per = (a.S + kDecodeThreads - 1) / kDecodeThreads;
   const int s_lo = min(a.S, tid * per), s_hi = min(a.S, s_lo + per);
-  long long my_units = 0;
-  for (int s = s_lo; s < s_hi; ++s) {
+  // cost of a sequence: its units, twice for a query of 9..16 rows in the 8-bit 16-row kernels
+  // (both warps of a pair then compute every stage instead of alternating)
+  constexpr bool WEIGHTED = (NT == 2) && !KV16;
+  auto seq_cost = [&](int s) -> long long {
     int qb, ql;
     seq_q(a, s, qb, ql);
-    int c = eff_ctx(a, s, PAGE);
-    if (ql > 0 && c > 0) my_units += (long long)((c + TOK_STAGE - 1) / TOK_STAGE) * a.n_hg;
-  }
+    const int c = eff_ctx(a, s, PAGE);
+    if (ql <= 0 || c <= 0) return 0;
+    const int w = (WEIGHTED && a.group * ql > 8) ? 2 : 1;
+    return (long long)((c + TOK_STAGE - 1) / TOK_STAGE) * a.n_hg * w;
+  };
+  long long my_units = 0;
+  for (int s = s_lo; s < s_hi; ++s) my_units += seq_cost(s);
   // block-wide exclusive scan of my_units: warp shuffles, then the warp totals
   long long incl = my_units;
 #pragma unroll
@@ -241,18 +251,18 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   // unit counts fit 32 bits in practice (a unit moves at least 2 KB); 64-bit division is kept as
   // the fallback only
   const bool small_units = total_units < (1ll << 31) - (long long)gridDim.x;
-  const long long per_cta = small_units ? (long long)(((unsigned)total_units + gridDim.x - 1) / gridDim.x)
-                                        : (total_units + gridDim.x - 1) / gridDim.x;
+  // a range is never narrower than the largest unit weight, so that every CTA between the first
+  // and the last one of a (sequence, head group) owns at least one of its units
+  const long long per_cta = max(small_units ? (long long)(((unsigned)total_units + gridDim.x - 1) / gridDim.x)
+                                            : (total_units + gridDim.x - 1) / gridDim.x,
+                                (long long)(WEIGHTED ? 2 : 1));
   const int vb = (a.debug & 32) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // diagnostics: reversed ranges
   const long long u_begin = min(total_units, (long long)vb * per_cta);
   const long long u_end = min(total_units, u_begin + per_cta);
   if (u_begin < u_end && my_units > 0 && u_begin >= my_prefix && u_begin < my_prefix + my_units) {
     long long U = my_prefix;
     for (int s = s_lo; s < s_hi; ++s) {
-      int qb, ql;
-      seq_q(a, s, qb, ql);
-      int c = eff_ctx(a, s, PAGE);
-      long long n = (ql > 0 && c > 0) ? (long long)((c + TOK_STAGE - 1) / TOK_STAGE) * a.n_hg : 0;
+      const long long n = seq_cost(s);
       if (u_begin < U + n) {
         plan[1] = s;
         plan[2] = U;
@@ -268,7 +278,6 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     a.trace[blockIdx.x * 8 + 4] = smid;
   }
   if (u_begin >= u_end) return;
-  const int n_units = (int)(u_end - u_begin);
 
   if (warp == kConsumerWarps) {
     // =============================================================== producer warp
@@ -284,41 +293,56 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       c.ctx = eff_ctx(a, c.s, PAGE);
       seq_q(a, c.s, c.qbase, c.qlen);
       c.tiles = (c.qlen > 0) ? (c.ctx + TOK_STAGE - 1) / TOK_STAGE : 0;
+      c.w = (WEIGHTED && a.group * c.qlen > 8) ? 2 : 1;
     };
     // step to the next unit (tile -> head group -> sequence)
     auto advance = [&](UnitCursor& c) {
+      c.pos += c.w;
+      if (c.pos >= u_end) return;  // end of this CTA's range: the cursor is not used again
       if (++c.tile < c.tiles) return;
       c.tile = 0;
-      c.seg_first += c.tiles;
+      c.seg_first = c.pos;
       if (++c.hg < a.n_hg) return;
       c.hg = 0;
       for (;;) {  // next sequence with work
         ++c.s;
-        if (c.s >= a.S) {  // cannot happen while the plan and this walk agree; never read past the inputs
+        if (c.s >= a.S) {  // past the last sequence: the position is now the total cost, nothing follows
           c.s = a.S - 1;
-          atomicOr(a.status, CUDA_LLM_ST_TIMEOUT);
-          c.tiles = 1 << 24;
+          c.tiles = 0;
           return;
         }
         load_seq(c);
         if (c.tiles > 0) return;
       }
     };
+    // seat on the first unit whose cost position is >= u_begin (a weight-2 unit that starts before
+    // the cut belongs to the previous CTA)
     UnitCursor ic;
     ic.s = (int)plan[1];
     load_seq(ic);
     {
-      const int local = (int)(u_begin - plan[2]);
-      ic.hg = local / ic.tiles;
-      ic.tile = local - ic.hg * ic.tiles;
-      ic.seg_first = plan[2] + (long long)ic.hg * ic.tiles;
+      const long long base = plan[2];
+      int local = (int)((u_begin - base + ic.w - 1) / ic.w);
+      const int n_seq = ic.tiles * a.n_hg;
+      if (local >= n_seq) {  // the cut fell into the last unit of this sequence: start at the next one
+        ic.pos = base + (long long)(n_seq - 1) * ic.w;
+        ic.hg = a.n_hg - 1;
+        ic.tile = ic.tiles - 1;
+        ic.seg_first = base + (long long)ic.hg * ic.tiles * ic.w;
+        advance(ic);
+      } else {
+        ic.hg = local / ic.tiles;
+        ic.tile = local - ic.hg * ic.tiles;
+        ic.pos = base + (long long)local * ic.w;
+        ic.seg_first = base + (long long)ic.hg * ic.tiles * ic.w;
+      }
     }
     UnitCursor pc = ic;
     const uint32_t ring = smem_base + kBtRingOff;
     int pf_done = 0;  // units whose block-table entries have been requested
     auto prefetch = [&]() {
       if (TM) return;  // contiguous K/V: no block table
-      if (pf_done < n_units) {
+      if (pc.pos < u_end) {
         const int tok0 = pc.tile * TOK_STAGE;
         const int np = min(PPS, (pc.ctx - tok0 + PAGE - 1) / PAGE);
         if (lane < np) {
@@ -326,11 +350,11 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           cp_async_4(ring + ((pf_done % kBtRing) * kMaxPagesPerStage + lane) * 4, src);
         }
         ++pf_done;
-        if (pf_done < n_units) advance(pc);
+        advance(pc);
       }
       cp_async_commit();
     };
-    if (!TM && n_units >= kBtAhead && pc.tile + kBtAhead <= pc.tiles) {
+    if (!TM && pc.pos + (long long)kBtAhead * pc.w <= u_end && pc.tile + kBtAhead <= pc.tiles) {
       // common start: the first kBtAhead units are consecutive tiles of one (sequence, head group),
       // so their table entries are fetched by the lanes in parallel instead of unit by unit
       for (int idx = lane; idx < kBtAhead * PPS; idx += 32) {
@@ -346,7 +370,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int j = 0; j < kBtAhead; ++j) cp_async_commit();
       pf_done = kBtAhead;
       pc.tile += kBtAhead - 1;
-      if (pf_done < n_units) advance(pc);
+      pc.pos += (long long)(kBtAhead - 1) * pc.w;
+      advance(pc);
     } else {
       for (int j = 0; j < kBtAhead; ++j) prefetch();
     }
@@ -357,19 +382,32 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     bool seg_direct = false, seg_fresh = true;
     bool ok = true;
     int issued = 0;
-    for (int it = 0; it < n_units; ++it) {
+    for (int it = 0;; ++it) {
       const int slot = it % NS;
       const uint32_t phase = (it / NS) & 1;
+      if (ic.pos >= u_end) {
+        // terminal stage: no bytes, tells the consumers that this CTA's range is done
+        if (it >= NS && !mbar_wait(empty_bar + 8 * slot, phase ^ 1)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          sts128(smem_base + kMetaOff + slot * (uint32_t)sizeof(StageMeta) + 16, FLAG_END, 0, 0, 0);
+          mbar_arrive_expect_tx(full_bar + 8 * slot, 0u);
+        }
+        break;
+      }
       cp_async_wait<kBtAhead - 1>();  // the group of unit `it` has landed
       __syncwarp();
       if (tracing && it == 0 && lane == 0) a.trace[blockIdx.x * 8 + 6] = globaltimer_ns();
       if (seg_fresh || ic.tile == 0) {
+        const long long seg_last = ic.seg_first + (long long)(ic.tiles - 1) * ic.w;  // its last unit
         if (small_units) {
           seg_cta_first = (int)((unsigned)ic.seg_first / (unsigned)per_cta);
-          seg_n_cta = (int)((unsigned)(ic.seg_first + ic.tiles - 1) / (unsigned)per_cta) - seg_cta_first + 1;
+          seg_n_cta = (int)((unsigned)seg_last / (unsigned)per_cta) - seg_cta_first + 1;
         } else {
           seg_cta_first = (int)(ic.seg_first / per_cta);
-          seg_n_cta = (int)((ic.seg_first + ic.tiles - 1) / per_cta) - seg_cta_first + 1;
+          seg_n_cta = (int)(seg_last / per_cta) - seg_cta_first + 1;
         }
         // direct output needs one warp per (head, row): not when two warps share the rows of a
         // short query (NT == 2 kernel, at most 8 live rows)
@@ -392,7 +430,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         }
       }
       const bool is_new = seg_fresh || (ic.tile == 0);
-      const bool is_last = (it == n_units - 1) || (ic.tile == ic.tiles - 1);
+      const bool is_last = (ic.pos + ic.w >= u_end) || (ic.tile == ic.tiles - 1);
       const uint32_t meta = smem_base + kMetaOff + slot * (uint32_t)sizeof(StageMeta);
       if (lane == 0) {
         const int flags = (is_new ? FLAG_NEW : 0) | (is_last ? FLAG_LAST : 0) | (seg_direct ? FLAG_DIRECT : 0);
@@ -448,7 +486,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       if (tracing && it == 0 && lane == 0) a.trace[blockIdx.x * 8 + 7] = globaltimer_ns();
       issued = it + 1;
       prefetch();  // table entries of unit it + kBtAhead
-      if (it + 1 < n_units) advance(ic);
+      advance(ic);
     }
     cp_async_wait<0>();
     if (!ok) {
@@ -518,7 +556,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   bool helper = false;
   int rb = 0;  // first query row of this warp
 
-  for (int it = 0; it < n_units; ++it) {
+  for (int it = 0;; ++it) {
     const int slot = it % NS;
     const uint32_t phase = (it / NS) & 1;
     if (!mbar_wait(full_bar + 8 * slot, phase)) {
@@ -530,6 +568,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     const uint4 m0 = lds128(meta);
     const uint4 m1 = lds128(meta + 16);
     const int hg = (int)m0.y, tok0 = (int)m0.z, ctx = (int)m0.w, flags = (int)m1.x;
+    if (flags & FLAG_END) {  // the producer has no more work for this CTA
+      if (tracing && warp == 0 && lane == 0) a.trace[blockIdx.x * 8 + 2] = globaltimer_ns();
+      break;
+    }
     const int mslot = (int)m1.y;
     const uint32_t sb = stage0 + slot * a.stage_bytes;
 
@@ -868,7 +910,6 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     // stage consumed: hand the slot back before the epilogue
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar + 8 * slot);
-    if (tracing && it == n_units - 1 && warp == 0 && lane == 0) a.trace[blockIdx.x * 8 + 2] = globaltimer_ns();
 
     if (flags & FLAG_LAST) {
       // ------------------------------------------------------------ epilogue of the segment

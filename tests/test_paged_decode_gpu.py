@@ -151,6 +151,24 @@ def test_q_len_causal(ops, mode, vfmt, group):
     assert (lse.cpu() - ref_lse).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("num_ctas", [1, 2, 3, 7, 33, 148])
+@pytest.mark.parametrize("seed", [21, 22])
+def test_mixed_rows_partition(ops, num_ctas, seed):
+    """A batch that mixes 4-row and 16-row queries: units of the 16-row sequences weigh twice in
+    the partition, cuts fall inside them, and every CTA count must give the same answer."""
+    W = _W()
+    g = torch.Generator().manual_seed(seed)
+    n = 14
+    lens = torch.randint(1, 700, (n,), generator=g).tolist()
+    qls = [4 if x else 1 for x in (torch.rand(n, generator=g) < 0.4).tolist()]
+    wl = W.build_workload("mixed", context_lens=lens, q_lens=qls, num_q_heads=8, num_kv_heads=2,
+                          head_dim=128, page_size=16, q_dtype=torch.bfloat16, v_format="fp4_e2m1",
+                          scale_mode="mx_e8m0", pool_factor=1.4, seed=seed)
+    ref = oracle_out(wl)
+    out = ops.run_workload(wl.to("cuda"), num_ctas=num_ctas, check_status=True)
+    assert_parity(out, ref, torch.bfloat16, f"mixed rows, {num_ctas} CTAs")
+
+
 def test_fp32_query_is_tight(ops):
     """fp32 Q/out (the reference's <float,float> instantiation) uses split operands."""
     W = _W()
