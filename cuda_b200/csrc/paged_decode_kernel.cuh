@@ -789,7 +789,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
 
       // ------------------------------------------------------------ O^T += V^T * P^T
       // P^T through an 8x8 transpose of the packed f16 accumulators.  k index <-> token of an
-      // m-tile: {4t, 4t+2} (a0/a1, b0) and {4t+1, 4t+3} (a2/a3, b1).  One plain ldmatrix.x4 brings
+      // m-tile: {4t, 4t+2} (a0/a1, b0) and {4t+1, 4t+3} (a2/a3, b1); for E4M3 V the pairs are
+      // regrouped below to {4t, 4t+1} and {4t+2, 4t+3}.  One plain ldmatrix.x4 brings
       // 32 rows of V (bytes 4t..4t+3 of row 8m+g per matrix m).
       uint32_t pb[MT][2];
       uint32_t pbl[PRECISE ? MT : 1][2];
@@ -804,6 +805,21 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             pbl[PRECISE ? mt : 0][hf] = movmatrix_trans(
                 pack_f16x2(pv[mt][2 * hf] - f16x2_lo(pk), pv[mt][2 * hf + 1] - f16x2_hi(pk)));
         }
+      if (!V4 && !KV16) {
+        // E4M3 V arrives as bytes of tokens 4t..4t+3 and is widened in adjacent pairs; regrouping P
+        // to {4t, 4t+1} / {4t+2, 4t+3} here (two byte shuffles) saves one shuffle per V register
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint32_t p0 = pb[mt][0], p1 = pb[mt][1];
+          pb[mt][0] = prmt(p0, p1, 0x5410);
+          pb[mt][1] = prmt(p0, p1, 0x7632);
+          if (PRECISE) {
+            const uint32_t q0 = pbl[PRECISE ? mt : 0][0], q1 = pbl[PRECISE ? mt : 0][1];
+            pbl[PRECISE ? mt : 0][0] = prmt(q0, q1, 0x5410);
+            pbl[PRECISE ? mt : 0][1] = prmt(q0, q1, 0x7632);
+          }
+        }
+      }
       uint32_t vmask[MT];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
@@ -864,8 +880,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             if (MX) {
               uint32_t e = lds32(sb + vs_mx[mt] + dp * PAGE);  // E8M0 of tokens 4t..4t+3, block dp
               if (tail) e = (e & vmask[mt]) | (0x7f7f7f7fu & ~vmask[mt]);
-              s02 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4240));  // tokens 4t, 4t+2
-              s13 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4341));  // tokens 4t+1, 4t+3
+              s02 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4140));  // tokens 4t, 4t+1
+              s13 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4342));  // tokens 4t+2, 4t+3
             }
             // a block scale multiplies P (two registers per 32 head_dim rows), not the V operand
             uint32_t b0 = pb[mt][0], b1 = pb[mt][1];
@@ -877,7 +893,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
 #pragma unroll
             for (int kk = 0; kk < 2; ++kk) {
               const int mo = 2 * dp + kk;
-              const uint32_t x0 = prmt(va[2 * kk], 0u, 0x3120), x1 = prmt(va[2 * kk + 1], 0u, 0x3120);
+              const uint32_t x0 = va[2 * kk], x1 = va[2 * kk + 1];  // bytes of tokens 4t..4t+3, rows g and g+8
               const uint32_t A0 = e4m3x2_to_f16x2_lo(x0), A1 = e4m3x2_to_f16x2_lo(x1);
               const uint32_t A2 = e4m3x2_to_f16x2_hi(x0), A3 = e4m3x2_to_f16x2_hi(x1);
               mma_f16(oacc[mo], A0, A1, A2, A3, b0, b1);
