@@ -382,9 +382,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     bool seg_direct = false, seg_fresh = true;
     bool ok = true;
     int issued = 0;
-    for (int it = 0;; ++it) {
-      const int slot = it % NS;
-      const uint32_t phase = (it / NS) & 1;
+    // ring slot and phase are stepped, not divided out: NS is a run-time value
+    int slot = 0;
+    uint32_t phase = 0;
+    for (int it = 0;; ++it, slot = (slot + 1 == NS) ? 0 : slot + 1, phase ^= (slot == 0) ? 1u : 0u) {
       if (ic.pos >= u_end) {
         // terminal stage: no bytes, tells the consumers that this CTA's range is done
         if (it >= NS && !mbar_wait(empty_bar + 8 * slot, phase ^ 1)) {
@@ -556,9 +557,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   bool helper = false;
   int rb = 0;  // first query row of this warp
 
-  for (int it = 0;; ++it) {
-    const int slot = it % NS;
-    const uint32_t phase = (it / NS) & 1;
+  int slot = 0;
+  uint32_t phase = 0;
+  for (int it = 0;; ++it, slot = (slot + 1 == NS) ? 0 : slot + 1, phase ^= (slot == 0) ? 1u : 0u) {
     if (!mbar_wait(full_bar + 8 * slot, phase)) {
       if (lane == 0) atomicOr(a.status, CUDA_LLM_ST_TIMEOUT);
       return;
@@ -823,8 +824,11 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       uint32_t vmask[MT];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const int kc = max(0, min(4, nv - 16 * mt - 4 * t));
-        vmask[mt] = kc >= 4 ? 0xffffffffu : ((1u << (8 * kc)) - 1u);
+        vmask[mt] = 0xffffffffu;
+        if (tail) {
+          const int kc = max(0, min(4, nv - 16 * mt - 4 * t));
+          vmask[mt] = kc >= 4 ? 0xffffffffu : ((1u << (8 * kc)) - 1u);
+        }
       }
       if (KV16) {
         // 16-bit V: registers 0,1 hold tokens 2t, 2t+1 (rows g, g+8), registers 2,3 tokens 2t+8, 2t+9;
