@@ -36,7 +36,7 @@ FALLBACK_HBM_GBS = 6650.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode-kernel launch,
 # from the ncu capture summarised in profiles/paged_decode_kernel_cfg2.md (traffic grows with the
 # bytes streamed, so the ratio carries over to the full-size launch)
-DRAM_TRAFFIC_PER_KV_BYTE = {"cfg2_llama8b_fp8_pertoken": 1.026}
+DRAM_TRAFFIC_PER_KV_BYTE = {"cfg2_llama8b_fp8_pertoken": 1.03}
 
 
 def measured_peak():
