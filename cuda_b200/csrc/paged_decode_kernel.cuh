@@ -183,6 +183,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   constexpr int SUB = (KV16 || NT == 1) ? 16 : 32;  // tokens per warp sub-tile
   constexpr int MT = SUB / 16;                   // m-tiles of S^T == k-tiles of PV per sub-tile
   constexpr float NEG_INF = -__builtin_huge_valf();
+  constexpr float kMaxFloor = -1.0e30f;  // running maximum before any live token
 
   extern __shared__ __align__(1024) uint8_t smem[];
   // layout: [0,64) full barriers, [64,128) empty barriers, [128,192) plan, [256, +8*128) stage
@@ -615,7 +616,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           qf[kt][hf] = pk;
           if (PRECISE) ql[PRECISE ? kt : 0][hf] = pack_f16x2(lo - f16x2_lo(pk), hi - f16x2_hi(pk));
         }
-      m_run[0] = m_run[1] = NEG_INF;
+      // a finite floor instead of -inf: max - max never becomes inf - inf, no special case below
+      m_run[0] = m_run[1] = kMaxFloor;
       l_run[0] = l_run[1] = 0.f;
 #pragma unroll
       for (int mt = 0; mt < KT; ++mt)
@@ -711,16 +713,16 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             v1 = (16 * mt + 2 * g + 1 < nv) ? v1 : 1.f;
           }
           v0 = fmaxf(v0, 1e-30f); v1 = fmaxf(v1, 1e-30f);
-          vlg[mt][0] = __log2f(v0); vlg[mt][1] = __log2f(v1);
-          vrc[mt][0] = __frcp_rn(v0); vrc[mt][1] = __frcp_rn(v1);
+          vlg[mt][0] = fast_log2(v0); vlg[mt][1] = fast_log2(v1);
+          vrc[mt][0] = fast_rcp(v0); vrc[mt][1] = fast_rcp(v1);
         } else if (MODE == MODE_PAGE_SCALE) {
           float kp = kscale_head, vl = 0.f, vr = 1.f;
           if (a.per_block) {
             const int bidx = (int)lds32(meta + 64 + 4 * ((ts * SUB + 16 * mt) / PAGE));
             kp = reinterpret_cast<const float*>(a.ks)[(size_t)bidx * a.Hkv + kvh];
             const float vp = fmaxf(reinterpret_cast<const float*>(a.vs)[(size_t)bidx * a.Hkv + kvh], 1e-30f);
-            vl = __log2f(vp);
-            vr = __frcp_rn(vp);
+            vl = fast_log2(vp);
+            vr = fast_rcp(vp);
           }
           ksc[mt][0] = ksc[mt][1] = kp;
           vlg[mt][0] = vlg[mt][1] = vl;
@@ -763,7 +765,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
       }
       const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-      const float mu0 = (mn0 == NEG_INF) ? 0.f : mn0, mu1 = (mn1 == NEG_INF) ? 0.f : mn1;
+      const float mu0 = mn0, mu1 = mn1;
       const float al0 = fast_exp2(m_run[0] - mu0), al1 = fast_exp2(m_run[1] - mu1);
       m_run[0] = mn0;
       m_run[1] = mn1;

@@ -174,6 +174,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float fast_log2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // E8M0 byte -> fp32 2^(e-127).  0 -> 2^-127 (fp32 subnormal), 255 -> NaN.
 __device__ __forceinline__ float e8m0_to_f32(uint32_t e) {
   uint32_t bits = (e == 0u) ? 0x00400000u : (e == 255u ? 0x7fc00000u : (e << 23));
