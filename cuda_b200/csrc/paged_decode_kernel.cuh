@@ -31,7 +31,8 @@
 //
 // Numerical notes.  E4M3 -> f16 and E2M1 -> f16 are exact.  Q is used in f16 (bf16 -> f16 is
 // exact for |q| in [2^-14, 65504]); an fp32 Q is split into an f16 high and low part when
-// PRECISE.  P is rounded to f16 (again hi+lo when PRECISE).  An E8M0 scale 2^e of an E4M3 V block
+// PRECISE.  E8M0 K scales are placed into the fp32 exponent field (byte 0 acts as 0, not 2^-127;
+// byte 255 as inf, not NaN).  P is rounded to f16 (again hi+lo when PRECISE).  An E8M0 scale 2^e of an E4M3 V block
 // multiplies P in f16 (exact up to e = 15; below about e = -10 the product loses bits to f16
 // subnormals); for packed E2M1 V the product V * 2^e is formed in f16 and is exact for e in
 // [-16, 8]; smaller exponents flush to zero, larger ones overflow to inf.
@@ -686,8 +687,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             if (PRECISE) mma_f16(acc, a0, a1, a2, a3, ql[PRECISE ? kt : 0][0], ql[PRECISE ? kt : 0][1]);
           }
           if (MX) {
-            const uint32_t e2 = lds16(sb + ks_mx[mt] + ks * PAGE);  // E8M0 of tokens 2g, 2g+1, block ks
-            const float s0 = e8m0_to_f32(e2 & 0xffu), s1 = e8m0_to_f32(e2 >> 8);
+            // E8M0 of tokens 2g, 2g+1, block ks, placed straight into the fp32 exponent field
+            // (byte 0 reads as 0 instead of 2^-127, byte 255 as inf instead of NaN)
+            const uint32_t e2 = lds16(sb + ks_mx[mt] + ks * PAGE);
+            const float s0 = __uint_as_float((e2 & 0xffu) << 23), s1 = __uint_as_float((e2 << 15) & 0x7f800000u);
             sacc[mt][0] = fmaf(tacc[0], s0, sacc[mt][0]);
             sacc[mt][1] = fmaf(tacc[1], s0, sacc[mt][1]);
             sacc[mt][2] = fmaf(tacc[2], s1, sacc[mt][2]);
