@@ -39,6 +39,7 @@ struct Layout {
   uint32_t k_page_stride, v_page_stride, ks_page_stride, vs_page_stride;
   uint32_t k_chunk, v_chunk, ks_chunk, vs_chunk;
   size_t smem_bytes;
+  uint32_t q_smem_off, q_smem_bytes;  // per-slot query area behind the stages (0: does not fit)
   // workspace
   size_t ws_table, ws_lse, ws_o, ws_total;
 };
@@ -59,7 +60,7 @@ static int sm_count_cached() {
 // Pure arithmetic (no device access when num_ctas > 0): shared-memory stage layout and
 // workspace carving for one problem shape.
 static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, int k_format, int v_format,
-                       int scale_mode, int num_ctas, Layout& L, bool token_major = false) {
+                       int scale_mode, int num_ctas, Layout& L, bool token_major = false, int q_elem_bytes = 2) {
   if (S < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return fail(CUDA_LLM_EINVAL, "num_q_heads must be a positive multiple of num_kv_heads");
   if (D != 64 && D != 128) return fail(CUDA_LLM_EINVAL, "Only head_dim 64 and 128 supported");
   if (page != 16 && page != 32 && page != 64) return fail(CUDA_LLM_EINVAL, "Only page_size 16, 32 and 64 supported");
@@ -110,6 +111,17 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   L.n_stages = ns;
   L.smem_bytes = stages_off + (size_t)ns * L.stage_bytes;
   if (L.smem_bytes < stages_off + kDecodeThreads * 8) L.smem_bytes = stages_off + kDecodeThreads * 8;
+  // query rows of one (sequence, head group), one area per ring slot, if shared memory is left
+  L.q_smem_off = L.q_smem_bytes = 0;
+  {
+    const size_t per_slot = align_up((size_t)max_q_len * HG * group * D * q_elem_bytes, 128);
+    const size_t off = align_up(L.smem_bytes, 128);
+    if (off + (size_t)ns * per_slot <= kSmemBudget) {
+      L.q_smem_off = (uint32_t)off;
+      L.q_smem_bytes = (uint32_t)per_slot;
+      L.smem_bytes = off + (size_t)ns * per_slot;
+    }
+  }
   if (num_ctas <= 0) num_ctas = sm_count_cached();
   if (num_ctas <= 0) return fail(CUDA_LLM_ECUDA, "cannot query the SM count");
   L.grid = num_ctas;
@@ -213,7 +225,8 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
 
   Layout L;
   int rc = make_layout(p->num_seqs, p->num_q_heads, p->num_kv_heads, p->head_dim, p->page_size,
-                       p->max_q_len, p->k_format, p->v_format, p->scale_mode, p->num_ctas, L);
+                       p->max_q_len, p->k_format, p->v_format, p->scale_mode, p->num_ctas, L, false,
+                       p->q_dtype == CUDA_LLM_F32 ? 4 : 2);
   if (rc != CUDA_LLM_OK) return rc;
   if (!p->workspace || p->workspace_bytes < L.ws_total)
     return fail(CUDA_LLM_EWORKSPACE, "workspace missing or smaller than cuda_llm_paged_decode_workspace_bytes()");
@@ -254,6 +267,10 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   a.helper_pairs = kv16 ? 0 : 1;
   a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
   a.n_stages = L.n_stages;
+  if (!((uintptr_t)p->query & 15)) {  // bulk copies need a 16-byte aligned source
+    a.q_smem_off = L.q_smem_off;
+    a.q_smem_bytes = L.q_smem_bytes;
+  }
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_MATH) a.debug |= 1;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_COPY) a.debug |= 2;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_SCALE_COPY) a.debug |= 16;
@@ -466,6 +483,10 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
     a.q_dtype = a.out_dtype = dtype;
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.n_stages = L.n_stages;
+    if (!((uintptr_t)q & 15)) {
+      a.q_smem_off = L.q_smem_off;
+      a.q_smem_bytes = L.q_smem_bytes;
+    }
     a.stage_bytes = L.stage_bytes; a.off_v = L.off_v; a.off_ks = L.off_ks; a.off_vs = L.off_vs;
     a.k_page_stride = L.k_page_stride; a.v_page_stride = L.v_page_stride;
     a.k_chunk = L.k_chunk; a.v_chunk = L.v_chunk;

@@ -49,6 +49,7 @@ constexpr int kMaxPagesPerStage = 16;
 constexpr uint32_t kSmemBudget = 232448;  // 227 KB opt-in maximum per CTA
 constexpr int kBtAhead = 8;               // block-table prefetch distance, in stages
 constexpr int kBtRing = 16;               // ring slots for prefetched block-table entries
+constexpr int kSegGap = 2;                // cost units charged for starting a (sequence, head group) inside a range
 
 enum : int {
   MODE_PAGE_SCALE = 0, MODE_TOKEN_SCALE = 1, MODE_MX8 = 2, MODE_MX8K_MX4V = 3,
@@ -86,6 +87,8 @@ struct DecodeArgs {
   int S, Hq, Hkv, group, max_blocks, num_blocks;
   int HG, SUBS, n_hg, rows_max, tok_stage;
   int q_dtype, out_dtype, per_block;
+  uint32_t q_smem_off;    // shared-memory offset of the per-slot query area (0: consumers read Q from global)
+  uint32_t q_smem_bytes;  // bytes of one slot's query area
   int fixed_ctx;     // context length of every sequence when `ctx` is null (contiguous K/V)
   int helper_pairs;  // 16-row kernels of the 8-bit modes pair two warps on a short query (two results per sub-tile)
   int debug;  // diagnostics: bit 0 = consumers skip the math, bit 1 = producer skips the copies,
@@ -229,7 +232,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     const int c = eff_ctx(a, s, PAGE);
     if (ql <= 0 || c <= 0) return 0;
     const int w = (WEIGHTED && a.group * ql > 8) ? 2 : 1;
-    return (long long)((c + TOK_STAGE - 1) / TOK_STAGE) * a.n_hg * w;
+    // every (sequence, head group) also costs kSegGap units up front: finishing one inside a range
+    // and starting the next (epilogue, partial rows, new query rows) was measured at 3-5 us, about two
+    // stages, and the CTA whose range holds two such starts otherwise finishes last
+    return ((long long)((c + TOK_STAGE - 1) / TOK_STAGE) * w + kSegGap) * a.n_hg;
   };
   long long my_units = 0;
   for (int s = s_lo; s < s_hi; ++s) my_units += seq_cost(s);
@@ -303,6 +309,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       if (c.pos >= u_end) return;  // end of this CTA's range: the cursor is not used again
       if (++c.tile < c.tiles) return;
       c.tile = 0;
+      c.pos += kSegGap;  // the gap in front of the next (sequence, head group)
+      if (c.pos >= u_end) return;
       c.seg_first = c.pos;
       if (++c.hg < a.n_hg) return;
       c.hg = 0;
@@ -323,20 +331,21 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     ic.s = (int)plan[1];
     load_seq(ic);
     {
+      // inside the sequence every head group spans kSegGap + tiles * w cost units, its units start
+      // behind the gap
       const long long base = plan[2];
-      int local = (int)((u_begin - base + ic.w - 1) / ic.w);
-      const int n_seq = ic.tiles * a.n_hg;
-      if (local >= n_seq) {  // the cut fell into the last unit of this sequence: start at the next one
-        ic.pos = base + (long long)(n_seq - 1) * ic.w;
-        ic.hg = a.n_hg - 1;
+      const int stride = kSegGap + ic.tiles * ic.w;
+      const int o = (int)(u_begin - base);
+      ic.hg = o / stride;
+      const int rem = o - ic.hg * stride - kSegGap;           // offset behind the gap (negative: inside it)
+      ic.tile = rem <= 0 ? 0 : (rem + ic.w - 1) / ic.w;
+      ic.seg_first = base + (long long)ic.hg * stride + kSegGap;
+      if (ic.tile >= ic.tiles) {  // the cut fell into the last unit of this head group: start at the next one
         ic.tile = ic.tiles - 1;
-        ic.seg_first = base + (long long)ic.hg * ic.tiles * ic.w;
+        ic.pos = ic.seg_first + (long long)ic.tile * ic.w;
         advance(ic);
       } else {
-        ic.hg = local / ic.tiles;
-        ic.tile = local - ic.hg * ic.tiles;
-        ic.pos = base + (long long)local * ic.w;
-        ic.seg_first = base + (long long)ic.hg * ic.tiles * ic.w;
+        ic.pos = ic.seg_first + (long long)ic.tile * ic.w;
       }
     }
     UnitCursor pc = ic;
@@ -450,11 +459,15 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       seg_fresh = false;
       const uint32_t fb = full_bar + 8 * slot;
       const bool no_copy = (a.debug & 2) != 0;  // diagnostics: math on whatever shared memory holds
+      // the query rows of a new (sequence, head group) travel with its first stage, so that the
+      // consumers find them in shared memory instead of waiting for a global load with the ring full
+      const uint32_t q_row_bytes = (uint32_t)(a.HG * a.group * D) * (a.q_dtype == CUDA_LLM_F32 ? 4u : 2u);
+      const uint32_t q_bytes = (a.q_smem_bytes != 0 && is_new && !no_copy) ? (uint32_t)ic.qlen * q_row_bytes : 0u;
       if (TM) {
         // one copy each for the K and the V rows of the live tokens of this (batch, head) tile
         if (lane == 0) {
           const uint32_t bytes = (uint32_t)min(TOK_STAGE, ic.ctx - tok0) * (D * 2);
-          mbar_arrive_expect_tx(fb, no_copy ? 0u : 2u * bytes);
+          mbar_arrive_expect_tx(fb, no_copy ? 0u : 2u * bytes + q_bytes);
           if (!no_copy) {
             const uint32_t sb = stage0 + slot * a.stage_bytes;
             const uint64_t off = (((uint64_t)ic.s * a.Hkv + ic.hg) * a.fixed_ctx + tok0) * (D * 2);
@@ -466,9 +479,15 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       } else if (lane == 0) {
         uint32_t bytes = (uint32_t)np * (a.k_chunk + a.v_chunk);
         if (NTYPES == 4 && !(a.debug & 16)) bytes += (uint32_t)np * (a.ks_chunk + a.vs_chunk);
-        mbar_arrive_expect_tx(fb, no_copy ? 0u : bytes);
+        mbar_arrive_expect_tx(fb, no_copy ? 0u : bytes + q_bytes);
       }
       __syncwarp();
+      if (q_bytes != 0 && lane < ic.qlen) {  // lane j copies the rows of query token j (contiguous over the heads of the group)
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(a.q) +
+                             ((size_t)(ic.qbase + lane) * a.Hq + (size_t)ic.hg * a.HG * a.group) * D *
+                                 (a.q_dtype == CUDA_LLM_F32 ? 4 : 2);
+        bulk_g2s(smem_base + a.q_smem_off + slot * a.q_smem_bytes + lane * q_row_bytes, src, q_row_bytes, fb);
+      }
       if (!TM && !no_copy) {
         const uint32_t sb = stage0 + slot * a.stage_bytes;
         // lane pi issues the copies of page pi
@@ -600,7 +619,19 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           // token-major K: the thread's 16-byte chunk (t + 4*(kt/2)) holds the columns of two k-tiles
           const int d = TM ? 8 * (t + 4 * (kt >> 1)) + 4 * (kt & 1) + 2 * hf : 16 * kt + 8 * hf + 2 * t;
           float lo = 0.f, hi = 0.f;
-          if (row_live) {
+          if (row_live && a.q_smem_bytes != 0) {
+            // row (jq, h, iq) of this slot's query area
+            const uint32_t el = (uint32_t)((jq * a.HG + h) * a.group + iq) * D + d;
+            const uint32_t qa = smem_base + a.q_smem_off + slot * a.q_smem_bytes;
+            if (a.q_dtype == CUDA_LLM_F32) {
+              const uint2 v = lds64(qa + el * 4);
+              lo = __uint_as_float(v.x); hi = __uint_as_float(v.y);
+            } else {
+              const uint32_t v = lds32(qa + el * 2);
+              if (a.q_dtype == CUDA_LLM_F16) { lo = f16x2_lo(v); hi = f16x2_hi(v); }
+              else { lo = __uint_as_float(v << 16); hi = __uint_as_float(v & 0xffff0000u); }
+            }
+          } else if (row_live) {
             if (a.q_dtype == CUDA_LLM_F32) {
               const float2 v = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(a.q) + base + d);
               lo = v.x; hi = v.y;
