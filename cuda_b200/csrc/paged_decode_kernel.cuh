@@ -1006,27 +1006,18 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       // value; a per-head V scale multiplies once at the end
       float unit = V4 ? (float)(1 << (14 - kE2M1ScaleShift)) : 1.f;
       if (MODE == MODE_PAGE_SCALE && !a.per_block) unit *= vscale_head;
-      const float inv0 = (l0 > 0.f) ? unit / l0 : 0.f, inv1 = (l1 > 0.f) ? unit / l1 : 0.f;
-      const float lse0 = (l0 > 0.f) ? m_run[0] + log2f(l0) : NEG_INF;
-      const float lse1 = (l1 > 0.f) ? m_run[1] + log2f(l1) : NEG_INF;
+      // (approximate reciprocal and logarithm: relative error below 2^-22, and far less code than the
+      // IEEE sequences; this path is cold in the instruction cache every time it runs)
+      const float inv0 = (l0 > 0.f) ? unit * fast_rcp(l0) : 0.f, inv1 = (l1 > 0.f) ? unit * fast_rcp(l1) : 0.f;
+      const float lse0 = (l0 > 0.f) ? m_run[0] + fast_log2(l0) : NEG_INF;
+      const float lse1 = (l1 > 0.f) ? m_run[1] + fast_log2(l1) : NEG_INF;
+      if (!direct) {
+        // the usual case, kept together: normalised partial rows for the split merge
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int r = rb + 2 * t + cc;
-        if (r >= R) continue;
-        const float inv = cc ? inv1 : inv0;
-        const float lse2 = cc ? lse1 : lse0;
-        const int j = r / a.group, i = r - j * a.group;
-        if (direct) {
-          const size_t row = (size_t)(qbase + j) * a.Hq + (size_t)kvh * a.group + i;
-#pragma unroll
-          for (int mt = 0; mt < KT; ++mt) {
-            const int d0 = TM ? 8 * ((g >> 1) + 4 * (mt >> 1)) + 4 * (mt & 1) + (g & 1) : V4 ? mt * 16 + 2 * g : mt * 16 + g;
-            const int d1 = TM ? d0 + 2 : V4 ? d0 + 1 : d0 + 8;
-            store_out_elem(a.out, a.out_dtype, row * D + d0, oacc[mt][cc] * inv);
-            store_out_elem(a.out, a.out_dtype, row * D + d1, oacc[mt][2 + cc] * inv);
-          }
-          if (a.lse && g == 0) a.lse[row] = lse2 * 0.69314718055994531f;
-        } else {
+        for (int cc = 0; cc < 2; ++cc) {
+          const int r = rb + 2 * t + cc;
+          if (r >= R) continue;
+          const float inv = cc ? inv1 : inv0;
           // a helper pair stores its second result in the unused upper rows
           const size_t prow = (((size_t)mslot * a.SUBS + psub) * a.HG + h) * a.rows_max + r + (helper ? nt_w * 8 : 0);
           float* po = a.part_o + prow * D;
@@ -1037,7 +1028,24 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             po[d0] = oacc[mt][cc] * inv;
             po[d1] = oacc[mt][2 + cc] * inv;
           }
-          if (g == 0) a.part_lse[prow] = lse2;
+          if (g == 0) a.part_lse[prow] = cc ? lse1 : lse0;
+        }
+      } else {
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int r = rb + 2 * t + cc;
+          if (r >= R) continue;
+          const float inv = cc ? inv1 : inv0;
+          const int j = r / a.group, i = r - j * a.group;
+          const size_t row = (size_t)(qbase + j) * a.Hq + (size_t)kvh * a.group + i;
+#pragma unroll
+          for (int mt = 0; mt < KT; ++mt) {
+            const int d0 = TM ? 8 * ((g >> 1) + 4 * (mt >> 1)) + 4 * (mt & 1) + (g & 1) : V4 ? mt * 16 + 2 * g : mt * 16 + g;
+            const int d1 = TM ? d0 + 2 : V4 ? d0 + 1 : d0 + 8;
+            store_out_elem(a.out, a.out_dtype, row * D + d0, oacc[mt][cc] * inv);
+            store_out_elem(a.out, a.out_dtype, row * D + d1, oacc[mt][2 + cc] * inv);
+          }
+          if (a.lse && g == 0) a.lse[row] = (cc ? lse1 : lse0) * 0.69314718055994531f;
         }
       }
     }
