@@ -613,19 +613,21 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       const int iq = row_live ? r - jq * a.group : 0;
       const size_t base = ((size_t)(qbase + jq) * a.Hq + (size_t)kvh * a.group + iq) * D;
       // Common case, kept small because this code runs once per (sequence, head group) and is cold
-      // in the instruction cache every time: 16-bit query rows already in this slot's shared-memory
-      // area, one 32-bit load and a branch-free conversion per fragment register.
-      const bool q_fast = !PRECISE && a.q_smem_bytes != 0 && a.q_dtype != CUDA_LLM_F32;
+      // in the instruction cache every time: 16-bit query rows, from this slot's shared-memory area
+      // when there is one, one 32-bit load and a branch-free conversion per fragment register.
+      const bool q_fast = !PRECISE && a.q_dtype != CUDA_LLM_F32;
       if (q_fast) {
+        const bool q_in_smem = a.q_smem_bytes != 0;
         const uint32_t qrow = smem_base + a.q_smem_off + slot * a.q_smem_bytes +
                               (uint32_t)((jq * a.HG + h) * a.group + iq) * (D * 2);
+        const uint32_t* qglob = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(a.q) + base);
         const bool src_f16 = (a.q_dtype == CUDA_LLM_F16);
 #pragma unroll
         for (int kt = 0; kt < KT; ++kt)
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
             const int d = TM ? 8 * (t + 4 * (kt >> 1)) + 4 * (kt & 1) + 2 * hf : 16 * kt + 8 * hf + 2 * t;
-            const uint32_t w = lds32(qrow + d * 2);
+            const uint32_t w = q_in_smem ? lds32(qrow + d * 2) : (row_live ? qglob[d >> 1] : 0u);
             uint32_t pk;
             if (BF) {  // bf16 operands: bf16 rows pass through, f16 rows are re-rounded
               const uint32_t conv = pack_bf16x2(f16x2_lo(w), f16x2_hi(w));
