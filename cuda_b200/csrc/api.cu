@@ -270,6 +270,7 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   if (!((uintptr_t)p->query & 15)) {  // bulk copies need a 16-byte aligned source
     a.q_smem_off = L.q_smem_off;
     a.q_smem_bytes = L.q_smem_bytes;
+    a.q_smem_tokens = p->max_q_len < 1 ? 1 : p->max_q_len;
   }
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_MATH) a.debug |= 1;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_COPY) a.debug |= 2;
@@ -486,6 +487,7 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
     if (!((uintptr_t)q & 15)) {
       a.q_smem_off = L.q_smem_off;
       a.q_smem_bytes = L.q_smem_bytes;
+      a.q_smem_tokens = 1;
     }
     a.stage_bytes = L.stage_bytes; a.off_v = L.off_v; a.off_ks = L.off_ks; a.off_vs = L.off_vs;
     a.k_page_stride = L.k_page_stride; a.v_page_stride = L.v_page_stride;

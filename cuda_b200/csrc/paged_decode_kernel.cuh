@@ -57,7 +57,7 @@ enum : int {
   MODE_KV_F16_TM = 6, MODE_KV_BF16_TM = 7  // unquantised 16-bit contiguous K/V [batch, heads, seq, head_dim]
 };
 
-enum : int { FLAG_NEW = 1, FLAG_LAST = 2, FLAG_DIRECT = 4, FLAG_END = 8 };
+enum : int { FLAG_NEW = 1, FLAG_LAST = 2, FLAG_DIRECT = 4, FLAG_END = 8, FLAG_QSMEM = 16 };
 
 struct StageMeta {  // 32 ints
   int s, hg, tok0, ctx, flags, slot, qbase, qlen;
@@ -89,6 +89,7 @@ struct DecodeArgs {
   int q_dtype, out_dtype, per_block;
   uint32_t q_smem_off;    // shared-memory offset of the per-slot query area (0: consumers read Q from global)
   uint32_t q_smem_bytes;  // bytes of one slot's query area
+  int q_smem_tokens;      // query tokens per sequence the area was sized for
   int fixed_ctx;     // context length of every sequence when `ctx` is null (contiguous K/V)
   int helper_pairs;  // 16-row kernels of the 8-bit modes pair two warps on a short query (two results per sub-tile)
   int debug;  // diagnostics: bit 0 = consumers skip the math, bit 1 = producer skips the copies,
@@ -444,8 +445,11 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       const bool is_new = seg_fresh || (ic.tile == 0);
       const bool is_last = (ic.pos + ic.w >= u_end) || (ic.tile == ic.tiles - 1);
       const uint32_t meta = smem_base + kMetaOff + slot * (uint32_t)sizeof(StageMeta);
+      // (a sequence with more query tokens than the query area was sized for keeps the global path)
+      const bool q_to_smem = a.q_smem_bytes != 0 && is_new && ic.qlen <= a.q_smem_tokens;
       if (lane == 0) {
-        const int flags = (is_new ? FLAG_NEW : 0) | (is_last ? FLAG_LAST : 0) | (seg_direct ? FLAG_DIRECT : 0);
+        const int flags = (is_new ? FLAG_NEW : 0) | (is_last ? FLAG_LAST : 0) | (seg_direct ? FLAG_DIRECT : 0) |
+                          (q_to_smem ? FLAG_QSMEM : 0);
         sts128(meta, ic.s, ic.hg, tok0, ic.ctx);
         sts128(meta + 16, flags, ic.s * a.n_hg + ic.hg + vb, ic.qbase, ic.qlen);
         if (ic.tile == 0) {
@@ -462,7 +466,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       // the query rows of a new (sequence, head group) travel with its first stage, so that the
       // consumers find them in shared memory instead of waiting for a global load with the ring full
       const uint32_t q_row_bytes = (uint32_t)(a.HG * a.group * D) * (a.q_dtype == CUDA_LLM_F32 ? 4u : 2u);
-      const uint32_t q_bytes = (a.q_smem_bytes != 0 && is_new && !no_copy) ? (uint32_t)ic.qlen * q_row_bytes : 0u;
+      const uint32_t q_bytes = (q_to_smem && !no_copy) ? (uint32_t)ic.qlen * q_row_bytes : 0u;
       if (TM) {
         // one copy each for the K and the V rows of the live tokens of this (batch, head) tile
         if (lane == 0) {
@@ -617,7 +621,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       // when there is one, one 32-bit load and a branch-free conversion per fragment register.
       const bool q_fast = !PRECISE && a.q_dtype != CUDA_LLM_F32;
       if (q_fast) {
-        const bool q_in_smem = a.q_smem_bytes != 0;
+        const bool q_in_smem = (flags & FLAG_QSMEM) != 0;
         const uint32_t qrow = smem_base + a.q_smem_off + slot * a.q_smem_bytes +
                               (uint32_t)((jq * a.HG + h) * a.group + iq) * (D * 2);
         const uint32_t* qglob = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(a.q) + base);
@@ -647,7 +651,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           // token-major K: the thread's 16-byte chunk (t + 4*(kt/2)) holds the columns of two k-tiles
           const int d = TM ? 8 * (t + 4 * (kt >> 1)) + 4 * (kt & 1) + 2 * hf : 16 * kt + 8 * hf + 2 * t;
           float lo = 0.f, hi = 0.f;
-          if (row_live && a.q_smem_bytes != 0) {
+          if (row_live && (flags & FLAG_QSMEM)) {
             // row (jq, h, iq) of this slot's query area
             const uint32_t el = (uint32_t)((jq * a.HG + h) * a.group + iq) * D + d;
             const uint32_t qa = smem_base + a.q_smem_off + slot * a.q_smem_bytes;

@@ -169,6 +169,21 @@ def test_mixed_rows_partition(ops, num_ctas, seed):
     assert_parity(out, ref, torch.bfloat16, f"mixed rows, {num_ctas} CTAs")
 
 
+def test_query_longer_than_declared_still_fits_the_rows(ops):
+    """max_q_len sizes the shared-memory query area; a sequence with more query tokens than declared
+    that still fits the 8 rows of the kernel must take the global-memory path, not overrun the area."""
+    W = _W()
+    wl = W.build_workload("qlen2", context_lens=[300, 40, 1000, 17], q_lens=[2, 1, 2, 2], num_q_heads=8,
+                          num_kv_heads=2, head_dim=128, page_size=16, q_dtype=torch.bfloat16,
+                          scale_mode="per_token", pool_factor=1.3, seed=31)
+    ref = oracle_out(wl)
+    g = wl.to("cuda")
+    out = ops.fp8_paged_attention_forward(g.query, g.key_cache, g.value_cache, g.k_scale, g.v_scale, g.block_tables,
+                                          g.context_lens, g.softmax_scale, cu_q_lens=g.cu_q_lens, max_q_len=1,
+                                          check_status=True)
+    assert_parity(out, ref, torch.bfloat16, "q_len 2 with max_q_len 1")
+
+
 def test_fp32_query_is_tight(ops):
     """fp32 Q/out (the reference's <float,float> instantiation) uses split operands."""
     W = _W()
