@@ -16,6 +16,7 @@ F32, F16, BF16 = 0, 1, 2
 KV_FP8_E4M3, KV_FP4_E2M1, KV_INT8, KV_F16, KV_BF16 = 0, 1, 2, 3, 4
 SCALE_PER_HEAD, SCALE_PER_BLOCK, SCALE_PER_TOKEN, SCALE_MX_E8M0 = 0, 1, 2, 3
 FLAG_SKIP_MERGE = 1
+FLAG_STABLE_METADATA = 64   # lengths / offsets / block tables are not written by the kernel in front of the call
 
 
 class PagedDecodeParams(C.Structure):

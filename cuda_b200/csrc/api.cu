@@ -272,6 +272,7 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
     a.q_smem_bytes = L.q_smem_bytes;
     a.q_smem_tokens = p->max_q_len < 1 ? 1 : p->max_q_len;
   }
+  a.early_plan = (p->flags & CUDA_LLM_FLAG_STABLE_METADATA) ? 1 : 0;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_MATH) a.debug |= 1;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_COPY) a.debug |= 2;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_SCALE_COPY) a.debug |= 16;

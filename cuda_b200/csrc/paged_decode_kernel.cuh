@@ -90,6 +90,7 @@ struct DecodeArgs {
   uint32_t q_smem_off;    // shared-memory offset of the per-slot query area (0: consumers read Q from global)
   uint32_t q_smem_bytes;  // bytes of one slot's query area
   int q_smem_tokens;      // query tokens per sequence the area was sized for
+  int early_plan;         // plan and first table prefetch may run before the previous kernel has finished
   int fixed_ctx;     // context length of every sequence when `ctx` is null (contiguous K/V)
   int helper_pairs;  // 16-row kernels of the 8-bit modes pair two warps on a short query (two results per sub-tile)
   int debug;  // diagnostics: bit 0 = consumers skip the math, bit 1 = producer skips the copies,
@@ -207,9 +208,12 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   const int TOK_STAGE = a.tok_stage;
 
   // Launched as a programmatic dependent: nothing a previous kernel may still be writing (query,
-  // tables, the workspace the previous merge reads) is touched before this wait.  Our own dependent,
-  // the split merge, may be scheduled from here on.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // K/V, the workspace the previous merge reads) is touched before griddepcontrol.wait.  Lengths,
+  // query offsets and block tables are read before it only when the caller has promised that the
+  // kernel in front of this one does not write them (early_plan): the plan and the first table
+  // prefetch then overlap that kernel's tail.  Our own dependent, the split merge, may be
+  // scheduled from here on.
+  if (!a.early_plan) asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;");
   const bool tracing = (a.debug & 4) && a.trace != nullptr;
   if (tracing && threadIdx.x == 0) a.trace[blockIdx.x * 8 + 0] = globaltimer_ns();
@@ -388,6 +392,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       for (int j = 0; j < kBtAhead; ++j) prefetch();
     }
     if (tracing && lane == 0) a.trace[blockIdx.x * 8 + 5] = globaltimer_ns();
+    if (a.early_plan) asm volatile("griddepcontrol.wait;" ::: "memory");  // K/V, Q and the workspace from here on
 
     // per-segment constants of the issue cursor
     int seg_cta_first = 0, seg_n_cta = 1;
@@ -525,6 +530,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   }
 
   // ================================================================= consumer warps
+  if (a.early_plan) asm volatile("griddepcontrol.wait;" ::: "memory");  // before any store to the workspace or out
   const int g = lane >> 2, t = lane & 3;
   // 16-bit cache: a stage holds 128 (token, head) pairs, half of the 8-bit stage.  With up to 8
   // query rows the two groups of 8 warps take alternate stages (`par`); with 9..16 rows every

@@ -41,6 +41,14 @@ extern "C" {
 #define CUDA_LLM_FLAG_SKIP_MERGE 1 /* launch the attention kernel only (profiling: sequences
                                       that were split across CTAs are left unmerged)         */
 
+#define CUDA_LLM_FLAG_STABLE_METADATA 64 /* promise: the kernel immediately in front of this call on the
+                                            stream does not write context_lens, cu_q_lens or
+                                            block_tables (they were prepared earlier, e.g. once per
+                                            model step for all layers).  The decode kernel is launched
+                                            as a programmatic dependent and then plans its ranges and
+                                            prefetches its first table entries while that kernel is
+                                            still finishing; query, K/V and the workspace are not
+                                            touched before it has finished either way. */
 #define CUDA_LLM_FLAG_DIAG_NO_MATH 2 /* diagnostics: stream the pages but skip the attention math
                                         (output is meaningless; measures the copy pipeline)   */
 #define CUDA_LLM_FLAG_DIAG_NO_COPY 4 /* diagnostics: do the attention math on stale shared memory,

@@ -184,6 +184,24 @@ def test_query_longer_than_declared_still_fits_the_rows(ops):
     assert_parity(out, ref, torch.bfloat16, "q_len 2 with max_q_len 1")
 
 
+def test_stable_metadata_flag_back_to_back(ops):
+    """With CUDA_LLM_FLAG_STABLE_METADATA the kernel plans before the previous kernel on the stream
+    has finished; calls issued back to back on two workloads must still be exact copies of the
+    results without the flag."""
+    W = _W()
+    a = W.make_config(2, "cuda", batch=8, ctx_scale=1 / 8, seed=41)
+    b = W.make_config(3, "cuda", batch=6, ctx_scale=1 / 16, seed=42)
+    ref_a, ref_b = ops.run_workload(a), ops.run_workload(b)
+    outs = []
+    for i in range(12):
+        wl = a if i % 2 == 0 else b
+        outs.append(ops.run_workload(wl, flags=ops.L.FLAG_STABLE_METADATA, out=torch.empty_like(wl.query)))
+    torch.cuda.synchronize()
+    for i, o in enumerate(outs):
+        assert torch.equal(o, ref_a if i % 2 == 0 else ref_b), f"call {i}"
+    assert ops.decode_status(ops.get_workspace(torch.device("cuda", torch.cuda.current_device()), 1)) == 0
+
+
 def test_fp32_query_is_tight(ops):
     """fp32 Q/out (the reference's <float,float> instantiation) uses split operands."""
     W = _W()
