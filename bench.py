@@ -119,7 +119,11 @@ def cpu_reference_run(wl_cpu, budget_s: float, max_seqs=None):
     cu = list(range(S + 1)) if wl_cpu.cu_q_lens is None else wl_cpu.cu_q_lens.tolist()
     t0 = time.perf_counter()
     done, nbytes, qtok = 0, 0, 0
-    for s in range(S):
+    # whole passes over the batch until about two thirds of the budget is used (at least one pass,
+    # cut short inside a pass when the budget runs out)
+    for s in (i % S for i in range(S * 10000)):
+        if s == 0 and done >= S and time.perf_counter() - t0 > 0.66 * budget_s:
+            break
         sub = O.PagedKV(kv.key_cache, kv.value_cache, kv.block_tables[s:s + 1], kv.context_lens[s:s + 1],
                         kv.page_size, kv.head_dim, kv.k_format, kv.v_format, kv.k_scale_mode,
                         kv.v_scale_mode, kv.k_scale, kv.v_scale)
@@ -237,7 +241,7 @@ def main():
             "ms_per_step": tot_t / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3->f32", "data": "synthetic",
             "tokens_per_s": tot_q / tot_t,
-            "config": {"workload": wl.name, "sample": f"first {n // max(1, args.steps)} of {wl.num_seqs} sequences per step",
+            "config": {"workload": wl.name, "sample": f"{n // max(1, args.steps)} sequence passes per step over the batch of {wl.num_seqs}",
                        "heads": f"{wl.num_q_heads}q/{wl.num_kv_heads}kv",
                        "head_dim": wl.head_dim, "page_size": wl.page_size},
             "cpu_baseline": {"value": val, "unit": "TB/s", "cores": torch.get_num_threads(), "kind": "port",
@@ -487,7 +491,7 @@ def main():
         t, b, q, n = cpu_reference_run(wl.to("cpu"), args.cpu_budget_s)
         line["cpu_baseline"] = {"value": b / t / 1e12, "unit": "TB/s", "cores": torch.get_num_threads(),
                                 "kind": "port", "tokens_per_s": q / t,
-                                "sample": f"first {n} of {wl.num_seqs} sequences of the same batch, {t:.1f} s"}
+                                "sample": f"{n} sequence passes over the same batch of {wl.num_seqs} ({n / wl.num_seqs:.1f} batches), {t:.1f} s"}
     print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
