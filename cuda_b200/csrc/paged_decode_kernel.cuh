@@ -24,18 +24,17 @@
 //    accumulate).  Tokens sit on the M side (always a full 16-row tile); the query rows (GQA
 //    group x q_len) sit on the 8-wide N side.  E4M3 / E2M1 bytes are widened to f16 in
 //    registers (exact), fp32 per-token scales are applied to the fp32 logits and folded into P,
-//    E8M0 block scales are applied to the fp32 partial logits (K), to P (E4M3 V) or to the f16
-//    V operand (packed E2M1 V).
+//    E8M0 block scales are applied to the fp32 partial logits (K) or to P (V).
 //  * Online softmax state (m, l) per query row lives in registers; every warp writes its
 //    result normalised, with a base-2 log-sum-exp, and merge_splits_kernel combines them.
 //
 // Numerical notes.  E4M3 -> f16 and E2M1 -> f16 are exact.  Q is used in f16 (bf16 -> f16 is
 // exact for |q| in [2^-14, 65504]); an fp32 Q is split into an f16 high and low part when
 // PRECISE.  E8M0 K scales are placed into the fp32 exponent field (byte 0 acts as 0, not 2^-127;
-// byte 255 as inf, not NaN).  P is rounded to f16 (again hi+lo when PRECISE).  An E8M0 scale 2^e of an E4M3 V block
-// multiplies P in f16 (exact up to e = 15; below about e = -10 the product loses bits to f16
-// subnormals); for packed E2M1 V the product V * 2^e is formed in f16 and is exact for e in
-// [-16, 8]; smaller exponents flush to zero, larger ones overflow to inf.
+// byte 255 as inf, not NaN).  P is rounded to f16 (again hi+lo when PRECISE).  An E8M0 scale 2^e of a
+// V block multiplies P in f16 (E4M3 V: exact up to e = 15; packed E2M1 V: the codes enter the
+// tensor core as placed, at 2^-14 of their value, and the scale carries 2^7, exact up to e = 8);
+// below about e = -10 the product loses bits to f16 subnormals, larger exponents overflow to inf.
 #pragma once
 #include "sm100_primitives.cuh"
 #include "cuda_llm_b200.h"
@@ -987,13 +986,14 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
               if (tail) e = (e & vmask[mt]) | (0x7f7f7f7fu & ~vmask[mt]);
               const uint32_t s02 = e8m0_pair_to_f16x2<kE2M1ScaleShift>(prmt(e, 0u, 0x4240));
               const uint32_t s13 = e8m0_pair_to_f16x2<kE2M1ScaleShift>(prmt(e, 0u, 0x4341));
+              // the block scale multiplies P; the codes go to the tensor core as placed (value * 2^-14)
+              const uint32_t b0 = hmul2(pb[mt][0], s02), b1 = hmul2(pb[mt][1], s13);
 #pragma unroll
               for (int mm = 0; mm < 2; ++mm) {
                 const int m = 2 * bb + mm, mo = 4 * dp + m;
                 const uint32_t ex = e2m1_lo_nibbles_to_f16_hi_bytes(va[m]), ox = e2m1_hi_nibbles_to_f16_hi_bytes(va[m]);
-                const uint32_t A0 = hmul2(prmt(ex, 0u, 0x2404), s02), A1 = hmul2(prmt(ox, 0u, 0x2404), s02);
-                const uint32_t A2 = hmul2(prmt(ex, 0u, 0x3414), s13), A3 = hmul2(prmt(ox, 0u, 0x3414), s13);
-                mma_f16(oacc[mo], A0, A1, A2, A3, pb[mt][0], pb[mt][1]);
+                mma_f16(oacc[mo], prmt(ex, 0u, 0x2404), prmt(ox, 0u, 0x2404), prmt(ex, 0u, 0x3414), prmt(ox, 0u, 0x3414),
+                        b0, b1);
               }
             }
           }
