@@ -385,3 +385,28 @@ def test_reference_cxx_dispatcher_paged_and_decode(ops, golden):
     fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 2, 4, 500, 128, 1.0 / 128 ** 0.5, st)
     torch.cuda.synchronize()
     assert torch.allclose(out.cpu(), O.ref_flash_decode(q.cpu(), k.cpu(), v.cpu()), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("hkv,q4,num_ctas", [(8, False, 148), (16, False, 37), (8, True, 148), (16, True, 5)])
+def test_segment_table_matches_host_plan(ops, hkv, q4, num_ctas):
+    """The (first CTA, number of CTAs) the kernel records per (sequence, head group) is exactly what
+    the host restatement of the plan predicts: integer parity of the range partition."""
+    from cuda_b200 import partition as P
+    W = _W()
+    g = torch.Generator().manual_seed(51)
+    n = 24
+    lens = torch.randint(1, 3000, (n,), generator=g).tolist()
+    qls = [4 if (q4 and x) else 1 for x in (torch.rand(n, generator=g) < 0.4).tolist()]
+    wl = W.build_workload("plan", context_lens=lens, q_lens=qls, num_q_heads=hkv * 4, num_kv_heads=hkv,
+                          head_dim=128, page_size=16, q_dtype=torch.bfloat16, scale_mode="per_token",
+                          pool_factor=1.1, seed=52).to("cuda")
+    need = ops.L.load().cuda_llm_paged_decode_workspace_bytes(n, hkv * 4, hkv, 128, 16, wl.max_q_len, num_ctas)
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    ops.run_workload(wl, workspace=ws, num_ctas=num_ctas, check_status=True)
+    n_hg = hkv // 8
+    table = ws[256:256 + n * n_hg * 16].view(torch.int32).view(n * n_hg, 4).cpu()
+    _, _, _, segs = P.plan(lens, qls, group=4, n_head_groups=n_hg, tok_stage=32, num_ctas=num_ctas,
+                           weighted=(wl.max_q_len * 4 > 8))
+    for (s, hg), (first, cnt) in segs.items():
+        row = table[s * n_hg + hg]
+        assert (int(row[0]), int(row[1])) == (first, cnt), (s, hg, row.tolist(), first, cnt)
