@@ -1112,8 +1112,12 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
     const int r = j * a.group + i;
     const size_t row = (size_t)(qbase + j) * a.Hq + qh;
     const size_t row0 = (((size_t)(sh + cta_first) * a.SUBS) * a.HG + h) * a.rows_max + r;
-    float mx = NEG_INF;
-    for (int p = threadIdx.x; p < n_parts; p += 32 * W) mx = fmaxf(mx, a.part_lse[part_row(row0, p)]);
+    // the log-sum-exp of the first 32 * W parts is loaded once, in the lane order the weighting loop
+    // below uses (warp w, lane l <-> part W * l + w), and kept for it
+    const int first = W * lane + warp;
+    const float lse_first = first < n_parts ? a.part_lse[part_row(row0, first)] : NEG_INF;
+    float mx = lse_first;
+    for (int p = 32 * W + threadIdx.x; p < n_parts; p += 32 * W) mx = fmaxf(mx, a.part_lse[part_row(row0, p)]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) s_max[warp] = mx;
@@ -1130,9 +1134,9 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
     // lane walks the rows of those parts with independent loads
     for (int base = 0; base < n_parts; base += 32 * W) {
       const int mine = base + W * lane + warp;
-      const float wl = mine < n_parts ? fast_exp2(a.part_lse[part_row(row0, mine)] - mu) : 0.f;
+      const float wl = mine < n_parts ? fast_exp2((base == 0 ? lse_first : a.part_lse[part_row(row0, mine)]) - mu) : 0.f;
       const int cnt = min(32, (n_parts - base - warp + W - 1) / W);
-#pragma unroll 4
+#pragma unroll 8
       for (int jj = 0; jj < cnt; ++jj) {
         const float w = __shfl_sync(0xffffffffu, wl, jj);
         wsum += w;
