@@ -40,6 +40,7 @@ struct Layout {
   uint32_t k_chunk, v_chunk, ks_chunk, vs_chunk;
   size_t smem_bytes;
   uint32_t q_smem_off, q_smem_bytes;  // per-slot query area behind the stages (0: does not fit)
+  int q_smem_tokens;                  // query tokens per sequence one area holds
   // workspace
   size_t ws_table, ws_lse, ws_o, ws_total;
 };
@@ -111,16 +112,27 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   L.n_stages = ns;
   L.smem_bytes = stages_off + (size_t)ns * L.stage_bytes;
   if (L.smem_bytes < stages_off + kDecodeThreads * 8) L.smem_bytes = stages_off + kDecodeThreads * 8;
-  // query rows of one (sequence, head group), one area per ring slot, if shared memory is left
+  // Query rows of one (sequence, head group), one area per ring slot, in the shared memory that is
+  // left: as many query tokens per sequence as fit (sequences with more keep the global path).  A
+  // ring deeper than three stages gives one stage up if that makes room for at least one token.
   L.q_smem_off = L.q_smem_bytes = 0;
-  {
-    const size_t per_slot = align_up((size_t)max_q_len * HG * group * D * q_elem_bytes, 128);
-    const size_t off = align_up(L.smem_bytes, 128);
-    if (off + (size_t)ns * per_slot <= kSmemBudget) {
+  L.q_smem_tokens = 0;
+  for (;;) {
+    const size_t token_bytes = (size_t)HG * group * D * q_elem_bytes;
+    const size_t off = align_up(stages_off + (size_t)ns * L.stage_bytes, 128);
+    const size_t room = off < kSmemBudget ? (kSmemBudget - off) / ns / 128 * 128 : 0;
+    int tokens = (int)(room / token_bytes);
+    if (tokens > max_q_len) tokens = max_q_len;
+    if (tokens >= 1) {
+      L.n_stages = ns;
       L.q_smem_off = (uint32_t)off;
-      L.q_smem_bytes = (uint32_t)per_slot;
-      L.smem_bytes = off + (size_t)ns * per_slot;
+      L.q_smem_bytes = (uint32_t)align_up((size_t)tokens * token_bytes, 128);
+      L.q_smem_tokens = tokens;
+      L.smem_bytes = off + (size_t)ns * L.q_smem_bytes;
+      break;
     }
+    if (ns <= 3) break;
+    --ns;
   }
   if (num_ctas <= 0) num_ctas = sm_count_cached();
   if (num_ctas <= 0) return fail(CUDA_LLM_ECUDA, "cannot query the SM count");
@@ -270,7 +282,7 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   if (!((uintptr_t)p->query & 15)) {  // bulk copies need a 16-byte aligned source
     a.q_smem_off = L.q_smem_off;
     a.q_smem_bytes = L.q_smem_bytes;
-    a.q_smem_tokens = p->max_q_len < 1 ? 1 : p->max_q_len;
+    a.q_smem_tokens = L.q_smem_tokens;
   }
   a.early_plan = (p->flags & CUDA_LLM_FLAG_STABLE_METADATA) ? 1 : 0;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_MATH) a.debug |= 1;
