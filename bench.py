@@ -265,8 +265,12 @@ def main():
     # How the workload spreads over N GPUs (north star): cfg2 one batch per rank (weak scaling);
     # cfg3 KV-head shards, cfg5 the batch dealt over the ranks, cfg4 KV ranges of the same
     # contexts with an all-gather + merge (strong scaling: total work fixed).
-    scaling, parallelism = "weak", f"sequence-sharded x{world}, one batch per rank"
+    scaling, parallelism = "weak", f"sequence-sharded x{world}: {world} batches dealt longest-first by context length"
     kw = dict(batch=args.batch, ctx_scale=args.ctx_scale, seed=seed, poison=False)
+    if cfg_id == 2 and world > 1:
+        # weak scaling: the job holds `world` batches; every rank draws the same length list and
+        # keeps the sequences the balancer deals to it (its own pages and tables, no collective)
+        kw.update(batch=(args.batch or 64) * world, len_seed=1002, deal=(world, rank))
     split_ctx = False
     if cfg_id == 3:
         scaling, parallelism = "strong", f"KV-head-sharded x{world}"
@@ -276,8 +280,9 @@ def main():
         kw.update(ctx_scale=args.ctx_scale / world)
         split_ctx = world > 1
     elif cfg_id == 5:
-        scaling, parallelism = "strong", f"sequence-sharded x{world}"
-        kw.update(batch=(args.batch or 256) // world)
+        scaling, parallelism = "strong", f"sequence-sharded x{world}, dealt longest-first by context length"
+        if world > 1:
+            kw.update(batch=(args.batch or 256), len_seed=1005, deal=(world, rank))
     wl = workloads.make_config(cfg_id, dev, **kw)
     kv_bytes = wl.kv_bytes()
     q_tokens = wl.query.shape[0]

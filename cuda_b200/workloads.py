@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import Tuple, List, Optional, Sequence
 
 import torch
 
@@ -261,17 +261,28 @@ def _lognormal_lens(n, median, sigma, lo, hi, gen):
 
 def make_config(config_id: int, device="cpu", *, batch: Optional[int] = None,
                 ctx_scale: float = 1.0, seed: Optional[int] = None,
-                poison: bool = True, head_shards: int = 1, len_seed: Optional[int] = None) -> DecodeWorkload:
+                poison: bool = True, head_shards: int = 1, len_seed: Optional[int] = None,
+                deal: Optional[Tuple[int, int]] = None) -> DecodeWorkload:
     """The benchmark configurations.  ``batch`` / ``ctx_scale`` shrink a configuration for
     parity tests (same shapes and value distributions, fewer / shorter sequences);
     ``head_shards`` builds one KV-head shard (1/head_shards of the KV and query heads);
     ``len_seed`` fixes the length draw independently of the data seed (ranks of a sharded run
-    share the lengths and differ in the data)."""
+    share the lengths and differ in the data); ``deal = (world, rank)`` draws the lengths of the
+    whole job (``batch`` sequences in total) and keeps the sequences that longest-first dealing
+    balanced by context length (``sharding.shard_sequences``) gives to ``rank``."""
     seed = 1000 + config_id if seed is None else seed
     cg = torch.Generator()
     cg.manual_seed(seed if len_seed is None else len_seed)
     hs = head_shards
     sc = lambda x: max(1, int(round(x * ctx_scale)))
+
+    def dealt(lens, *extras):
+        if deal is None:
+            return (lens,) + extras
+        from .sharding import shard_sequences
+        ids = shard_sequences(lens, deal[0])[deal[1]]
+        return tuple([x[i] for i in ids] for x in (lens,) + extras)
+
     if config_id == 1:
         b = batch or 4
         return build_workload("cfg1_mha_perhead_d64", context_lens=[sc(512)] * b, q_lens=None,
@@ -281,6 +292,7 @@ def make_config(config_id: int, device="cpu", *, batch: Optional[int] = None,
     if config_id == 2:
         b = batch or 64
         lens = torch.randint(sc(1024), sc(8192) + 1, (b,), generator=cg).tolist()
+        (lens,) = dealt(lens)
         return build_workload("cfg2_llama8b_fp8_pertoken", context_lens=lens, q_lens=None,
                               num_q_heads=32, num_kv_heads=8, head_dim=128, page_size=16,
                               q_dtype=torch.bfloat16, scale_mode=SCALE_PER_TOKEN, pool_factor=1.25,
@@ -303,6 +315,7 @@ def make_config(config_id: int, device="cpu", *, batch: Optional[int] = None,
         lens = _lognormal_lens(b, 2048 * ctx_scale, 1.0, max(4, sc(16)), sc(16384), cg)
         ql = torch.where(torch.rand(b, generator=cg) < 0.7, 1, 4).tolist()
         ql = [min(q, l) for q, l in zip(ql, lens)]
+        lens, ql = dealt(lens, ql)
         return build_workload("cfg5_continuous_batching_mx8k_mx4v", context_lens=lens, q_lens=ql,
                               num_q_heads=32, num_kv_heads=8, head_dim=128, page_size=16,
                               q_dtype=torch.bfloat16, k_format=KV_FP8_E4M3, v_format=KV_FP4_E2M1,
