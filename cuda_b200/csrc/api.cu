@@ -77,7 +77,7 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   int HG = 8;
   while (Hkv % HG) HG >>= 1;
   while (pairs / HG < page) HG >>= 1;  // a stage must hold whole pages
-  if (token_major) HG = 1;             // contiguous K/V: a stage is 128 consecutive tokens of one head
+  if (token_major) HG = (Hkv % 2 == 0) ? 2 : 1;  // contiguous K/V: a stage is 128 / HG consecutive tokens of HG heads
   L.HG = HG;
   // 16 consumer warps, 8 bit: NT == 1 -> (HG heads) x (16/HG sub-tiles of 16 tokens);
   //                           NT == 2 -> 2 row halves x (HG heads) x (8/HG sub-tiles of 32 tokens)
@@ -97,8 +97,8 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   else if (scale_mode == CUDA_LLM_SCALE_PER_TOKEN) L.ks_chunk = L.vs_chunk = (uint32_t)HG * page * 4;
   else if (scale_mode == CUDA_LLM_SCALE_MX_E8M0) L.ks_chunk = L.vs_chunk = (uint32_t)HG * (D / 32) * page;
   else L.ks_chunk = L.vs_chunk = 0;
-  L.k_page_stride = L.k_chunk + pad;
-  L.v_page_stride = L.v_chunk + pad;
+  L.k_page_stride = (token_major ? HG : 1) * L.k_chunk + pad;  // token-major: k_chunk is one head's rows
+  L.v_page_stride = (token_major ? HG : 1) * L.v_chunk + pad;
   L.ks_page_stride = L.ks_chunk;
   L.vs_page_stride = L.vs_chunk;
   L.off_v = L.PPS * L.k_page_stride;

@@ -472,16 +472,15 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       const uint32_t q_row_bytes = (uint32_t)(a.HG * a.group * D) * (a.q_dtype == CUDA_LLM_F32 ? 4u : 2u);
       const uint32_t q_bytes = (q_to_smem && !no_copy) ? (uint32_t)ic.qlen * q_row_bytes : 0u;
       if (TM) {
-        // one copy each for the K and the V rows of the live tokens of this (batch, head) tile
-        if (lane == 0) {
-          const uint32_t bytes = (uint32_t)min(TOK_STAGE, ic.ctx - tok0) * (D * 2);
-          mbar_arrive_expect_tx(fb, no_copy ? 0u : 2u * bytes + q_bytes);
-          if (!no_copy) {
-            const uint32_t sb = stage0 + slot * a.stage_bytes;
-            const uint64_t off = (((uint64_t)ic.s * a.Hkv + ic.hg) * a.fixed_ctx + tok0) * (D * 2);
-            bulk_g2s_hint(sb, a.kc + off, bytes, fb, stream_policy);
-            bulk_g2s_hint(sb + a.off_v, a.vc + off, bytes, fb, stream_policy);
-          }
+        // per head of the group one copy each for the K and the V rows of the live tokens of the tile
+        const uint32_t bytes = (uint32_t)min(TOK_STAGE, ic.ctx - tok0) * (D * 2);
+        if (lane == 0) mbar_arrive_expect_tx(fb, no_copy ? 0u : 2u * (uint32_t)a.HG * bytes + q_bytes);
+        __syncwarp();
+        if (!no_copy && lane < a.HG) {
+          const uint32_t sb = stage0 + slot * a.stage_bytes + lane * a.k_chunk;
+          const uint64_t off = (((uint64_t)ic.s * a.Hkv + (uint64_t)ic.hg * a.HG + lane) * a.fixed_ctx + tok0) * (D * 2);
+          bulk_g2s_hint(sb, a.kc + off, bytes, fb, stream_policy);
+          bulk_g2s_hint(sb + a.off_v, a.vc + off, bytes, fb, stream_policy);
         }
         __syncwarp();
       } else if (lane == 0) {
@@ -560,8 +559,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       // row = token, 2*D bytes.  Thread (g,t) reads 16-byte chunks t, t+4, ... of token rows g and
       // g+8 of its sub-tile: eight consecutive head_dim values each, used as two k-tile column
       // pairs (Q.K) or, after an 8x8 transpose across the warp, as rows of O^T (P.V).
-      k_lm[mt] = (ts * 16 + g) * (D * 2) + t * 16;
-      v_lm[mt] = a.off_v + (ts * 16 + g) * (D * 2) + t * 16;
+      k_lm[mt] = h * a.k_chunk + (ts * 16 + g) * (D * 2) + t * 16;
+      v_lm[mt] = a.off_v + h * a.k_chunk + (ts * 16 + g) * (D * 2) + t * 16;
     } else if (KV16) {
       // row = head_dim index, 2*PAGE bytes; a 16-token m-tile is 32 bytes of a row.  Four 8x8
       // matrices per ldmatrix.x4 -- K (transposed on load): lanes 8..15 the upper 8 tokens, lanes
