@@ -11,12 +11,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libcuda_llm_b200.so")
 
 OK, EINVAL, EALIGN, EWORKSPACE, ECUDA, EDEVICE = 0, -1, -2, -3, -4, -5
-ST_BAD_BLOCK, ST_BAD_CTX, ST_TIMEOUT, ST_BAD_QLEN = 1, 2, 4, 8
+ST_BAD_BLOCK, ST_BAD_CTX, ST_TIMEOUT, ST_BAD_QLEN, ST_SCALE_RANGE, ST_INCOMPLETE = 1, 2, 4, 8, 16, 32
 F32, F16, BF16 = 0, 1, 2
 KV_FP8_E4M3, KV_FP4_E2M1, KV_INT8, KV_F16, KV_BF16 = 0, 1, 2, 3, 4
 SCALE_PER_HEAD, SCALE_PER_BLOCK, SCALE_PER_TOKEN, SCALE_MX_E8M0 = 0, 1, 2, 3
 FLAG_SKIP_MERGE = 1
 FLAG_STABLE_METADATA = 64   # lengths / offsets / block tables are not written by the kernel in front of the call
+FLAG_TEST_STALL = 128       # failure-path test: one stage is announced but never sent; waits give up quickly
 
 
 class PagedDecodeParams(C.Structure):
@@ -41,6 +42,7 @@ SYMBOLS = {
     "cuda_llm_paged_decode": (C.c_int, [C.POINTER(PagedDecodeParams), C.c_void_p]),
     "cuda_llm_paged_decode_static": (C.c_int, [C.POINTER(PagedDecodeParams), C.c_void_p]),
     "cuda_llm_static_scratch_bytes": (C.c_size_t, []),
+    "cuda_llm_static_decode_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "cuda_llm_dense_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
     "cuda_llm_paged_attention": (C.c_int, [C.c_void_p] * 6 + [C.c_int32] * 7 + [C.c_float, C.c_int32, C.c_void_p,
                                                                             C.c_size_t, C.c_void_p]),

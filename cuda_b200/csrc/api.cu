@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstring>
 #include <cmath>
+#include <mutex>
 
 #include "decode_launch.cuh"
 
@@ -56,6 +57,23 @@ static int sm_count_cached() {
     counts[dev] = n;
   }
   return counts[dev];
+}
+
+// CUDA_LLM_OK when the current device is an sm_100 part (the only target of this library).
+static int check_device() {
+  static int major_of[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+  const int slot = dev < 64 ? dev : 63;
+  if (!major_of[slot]) {
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceGetAttribute");
+    major_of[slot] = major;
+  }
+  if (major_of[slot] != 10) return fail(CUDA_LLM_EDEVICE, "this library holds sm_100a code only; the current device is not an sm_100 GPU");
+  return CUDA_LLM_OK;
 }
 
 // Pure arithmetic (no device access when num_ctas > 0): shared-memory stage layout and
@@ -285,6 +303,11 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
     a.q_smem_tokens = L.q_smem_tokens;
   }
   a.early_plan = (p->flags & CUDA_LLM_FLAG_STABLE_METADATA) ? 1 : 0;
+  a.grid = L.grid;
+  a.n_slots = p->num_seqs * L.n_hg + L.grid;
+  a.stall_test = (p->flags & CUDA_LLM_FLAG_TEST_STALL) ? 1 : 0;
+  a.short_waits = a.stall_test;
+#ifdef CUDA_LLM_DIAGNOSTICS
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_MATH) a.debug |= 1;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_COPY) a.debug |= 2;
   if (p->flags & CUDA_LLM_FLAG_DIAG_NO_SCALE_COPY) a.debug |= 16;
@@ -295,9 +318,10 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
     a.lse = nullptr;
   }
   {
-    const int ns_req = (p->flags >> 8) & 0xF;  // diagnostics: cap the ring depth
+    const int ns_req = (p->flags >> 8) & 0xF;  // cap the ring depth
     if (ns_req >= 2 && ns_req < a.n_stages) a.n_stages = ns_req;
   }
+#endif
   a.stage_bytes = L.stage_bytes;
   a.off_v = L.off_v;
   a.off_ks = L.off_ks;
@@ -330,6 +354,8 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
     fn = pick_d<MODE_MX8>(D, page, L.NT, precise);
   if (!fn) return fail(CUDA_LLM_EINVAL, "no kernel for this shape");
 
+  rc = check_device();
+  if (rc != CUDA_LLM_OK) return rc;
   cudaError_t e = fn(a, L.grid, L.smem_bytes, st);
   if (e != cudaSuccess) return fail_cuda(e, "paged_decode_kernel launch");
   if (p->flags & CUDA_LLM_FLAG_SKIP_MERGE) return CUDA_LLM_OK;
@@ -340,32 +366,52 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
 
 size_t cuda_llm_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
-int cuda_llm_paged_decode_static(const CudaLlmPagedDecodeParams* p, void* stream) {
-  if (!p) return fail(CUDA_LLM_EINVAL, "params is null");
-  static void* scratch_addr[64] = {nullptr};  // device address of g_static_scratch, per device
+// Device address of g_static_scratch on the current device, resolved (and its status word
+// zeroed) the first time a device asks.  No allocation: a symbol look-up and a 256-byte memset.
+static int static_scratch_address(cudaStream_t st, void** out) {
+  static std::mutex mu;
+  static void* scratch_addr[64] = {nullptr};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
   if (dev < 0 || dev >= 64) return fail(CUDA_LLM_EINVAL, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(mu);
+  if (!scratch_addr[dev]) {  // first use on this device: resolve the symbol with this device current
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
+    // the status word starts at zero; after that it is sticky until cuda_llm_static_decode_status
+    e = cudaMemsetAsync(ptr, 0, 256, st);
+    if (e != cudaSuccess) return fail_cuda(e, "clearing the static scratch header");
+    scratch_addr[dev] = ptr;
+  }
+  *out = scratch_addr[dev];
+  return CUDA_LLM_OK;
+}
+
+int cuda_llm_paged_decode_static(const CudaLlmPagedDecodeParams* p, void* stream) {
+  if (!p) return fail(CUDA_LLM_EINVAL, "params is null");
   const size_t need = cuda_llm_paged_decode_workspace_bytes(p->num_seqs, p->num_q_heads, p->num_kv_heads,
                                                             p->head_dim, p->page_size, p->max_q_len, p->num_ctas);
   if (p->num_seqs > 0 && need == 0) return CUDA_LLM_EINVAL;  // message set by the layout check
   if (need > kStaticScratchBytes)
     return fail(CUDA_LLM_EWORKSPACE, "problem needs more scratch than the 16 MiB built into the library; "
                                      "use cuda_llm_paged_decode with a caller-provided workspace");
-  if (!scratch_addr[dev]) {  // first call on this device: resolve the symbol with this device current
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
-    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
-    scratch_addr[dev] = ptr;
-  }
-  // the array keeps whatever the previous call left: the status word has to start at zero
-  e = cudaMemsetAsync(scratch_addr[dev], 0, 256, reinterpret_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail_cuda(e, "clearing the static scratch header");
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(reinterpret_cast<cudaStream_t>(stream), &scratch);
+  if (rc != CUDA_LLM_OK) return rc;
   CudaLlmPagedDecodeParams q = *p;
-  q.workspace = scratch_addr[dev];
+  q.workspace = scratch;
   q.workspace_bytes = kStaticScratchBytes;
   return cuda_llm_paged_decode(&q, stream);
+}
+
+int cuda_llm_static_decode_status(void* stream, uint32_t* status_out) {
+  if (!status_out) return fail(CUDA_LLM_EINVAL, "null argument");
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(reinterpret_cast<cudaStream_t>(stream), &scratch);
+  if (rc != CUDA_LLM_OK) return rc;
+  return cuda_llm_decode_status(scratch, stream, status_out);
 }
 
 int cuda_llm_decode_status(void* workspace, void* stream, uint32_t* status_out) {
@@ -497,6 +543,8 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
     a.q_dtype = a.out_dtype = dtype;
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.n_stages = L.n_stages;
+    a.grid = L.grid;
+    a.n_slots = batch_size * L.n_hg + L.grid;
     if (!((uintptr_t)q & 15)) {
       a.q_smem_off = L.q_smem_off;
       a.q_smem_bytes = L.q_smem_bytes;
@@ -506,6 +554,8 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
     a.k_page_stride = L.k_page_stride; a.v_page_stride = L.v_page_stride;
     a.k_chunk = L.k_chunk; a.v_chunk = L.v_chunk;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    lrc = check_device();
+    if (lrc != CUDA_LLM_OK) return lrc;
     LaunchFn fn;
     if (dtype == CUDA_LLM_BF16) fn = head_dim == 64 ? launch_paged_decode<64, 16, MODE_KV_BF16_TM, 1, false> : launch_paged_decode<128, 16, MODE_KV_BF16_TM, 1, false>;
     else fn = head_dim == 64 ? launch_paged_decode<64, 16, MODE_KV_F16_TM, 1, false> : launch_paged_decode<128, 16, MODE_KV_F16_TM, 1, false>;

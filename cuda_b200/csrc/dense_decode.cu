@@ -190,7 +190,8 @@ static int choose_splits(int S, int Hkv, int max_tokens) {
 size_t dense_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens) {
   const int n = choose_splits(S, Hkv, max_tokens);
   const size_t rows = (size_t)S * Hq;
-  return ((size_t)n * rows * sizeof(float) + 255) / 256 * 256 + (size_t)n * rows * D * sizeof(float);
+  // the first 256 bytes stay free: a workspace shared with the paged decode keeps its status word there
+  return 256 + ((size_t)n * rows * sizeof(float) + 255) / 256 * 256 + (size_t)n * rows * D * sizeof(float);
 }
 
 cudaError_t run_dense_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
@@ -206,8 +207,8 @@ cudaError_t run_dense_decode(bool paged, const void* q, const void* k, const voi
   a.chunk = ((max_tokens + a.n_splits - 1) / a.n_splits + 31) / 32 * 32;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   const size_t rows = (size_t)S * Hq;
-  a.part_lse = reinterpret_cast<float*>(workspace);
-  a.part_o = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) +
+  a.part_lse = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + 256);  // behind the status header
+  a.part_o = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + 256 +
                                       ((size_t)a.n_splits * rows * sizeof(float) + 255) / 256 * 256);
   cudaError_t e;
   if (paged) e = (D == 64) ? launch_dense_t<64, true>(a, dtype, st) : launch_dense_t<128, true>(a, dtype, st);

@@ -31,13 +31,24 @@
 // Numerical notes.  E4M3 -> f16 and E2M1 -> f16 are exact.  Q is used in f16 (bf16 -> f16 is
 // exact for |q| in [2^-14, 65504]); an fp32 Q is split into an f16 high and low part when
 // PRECISE.  E8M0 K scales are placed into the fp32 exponent field (byte 0 acts as 0, not 2^-127;
-// byte 255 as inf, not NaN).  P is rounded to f16 (again hi+lo when PRECISE).  An E8M0 scale 2^e of a
-// V block multiplies P in f16 (E4M3 V: exact up to e = 15; packed E2M1 V: the codes enter the
-// tensor core as placed, at 2^-14 of their value, and the scale carries 2^7, exact up to e = 8);
-// below about e = -10 the product loses bits to f16 subnormals, larger exponents overflow to inf.
+// byte 255 as inf, not NaN).  P is rounded to f16 (again hi+lo when PRECISE).  E8M0 V scales: the
+// largest block exponent of a token, e_ref, is folded into that token's softmax exponent exactly as
+// an fp32 per-token V scale is (w = s + e_ref, running maximum over w, denominator accumulates
+// P * 2^-e_ref), and P is multiplied in f16 by 2^(e_b - e_ref) <= 1 per 32-element block.  Nothing
+// overflows whatever the exponents are; a block more than 2^14 below the largest block of its own
+// token contributes zero.  Scale bytes of live tokens outside [32, 223] (2^-95 .. 2^96) set
+// CUDA_LLM_ST_SCALE_RANGE: the fp32 denominator is not guaranteed there.
 #pragma once
 #include "sm100_primitives.cuh"
 #include "cuda_llm_b200.h"
+
+// Diagnostics (per-CTA timestamps, copy-only / math-only runs) exist only in builds made with
+// -DCUDA_LLM_DIAGNOSTICS; the shipped library compiles every such branch away.
+#ifdef CUDA_LLM_DIAGNOSTICS
+#define B200_DIAG(x) (x)
+#else
+#define B200_DIAG(x) false
+#endif
 
 namespace b200 {
 
@@ -98,6 +109,9 @@ struct DecodeArgs {
                               // SM id; ns of table prefetches issued, first table entry landed, first copy issued
   float scale_log2;
   int n_stages;
+  int grid, n_slots;    // CTAs of the decode launch; partial-result slots in the workspace
+  int short_waits;      // every mbarrier wait gives up after kShortPolls polls instead of kMaxPolls
+  int stall_test;       // failure-path test: CTA 0 arms its first stage but issues no copies for it
   uint32_t stage_bytes, off_v, off_ks, off_vs;
   uint32_t k_page_stride, v_page_stride, ks_page_stride, vs_page_stride;  // smem, per page
   uint32_t k_chunk, v_chunk, ks_chunk, vs_chunk;                          // bytes per page copy
@@ -140,16 +154,17 @@ __device__ __forceinline__ void store_out_elem(void* out, int dtype, size_t idx,
   else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16(v);
 }
 
-// E8M0 byte pair (two 16-bit lanes holding 0..255) -> f16x2 of 2^(e-127+SHIFT), clamped to
-// [2^-15 -> 0, 2^16 -> inf].
-template <int SHIFT>
-__device__ __forceinline__ uint32_t e8m0_pair_to_f16x2(uint32_t bytes_in_halves) {
-  constexpr uint32_t LO = 112u - SHIFT;          // byte whose power of two has f16 exponent field 0
-  constexpr uint32_t LO2 = LO | (LO << 16), HI2 = (LO + 31u) | ((LO + 31u) << 16);
-  uint32_t x;
-  asm("max.u16x2 %0, %1, %2;" : "=r"(x) : "r"(bytes_in_halves), "r"(LO2));
-  asm("min.u16x2 %0, %1, %2;" : "=r"(x) : "r"(x), "r"(HI2));
-  return (x - LO2) << 10;
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// Two E8M0 bytes (in 16-bit lanes) relative to a reference exponent -> f16x2 of
+// 2^(e - e_ref + SHIFT).  `c` holds (15 + SHIFT + 256) - e_ref per lane; e <= e_ref, so the f16
+// exponent field 15 + SHIFT + e - e_ref never exceeds 15 + SHIFT, and a field below 1 gives +0.
+__device__ __forceinline__ uint32_t e8m0_rel_pair_to_f16x2(uint32_t bytes_in_halves, uint32_t c) {
+  const uint32_t x = max_u16x2(bytes_in_halves + c, 0x01000100u);
+  return (x - 0x01000100u) << 10;
 }
 
 // Packed E2M1 -> f16 by bit placement.  A nibble s.ee.m put at f16 bits 15 and 11..9 reads as
@@ -214,7 +229,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   // scheduled from here on.
   if (!a.early_plan) asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;");
-  const bool tracing = (a.debug & 4) && a.trace != nullptr;
+  const bool tracing = B200_DIAG((a.debug & 4) && a.trace != nullptr);
   if (tracing && threadIdx.x == 0) a.trace[blockIdx.x * 8 + 0] = globaltimer_ns();
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
@@ -268,7 +283,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   const long long per_cta = max(small_units ? (long long)(((unsigned)total_units + gridDim.x - 1) / gridDim.x)
                                             : (total_units + gridDim.x - 1) / gridDim.x,
                                 (long long)(WEIGHTED ? 2 : 1));
-  const int vb = (a.debug & 32) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // diagnostics: reversed ranges
+  const int vb = B200_DIAG(a.debug & 32) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // diagnostics: reversed ranges
   const long long u_begin = min(total_units, (long long)vb * per_cta);
   const long long u_end = min(total_units, u_begin + per_cta);
   if (u_begin < u_end && my_units > 0 && u_begin >= my_prefix && u_begin < my_prefix + my_units) {
@@ -289,7 +304,12 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
     a.trace[blockIdx.x * 8 + 4] = smid;
   }
-  if (u_begin >= u_end) return;
+  if (u_begin >= u_end) {
+    // no work: still wait for the kernel in front, so that this grid (and with it the split merge,
+    // which waits on this grid only) never completes before that kernel has
+    if (a.early_plan) asm volatile("griddepcontrol.wait;" ::: "memory");
+    return;
+  }
 
   if (warp == kConsumerWarps) {
     // =============================================================== producer warp
@@ -404,7 +424,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     for (int it = 0;; ++it, slot = (slot + 1 == NS) ? 0 : slot + 1, phase ^= (slot == 0) ? 1u : 0u) {
       if (ic.pos >= u_end) {
         // terminal stage: no bytes, tells the consumers that this CTA's range is done
-        if (it >= NS && !mbar_wait(empty_bar + 8 * slot, phase ^ 1)) {
+        if (it >= NS && !mbar_wait(empty_bar + 8 * slot, phase ^ 1, a.short_waits)) {
           ok = false;
           break;
         }
@@ -441,7 +461,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         }
       }
       if (it >= NS) {
-        if (!mbar_wait(empty_bar + 8 * slot, phase ^ 1)) {
+        if (!mbar_wait(empty_bar + 8 * slot, phase ^ 1, a.short_waits)) {
           ok = false;
           break;
         }
@@ -466,7 +486,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       if (MODE == MODE_PAGE_SCALE && lane < kMaxPagesPerStage) sts32(meta + 64 + 4 * lane, c_blk);
       seg_fresh = false;
       const uint32_t fb = full_bar + 8 * slot;
-      const bool no_copy = (a.debug & 2) != 0;  // diagnostics: math on whatever shared memory holds
+      // failure-path test: the bytes are announced but never sent, so the consumers' wait runs out
+      const bool stalled = a.stall_test && blockIdx.x == 0 && it == 0;
+      const bool no_copy = B200_DIAG((a.debug & 2) != 0);  // diagnostics: math on whatever shared memory holds
       // the query rows of a new (sequence, head group) travel with its first stage, so that the
       // consumers find them in shared memory instead of waiting for a global load with the ring full
       const uint32_t q_row_bytes = (uint32_t)(a.HG * a.group * D) * (a.q_dtype == CUDA_LLM_F32 ? 4u : 2u);
@@ -476,7 +498,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         const uint32_t bytes = (uint32_t)min(TOK_STAGE, ic.ctx - tok0) * (D * 2);
         if (lane == 0) mbar_arrive_expect_tx(fb, no_copy ? 0u : 2u * (uint32_t)a.HG * bytes + q_bytes);
         __syncwarp();
-        if (!no_copy && lane < a.HG) {
+        if (!no_copy && !stalled && lane < a.HG) {
           const uint32_t sb = stage0 + slot * a.stage_bytes + lane * a.k_chunk;
           const uint64_t off = (((uint64_t)ic.s * a.Hkv + (uint64_t)ic.hg * a.HG + lane) * a.fixed_ctx + tok0) * (D * 2);
           bulk_g2s_hint(sb, a.kc + off, bytes, fb, stream_policy);
@@ -485,17 +507,17 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
         __syncwarp();
       } else if (lane == 0) {
         uint32_t bytes = (uint32_t)np * (a.k_chunk + a.v_chunk);
-        if (NTYPES == 4 && !(a.debug & 16)) bytes += (uint32_t)np * (a.ks_chunk + a.vs_chunk);
+        if (NTYPES == 4 && !B200_DIAG(a.debug & 16)) bytes += (uint32_t)np * (a.ks_chunk + a.vs_chunk);
         mbar_arrive_expect_tx(fb, no_copy ? 0u : bytes + q_bytes);
       }
       __syncwarp();
-      if (q_bytes != 0 && lane < ic.qlen) {  // lane j copies the rows of query token j (contiguous over the heads of the group)
+      if (q_bytes != 0 && !stalled && lane < ic.qlen) {  // lane j copies the rows of query token j (contiguous over the heads of the group)
         const uint8_t* src = reinterpret_cast<const uint8_t*>(a.q) +
                              ((size_t)(ic.qbase + lane) * a.Hq + (size_t)ic.hg * a.HG * a.group) * D *
                                  (a.q_dtype == CUDA_LLM_F32 ? 4 : 2);
         bulk_g2s(smem_base + a.q_smem_off + slot * a.q_smem_bytes + lane * q_row_bytes, src, q_row_bytes, fb);
       }
-      if (!TM && !no_copy) {
+      if (!TM && !no_copy && !stalled) {
         const uint32_t sb = stage0 + slot * a.stage_bytes;
         // lane pi issues the copies of page pi
         if (lane < np) {
@@ -504,7 +526,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
                    a.k_chunk, fb, stream_policy);
           bulk_g2s_hint(sb + a.off_v + lane * a.v_page_stride,
                    a.vc + b * a.v_blk_stride + (uint64_t)ic.hg * a.v_chunk, a.v_chunk, fb, stream_policy);
-          if (NTYPES == 4 && !(a.debug & 16)) {
+          if (NTYPES == 4 && !B200_DIAG(a.debug & 16)) {
             bulk_g2s_hint(sb + a.off_ks + lane * a.ks_page_stride,
                      a.ks + b * a.ks_blk_stride + (uint64_t)ic.hg * a.ks_chunk, a.ks_chunk, fb, stream_policy);
             bulk_g2s_hint(sb + a.off_vs + lane * a.vs_page_stride,
@@ -522,7 +544,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       if (lane == 0) atomicOr(a.status, CUDA_LLM_ST_TIMEOUT);
       // wait (bounded) for this warp's own copies still in flight before leaving
       for (int it = max(0, issued - NS); it < issued; ++it)
-        (void)mbar_wait(full_bar + 8 * (it % NS), (it / NS) & 1);
+        (void)mbar_wait(full_bar + 8 * (it % NS), (it / NS) & 1, a.short_waits);
     }
     return;
   }
@@ -573,6 +595,11 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     }
   }
 
+  // E8M0 V scales are also read where the softmax runs: bytes of tokens 2g, 2g+1, one block per
+  // thread of a quad (block t, or t & 1 when head_dim is 64), relative to vs_mx[]
+  const int mx_delta = 2 * g - 4 * t + (t & (NB - 1)) * PAGE;
+  uint32_t scale_range_bad = 0;  // MX: sticky, a live V scale byte outside [32, 223]
+
   constexpr int KS = D / 32;   // ldmatrix.x4 steps over head_dim (32 rows each)
   uint32_t qf[KT][2];
   uint32_t ql[PRECISE ? KT : 1][2];
@@ -589,7 +616,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   int slot = 0;
   uint32_t phase = 0;
   for (int it = 0;; ++it, slot = (slot + 1 == NS) ? 0 : slot + 1, phase ^= (slot == 0) ? 1u : 0u) {
-    if (!mbar_wait(full_bar + 8 * slot, phase)) {
+    if (!mbar_wait(full_bar + 8 * slot, phase, a.short_waits)) {
       if (lane == 0) atomicOr(a.status, CUDA_LLM_ST_TIMEOUT);
       return;
     }
@@ -698,7 +725,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     }
 
     const int nv = min(SUB, ctx - tok0 - ts * SUB);  // valid tokens of this warp's sub-tile
-    if (nv > 0 && live && !(a.debug & 1) && (par < 0 || (it & 1) == par) && (!helper || (it & 1) == nt_w)) {
+    if (nv > 0 && live && !B200_DIAG(a.debug & 1) && (par < 0 || (it & 1) == par) && (!helper || (it & 1) == nt_w)) {
       const bool tail = nv < SUB;  // masking path (dead tokens)
       // causal limit: query row r = j*group + i sees positions < ctx - qlen + 1 + j
       const int pos0 = tok0 + ts * SUB;  // absolute position of sub-tile token 0
@@ -771,6 +798,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       // maximum is taken over w, P = 2^(w - M) <= 1 multiplies the raw V codes, and the softmax
       // denominator accumulates P / v_scale.
       float ksc[MT][2], vlg[MT][2], vrc[MT][2];
+      uint32_t eref[MX ? MT : 1];  // MX: reference exponents of tokens 2g | 2g+1 << 16
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         if (MODE == MODE_TOKEN_SCALE) {
@@ -797,6 +825,24 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           ksc[mt][0] = ksc[mt][1] = kp;
           vlg[mt][0] = vlg[mt][1] = vl;
           vrc[mt][0] = vrc[mt][1] = vr;
+        } else if (MX) {
+          // reference exponent of a token = its largest V block exponent: the quad reduces the NB
+          // bytes of tokens 2g (low lane) and 2g+1 (high lane)
+          uint32_t em = prmt(lds16(sb + vs_mx[mt] + mx_delta), 0u, 0x4140);
+          em = max_u16x2(em, __shfl_xor_sync(0xffffffffu, em, 1));
+          if (NB == 4) em = max_u16x2(em, __shfl_xor_sync(0xffffffffu, em, 2));
+          if (tail) {  // a dead slot may hold anything
+            em = ((16 * mt + 2 * g < nv) ? (em & 0xffffu) : 127u) |
+                 ((16 * mt + 2 * g + 1 < nv) ? (em & 0xffff0000u) : (127u << 16));
+          }
+          eref[mt] = em;
+          scale_range_bad |= ((em + 0x00200020u) | (em - 0x00200020u)) & 0x01000100u;
+          ksc[mt][0] = ksc[mt][1] = 1.f;
+          // e - 127 as fp32 (integer in the mantissa of 2^23), 2^(127 - e) by exponent placement
+          vlg[mt][0] = __uint_as_float(0x4B000000u | (em & 0xffffu)) - 8388735.f;
+          vlg[mt][1] = __uint_as_float(0x4B000000u | (em >> 16)) - 8388735.f;
+          vrc[mt][0] = __uint_as_float(0x7F000000u - (em << 23));
+          vrc[mt][1] = __uint_as_float(0x7F000000u - ((em << 7) & 0x7F800000u));
         } else {
           ksc[mt][0] = ksc[mt][1] = 1.f;
           vlg[mt][0] = vlg[mt][1] = 0.f;
@@ -893,6 +939,20 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
           }
         }
       }
+      // MX: the reference exponents follow P through the same 8x8 transpose and regrouping, so that
+      // they sit beside the tokens whose block scales this thread reads (E4M3 V: {4t, 4t+1} and
+      // {4t+2, 4t+3}; packed E2M1 V: {4t, 4t+2} and {4t+1, 4t+3}); c = (15 + shift + 256) - e_ref
+      uint32_t c02[MX ? MT : 1], c13[MX ? MT : 1];
+      if (MX) {
+        constexpr uint32_t kRel = (15u + (V4 ? kE2M1ScaleShift : 0) + 256u) * 0x00010001u;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint32_t r0 = movmatrix_trans(prmt(eref[MX ? mt : 0], 0u, 0x1010));
+          const uint32_t r1 = movmatrix_trans(prmt(eref[MX ? mt : 0], 0u, 0x3232));
+          c02[MX ? mt : 0] = kRel - (V4 ? r0 : prmt(r0, r1, 0x5410));
+          c13[MX ? mt : 0] = kRel - (V4 ? r1 : prmt(r0, r1, 0x7632));
+        }
+      }
       uint32_t vmask[MT];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
@@ -954,10 +1014,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             // va[0], va[1]: rows g, g+8 of O m-tile 2dp; va[2], va[3]: of m-tile 2dp+1 (one scale block)
             uint32_t s02 = 0u, s13 = 0u;
             if (MX) {
-              uint32_t e = lds32(sb + vs_mx[mt] + dp * PAGE);  // E8M0 of tokens 4t..4t+3, block dp
-              if (tail) e = (e & vmask[mt]) | (0x7f7f7f7fu & ~vmask[mt]);
-              s02 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4140));  // tokens 4t, 4t+1
-              s13 = e8m0_pair_to_f16x2<0>(prmt(e, 0u, 0x4342));  // tokens 4t+2, 4t+3
+              // E8M0 of tokens 4t..4t+3, block dp (a dead slot gives a finite factor; its P is 0)
+              const uint32_t e = lds32(sb + vs_mx[mt] + dp * PAGE);
+              s02 = e8m0_rel_pair_to_f16x2(prmt(e, 0u, 0x4140), c02[MX ? mt : 0]);  // tokens 4t, 4t+1
+              s13 = e8m0_rel_pair_to_f16x2(prmt(e, 0u, 0x4342), c13[MX ? mt : 0]);  // tokens 4t+2, 4t+3
             }
             // a block scale multiplies P (two registers per 32 head_dim rows), not the V operand
             uint32_t b0 = pb[mt][0], b1 = pb[mt][1];
@@ -981,10 +1041,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             // m-tiles 4dp, 4dp+1 share scale block 2dp, m-tiles 4dp+2, 4dp+3 share block 2dp+1
 #pragma unroll
             for (int bb = 0; bb < 2; ++bb) {
-              uint32_t e = lds32(sb + vs_mx[mt] + (2 * dp + bb) * PAGE);
-              if (tail) e = (e & vmask[mt]) | (0x7f7f7f7fu & ~vmask[mt]);
-              const uint32_t s02 = e8m0_pair_to_f16x2<kE2M1ScaleShift>(prmt(e, 0u, 0x4240));
-              const uint32_t s13 = e8m0_pair_to_f16x2<kE2M1ScaleShift>(prmt(e, 0u, 0x4341));
+              const uint32_t e = lds32(sb + vs_mx[mt] + (2 * dp + bb) * PAGE);
+              const uint32_t s02 = e8m0_rel_pair_to_f16x2(prmt(e, 0u, 0x4240), c02[MX ? mt : 0]);
+              const uint32_t s13 = e8m0_rel_pair_to_f16x2(prmt(e, 0u, 0x4341), c13[MX ? mt : 0]);
               // the block scale multiplies P; the codes go to the tensor core as placed (value * 2^-14)
               const uint32_t b0 = hmul2(pb[mt][0], s02), b1 = hmul2(pb[mt][1], s13);
 #pragma unroll
@@ -1007,6 +1066,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
     if (flags & FLAG_LAST) {
       // ------------------------------------------------------------ epilogue of the segment
       const bool direct = (flags & FLAG_DIRECT) != 0;
+      if (MX && scale_range_bad) {
+        atomicOr(a.status, CUDA_LLM_ST_SCALE_RANGE);
+        scale_range_bad = 0;
+      }
       float l0 = l_run[0], l1 = l_run[1];
 #pragma unroll
       for (int o = 4; o < 32; o <<= 1) {
@@ -1100,8 +1163,20 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
     return;
   }
   const int32_t* tb = a.table + 4 * (size_t)sh;
-  const int cta_first = tb[0], n_cta = tb[1], direct = tb[2];
-  if (direct) return;
+  int cta_first = tb[0], n_cta = tb[1];
+  const int direct = tb[2];
+  // An entry is written by the CTA that owns the segment's first unit.  After a wait that gave up
+  // it may be missing (stale or never-initialised memory): nothing outside the partial slots is
+  // read, the rows come out as zeros and the status word says so.
+  const bool entry_ok = cta_first >= 0 && n_cta >= 1 && n_cta <= a.grid && cta_first <= a.grid - n_cta &&
+                        (long long)sh + cta_first + n_cta <= (long long)a.n_slots;
+  if (!entry_ok) {
+    if (threadIdx.x == 0) atomicOr(a.status, CUDA_LLM_ST_INCOMPLETE);
+    n_cta = 0;
+    cta_first = 0;
+  } else if (direct) {
+    return;
+  }
   // a 16-row kernel leaves two results per sub-tile for a query of at most 8 rows (rows r, r + 8)
   const int dup = (a.helper_pairs && a.rows_max == 16 && a.group * qlen <= 8) ? 2 : 1;
   const int n_parts = n_cta * a.SUBS * dup;

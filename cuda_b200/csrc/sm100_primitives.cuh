@@ -2,7 +2,7 @@
 // waits, 1-D bulk (TMA) global->shared copies, warp-level f16 MMA, E4M3 -> f16
 // conversion and byte shuffles.
 //
-// Every wait in this file gives up after a fixed number of polls and reports failure to
+// Every wait in this file gives up after a bounded number of polls and reports failure to
 // its caller instead of spinning forever; callers turn that into a status word the host
 // reads (the reference's only wait primitive spins without bound,
 // cuda_compat.h:174-193 in the reference project).
@@ -47,12 +47,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false after kMaxPolls unsuccessful polls (each poll may itself suspend for up
-// to kSuspendHintNs, so the bound is of the order of a few seconds at most).
+// Bounded wait: false after kMaxPolls unsuccessful polls (each poll may itself suspend for up to
+// kSuspendHintNs, so the bound is of the order of a few seconds at most), or after kShortPolls of
+// them when `short_limit` is set (a run-time switch, so that a test can make a wait run out in
+// milliseconds; written as a second comparison against a constant because a run-time loop bound
+// costs the decode kernel a register it does not have).
 constexpr uint32_t kMaxPolls = 1u << 21;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+constexpr uint32_t kShortPolls = 1u << 12;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int short_limit) {
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (short_limit && i >= kShortPolls) break;
   }
   return false;
 }
@@ -217,21 +222,6 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-
-// ----------------------------------------------------------------------------------------
-// Warp MMA m16n8k32, E4M3 inputs, fp32 accumulate:  D(16x8) += A(16x32) * B(32x8)
-//   a0:(row g, k 4t..4t+3) a1:(row g+8, k 4t..4t+3) a2:(row g, k 4t+16..19) a3:(row g+8, k 4t+16..19)
-//   b0:(k 4t..4t+3, col g) b1:(k 4t+16..19, col g)      c as for m16n8k16
-// Products of two E4M3 values are exact in the fp32 accumulator.
-// ----------------------------------------------------------------------------------------
-__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                         uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // ----------------------------------------------------------------------------------------

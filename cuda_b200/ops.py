@@ -63,12 +63,31 @@ def _scale_mode(k_scale: torch.Tensor) -> int:
                        "or 4D E8M0 [blocks, heads, head_dim/32, page]")
 
 
+def _byte_cache_format(key_cache, value_cache, kv_format: Optional[str]) -> int:
+    """Element format of an 8-bit cache.  ``uint8`` / ``float8_e4m3fn`` bytes are E4M3 codes.  An
+    ``int8`` tensor keeps the reference's integer meaning (``fp8_paged_attention_kernel.cuh:102`` in
+    the reference project) unless ``kv_format='fp8_e4m3'`` states otherwise; the library has no
+    integer reading and refuses it rather than reinterpret the bytes silently."""
+    byte_types = (torch.int8, torch.uint8, torch.float8_e4m3fn)
+    if key_cache.dtype not in byte_types or value_cache.dtype not in byte_types:
+        raise RuntimeError("KV caches must be 8-bit quantized (int8 or uint8)")
+    if kv_format not in (None, "fp8_e4m3"):
+        raise RuntimeError(f"unknown kv_format {kv_format!r}: only 'fp8_e4m3' is provided")
+    if kv_format is None and torch.int8 in (key_cache.dtype, value_cache.dtype):
+        raise RuntimeError(
+            "int8 KV caches are not accepted: this library reads cache bytes as FP8-E4M3 codes, the reference "
+            "kernel reads them as integers (fp8_paged_attention_kernel.cuh:102). Pass uint8 / float8_e4m3fn "
+            "tensors, or kv_format='fp8_e4m3' if the int8 tensor holds E4M3 codes.")
+    return L.KV_FP8_E4M3
+
+
 def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, v_scale,
                                 block_tables, context_lens, softmax_scale=None, *,
                                 cu_q_lens: Optional[torch.Tensor] = None, max_q_len: int = 1,
                                 return_lse: bool = False, out: Optional[torch.Tensor] = None,
                                 workspace: Optional[torch.Tensor] = None, num_ctas: int = 0,
-                                check_status: bool = False, flags: int = 0):
+                                check_status: bool = False, flags: int = 0,
+                                kv_format: Optional[str] = None):
     """Decode attention over a paged FP8 / MXFP8 / MXFP4 KV cache.
 
     query ``[total_q, Hq, D]``; caches ``[num_blocks, Hkv, D, page]`` bytes (V may be packed
@@ -76,7 +95,10 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
     smaller than ``Hq`` (GQA: kv_head = q_head // (Hq // Hkv), the rule of
     ``fused_gqa_kernel.cuh:39-41`` in the reference project).  Bytes are E4M3 codes: this is
     the semantics the reference's own test specifies (``tests/test_kernels_misc.py:42-64``),
-    not the int8 cast its kernel performs.
+    not the int8 cast its kernel performs (``fp8_paged_attention_kernel.cuh:102``).  A
+    ``torch.uint8`` or ``torch.float8_e4m3fn`` cache is read that way; a ``torch.int8`` cache is
+    refused unless ``kv_format="fp8_e4m3"`` says that its bytes are E4M3 codes too, because a caller
+    of the reference with real int8 data would otherwise get different numbers without a word.
     """
     if not (query.is_cuda and key_cache_fp8.is_cuda and value_cache_fp8.is_cuda):
         raise RuntimeError("Inputs must be on CUDA")
@@ -88,9 +110,7 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
         raise RuntimeError("Query must be 3D [num_seqs, num_heads, head_dim]")
     if key_cache_fp8.dim() != 4 or value_cache_fp8.dim() != 4:
         raise RuntimeError("KV caches must be 4D [num_blocks, num_heads, head_dim, page_size]")
-    byte_types = (torch.int8, torch.uint8, torch.float8_e4m3fn)
-    if key_cache_fp8.dtype not in byte_types or value_cache_fp8.dtype not in byte_types:
-        raise RuntimeError("KV caches must be 8-bit quantized (int8 or uint8)")
+    k_format = _byte_cache_format(key_cache_fp8, value_cache_fp8, kv_format)
     if query.dtype not in _DTYPE:
         raise RuntimeError("Unsupported query scalar type for FP8 PagedAttention. "
                            "Supported: Float32, Float16, BFloat16.")
@@ -146,7 +166,7 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
             lse=_ptr(lse), workspace=ws.data_ptr(), workspace_bytes=ws.numel(),
             num_seqs=num_seqs, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page,
             max_blocks_per_seq=block_tables.shape[1], num_blocks=nb, max_q_len=max_q_len,
-            q_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[out.dtype], k_format=L.KV_FP8_E4M3,
+            q_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[out.dtype], k_format=k_format,
             v_format=v_format, scale_mode=mode, softmax_scale=scale, num_ctas=num_ctas, flags=flags)
         L.check(lib.cuda_llm_paged_decode(C.byref(p), _stream_ptr(query.device)), "cuda_llm_paged_decode")
         if check_status:

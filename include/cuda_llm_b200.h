@@ -36,6 +36,9 @@ extern "C" {
 #define CUDA_LLM_ST_BAD_CTX 2u     /* context length exceeds max_blocks_per_seq * page_size  */
 #define CUDA_LLM_ST_TIMEOUT 4u     /* a bounded wait gave up                                 */
 #define CUDA_LLM_ST_BAD_QLEN 8u    /* group * q_len exceeds the rows the launch was sized for */
+#define CUDA_LLM_ST_SCALE_RANGE 16u /* an E8M0 V scale byte of a live token is outside [32, 223] */
+#define CUDA_LLM_ST_INCOMPLETE 32u /* a (sequence, head group) was left without a result: its rows
+                                      are zeros (follows CUDA_LLM_ST_TIMEOUT)                     */
 
 /* bits of CudaLlmPagedDecodeParams.flags */
 #define CUDA_LLM_FLAG_SKIP_MERGE 1 /* launch the attention kernel only (profiling: sequences
@@ -47,8 +50,17 @@ extern "C" {
                                             model step for all layers).  The decode kernel is launched
                                             as a programmatic dependent and then plans its ranges and
                                             prefetches its first table entries while that kernel is
-                                            still finishing; query, K/V and the workspace are not
-                                            touched before it has finished either way. */
+                                            still finishing; query, K/V, the split partials and the
+                                            outputs are not touched before it has finished either way
+                                            (a finding of the plan, such as CUDA_LLM_ST_BAD_CTX, may be
+                                            OR-ed into the status word early). */
+#define CUDA_LLM_FLAG_TEST_STALL 128 /* failure-path test: the first CTA announces the bytes of its first
+                                        stage but never sends them, and every wait gives up after a few
+                                        thousand polls instead of seconds.  The waits run out, all warps
+                                        return, CUDA_LLM_ST_TIMEOUT (and CUDA_LLM_ST_INCOMPLETE for the rows
+                                        left without a result) is set; nothing faults or hangs.          */
+
+#ifdef CUDA_LLM_DIAGNOSTICS /* honoured only by a library built with -DCUDA_LLM_DIAGNOSTICS */
 #define CUDA_LLM_FLAG_DIAG_NO_MATH 2 /* diagnostics: stream the pages but skip the attention math
                                         (output is meaningless; measures the copy pipeline)   */
 #define CUDA_LLM_FLAG_DIAG_NO_COPY 4 /* diagnostics: do the attention math on stale shared memory,
@@ -62,6 +74,7 @@ extern "C" {
 #define CUDA_LLM_FLAG_DIAG_REVERSED 32      /* diagnostics: CTA i takes the unit range of CTA grid-1-i
                                               (same result; separates SM effects from data effects) */
 /* bits 8..11: diagnostics: cap the shared-memory ring at this many stages (0 = as many as fit) */
+#endif
 
 /* ---- enums ---------------------------------------------------------------------------- */
 enum CudaLlmDType { CUDA_LLM_F32 = 0, CUDA_LLM_F16 = 1, CUDA_LLM_BF16 = 2 };
@@ -139,12 +152,16 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* params, void* stream);
  * every GPU that loads the library holds until the process exits.  Nothing is allocated or freed,
  * here or in anything this calls.  Problems whose workspace exceeds the array (see
  * cuda_llm_paged_decode_workspace_bytes) are refused with CUDA_LLM_EWORKSPACE.  The first call on
- * a device looks up the array's device address; make that first call outside any stream capture.
- * All calls on a device share the one array: two calls that overlap on the GPU (different
- * streams) race on it, so keep them on one stream or order them with events.  The array keeps
- * the previous call's contents; the status word is cleared on every call. */
+ * a device looks up the array's device address and zeroes its status word; make that first call
+ * outside any stream capture.  All calls on a device share the one array: two calls that overlap
+ * on the GPU (different streams) race on it, so keep them on one stream or order them with events.
+ * The array keeps the previous call's contents; the status word keeps its bits until
+ * cuda_llm_static_decode_status reads (and clears) them. */
 int cuda_llm_paged_decode_static(const CudaLlmPagedDecodeParams* params, void* stream);
 size_t cuda_llm_static_scratch_bytes(void);
+/* No counterpart in the reference.  Read (and clear) the device status word of the built-in
+ * scratch of the current device; synchronises `stream`.  Allocates nothing. */
+int cuda_llm_static_decode_status(void* stream, uint32_t* status_out);
 
 /* Read (and clear) the device status word of a workspace; synchronises `stream`. */
 int cuda_llm_decode_status(void* workspace, void* stream, uint32_t* status_out);

@@ -82,6 +82,25 @@ def test_misaligned_and_unsupported(lib):
     assert lib.cuda_llm_paged_decode(C.byref(p), None) == L.EWORKSPACE
 
 
+def test_int8_caches_are_refused_not_reinterpreted():
+    """The reference kernel reads an int8 cache as integers (fp8_paged_attention_kernel.cuh:102 in the
+    reference project); this library reads bytes as E4M3 codes, so an int8 tensor is refused unless the
+    caller says its bytes are E4M3 codes."""
+    import torch
+    from cuda_b200 import ops
+    c8 = torch.zeros(2, 2, 64, 16, dtype=torch.int8)
+    with pytest.raises(RuntimeError, match="int8 KV caches are not accepted"):
+        ops._byte_cache_format(c8, c8, None)
+    with pytest.raises(RuntimeError, match="int8 KV caches are not accepted"):
+        ops._byte_cache_format(c8.view(torch.uint8), c8, None)
+    assert ops._byte_cache_format(c8, c8, "fp8_e4m3") == L.KV_FP8_E4M3
+    assert ops._byte_cache_format(c8.view(torch.uint8), c8.view(torch.float8_e4m3fn), None) == L.KV_FP8_E4M3
+    with pytest.raises(RuntimeError, match="8-bit quantized"):
+        ops._byte_cache_format(c8.half(), c8.half(), None)
+    with pytest.raises(RuntimeError, match="unknown kv_format"):
+        ops._byte_cache_format(c8, c8, "int8")
+
+
 def test_ops_fail_loudly_without_library(monkeypatch):
     monkeypatch.setattr(L, "_lib", None)
     monkeypatch.setattr(L, "LIB_PATH", "/nonexistent/libcuda_llm_b200.so")

@@ -59,3 +59,24 @@ def test_static_scratch_refuses_what_does_not_fit():
     rc = lib.cuda_llm_paged_decode_static(C.byref(p), torch.cuda.current_stream().cuda_stream)
     assert rc == L.EWORKSPACE
     assert b"16 MiB" in lib.cuda_llm_last_cuda_error()
+
+
+def test_static_scratch_status_is_readable():
+    """A block-table entry outside the pool through the allocation-free entry point: the finding
+    lands in the status word of the built-in scratch and cuda_llm_static_decode_status reads it."""
+    from cuda_b200 import _lib as L, workloads
+    lib = L.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    st = C.c_uint32(0xFFFFFFFF)
+    L.check(lib.cuda_llm_static_decode_status(stream, C.byref(st)), "cuda_llm_static_decode_status")
+    assert st.value == 0                       # the other tests of this file left nothing behind
+    wl = workloads.make_config(2, "cpu", batch=2, ctx_scale=1 / 16, seed=6)
+    wl.block_tables[1, 0] = 1_000_000
+    wl = wl.to("cuda")
+    out = torch.empty_like(wl.query)
+    L.check(lib.cuda_llm_paged_decode_static(C.byref(_params(L, wl, out, None)), stream),
+            "cuda_llm_paged_decode_static")
+    L.check(lib.cuda_llm_static_decode_status(stream, C.byref(st)), "cuda_llm_static_decode_status")
+    assert st.value & L.ST_BAD_BLOCK
+    L.check(lib.cuda_llm_static_decode_status(stream, C.byref(st)), "cuda_llm_static_decode_status")
+    assert st.value == 0                       # cleared by the read
