@@ -1,6 +1,7 @@
 """Benchmark of the paged FP8 decode-attention path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+                    [--no-extra-workloads]
 
 One step = one decode-attention pass over one batch of the workload (default: the
 Llama-3-8B-shaped FP8 paged decode configuration: batch 64, 32/8 heads, head_dim 128, page 16,
@@ -9,6 +10,13 @@ HBM throughput on the algorithmic K+V bytes (payload + scales of valid tokens on
 reference benchmark's own "effective KV GB/s" (benchmark_pytorch.py:160,611 in the reference
 project).  With N > 1 (torchrun, one rank per GPU) every rank holds its own batch (sequence
 sharding, no collective on the data path): weak scaling, value = all ranks' bytes / max time.
+
+After the headline workload the same ranks also time the other three sharded configurations
+(MXFP8 by KV-head shards, the long context by KV ranges with an NCCL all-gather and a merge, the
+continuous-batching mix by sequence shards; total work fixed, i.e. strong scaling) and report them
+under "workloads" in the same line, each with a parity figure of a sampled sequence against the
+CPU oracle.  Every timed loop is repeated until at least 200 ms have been measured; the numbers
+are medians over the repeats.
 
 Prints ONE JSON line on rank 0.
 """
@@ -34,8 +42,8 @@ AUX_WORKLOADS = ("pa16", "fd16")
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode-kernel launch,
-# from the ncu capture summarised in profiles/paged_decode_kernel_cfg2.md (traffic grows with the
-# bytes streamed, so the ratio carries over to the full-size launch)
+# from an ncu capture of a batch-16 launch of the same workload (traffic grows with the bytes
+# streamed, so the ratio carries over to the full-size launch)
 DRAM_TRAFFIC_PER_KV_BYTE = {"cfg2_llama8b_fp8_pertoken": 1.03}
 
 
@@ -196,10 +204,220 @@ def aux_workload(args, rank, world, local):
                       "gpu_launches": 2 * args.steps}), flush=True)
 
 
+MIN_TIMED_MS = 200.0
+
+
+class Bench:
+    """Device, process group and timing helpers shared by all legs of one run."""
+
+    def __init__(self, args, rank, world, local):
+        self.args, self.rank, self.world, self.local = args, rank, world, local
+        self.dev = torch.device("cuda", local)
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_blocks(self, fn, steps, min_total_ms=MIN_TIMED_MS):
+        """Time blocks of exactly `steps` calls (CUDA events on the launching stream, a barrier and a
+        device synchronise on both sides of every block) until `min_total_ms` have been measured,
+        three blocks at least; every block's time is the maximum over the ranks.  Returns the
+        per-step milliseconds of every block."""
+        blocks, total = [], 0.0
+        while len(blocks) < 3 or (total < min_total_ms and len(blocks) < 400):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.barrier()
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            self.barrier()
+            ms = e0.elapsed_time(e1)
+            if self.world > 1:                    # the ranks must agree on when to stop
+                import torch.distributed as dist
+                t = torch.tensor([ms], device=self.dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            blocks.append(ms / steps)
+            total += ms
+        return blocks
+
+    def sum_over_ranks(self, *vals):
+        if self.world == 1:
+            return [float(v) for v in vals]
+        import torch.distributed as dist
+        t = torch.tensor([float(v) for v in vals], device=self.dev, dtype=torch.float64)
+        dist.all_reduce(t)
+        return [float(x) for x in t.tolist()]
+
+
+def median(xs):
+    xs = sorted(xs)
+    n = len(xs)
+    return xs[n // 2] if n % 2 else 0.5 * (xs[n // 2 - 1] + xs[n // 2])
+
+
+def sample_parity(wl, out, kv_heads=None, want_partial=False):
+    """Parity of ONE sequence of the workload (the one of median context length) against the CPU
+    oracle: its pages are gathered through the block table, copied to the host and attended over in
+    fp32.  `kv_heads` restricts the check to the first KV heads (a 131072-token context over all heads
+    would cost the host tens of seconds).  Returns (max_abs, mean_abs, sequence, tokens) or, with
+    `want_partial`, the oracle's (out, lse) and the matching rows of `out`."""
+    from oracle import paged_decode_oracle as O
+    ctx = wl.context_lens.tolist()
+    order = sorted(range(len(ctx)), key=lambda i: (ctx[i], i))
+    s = order[len(order) // 2]
+    page = wl.page_size
+    n = max(1, (ctx[s] + page - 1) // page)
+    pages = wl.block_tables[s, :n].long()
+    hk = wl.num_kv_heads if kv_heads is None else min(kv_heads, wl.num_kv_heads)
+    group = wl.num_q_heads // wl.num_kv_heads
+
+    def take(t, mode):
+        if t is None:
+            return None
+        if mode == "per_head":
+            return t[:hk].cpu()
+        return t[pages][:, :hk].cpu()
+
+    kv = O.PagedKV(wl.key_cache[pages][:, :hk].cpu(), wl.value_cache[pages][:, :hk].cpu(),
+                   torch.arange(n, dtype=torch.int32).view(1, n), torch.tensor([ctx[s]], dtype=torch.int32),
+                   page, wl.head_dim, wl.k_format, wl.v_format, wl.k_scale_mode, wl.v_scale_mode,
+                   take(wl.k_scale, wl.k_scale_mode), take(wl.v_scale, wl.v_scale_mode))
+    if wl.cu_q_lens is None:
+        r0, r1, cu = s, s + 1, None
+    else:
+        c = wl.cu_q_lens.tolist()
+        r0, r1 = c[s], c[s + 1]
+        cu = torch.tensor([0, r1 - r0], dtype=torch.int32)
+    q = wl.query[r0:r1, :hk * group].cpu()
+    got = out[r0:r1, :hk * group].float().cpu()
+    if want_partial:
+        ro, rl = O.ref_paged_decode(q, kv, wl.softmax_scale, cu, return_lse=True)
+        return ro, rl, got, s
+    ref = O.ref_paged_decode(q, kv, wl.softmax_scale, cu)
+    err = (got - ref).abs()
+    return float(err.max()), float(err.mean()), s, ctx[s]
+
+
+def parity_record(mx, mean, s, tokens, note=""):
+    return {"max_abs": mx, "mean_abs": mean, "ok": bool(mx <= 2e-2 and mean <= 2e-3),
+            "tolerance": "max-abs <= 2e-2, mean-abs <= 2e-3 (bf16 output)", "sequence": s, "tokens": tokens,
+            "against": "CPU oracle (gather pages, dequantise, fp32 attention)" + note}
+
+
+def build_leg(B, cfg_id, args, batch=None, ctx_scale=1.0):
+    """The workload of configuration `cfg_id` as this rank sees it, and how it is sharded."""
+    from cuda_b200 import workloads
+    rank, world = B.rank, B.world
+    seed = 1000 + cfg_id + 7919 * rank
+    kw = dict(batch=batch, ctx_scale=ctx_scale, seed=seed, poison=False)
+    scaling, split_ctx = "strong", False
+    if cfg_id == 2:
+        # weak scaling: the job holds `world` batches; every rank draws the same length list and
+        # keeps the sequences the balancer deals to it (its own pages and tables, no collective)
+        scaling = "weak"
+        parallelism = f"sequence-sharded x{world}: {world} batches dealt longest-first by context length"
+        if world > 1:
+            kw.update(batch=(batch or 64) * world, len_seed=1002, deal=(world, rank))
+    elif cfg_id == 3:
+        parallelism = f"KV-head-sharded x{world} (no collective)"
+        kw.update(head_shards=world, len_seed=1003)
+    elif cfg_id == 4:
+        parallelism = (f"KV-range-sharded x{world}: local decode, one NCCL all-gather of (out | lse), merge; "
+                       "issued from one C++ call" if world > 1 else "single GPU: decode + split merge")
+        kw.update(ctx_scale=ctx_scale / world, seed=1000 + cfg_id + 7919 * rank)
+        split_ctx = world > 1
+    elif cfg_id == 5:
+        parallelism = f"sequence-sharded x{world}, dealt longest-first by context length (no collective)"
+        if world > 1:
+            kw.update(batch=(batch or 256), len_seed=1005, deal=(world, rank))
+    else:
+        parallelism = "replicas"
+    wl = workloads.make_config(cfg_id, B.dev, **kw)
+    if split_ctx:                                   # one query attends every rank's KV range
+        import torch.distributed as dist
+        dist.broadcast(wl.query, src=0)
+    return wl, scaling, parallelism, split_ctx
+
+
+def run_extra_leg(B, cfg_id, args):
+    """Time one of the other configurations on the same ranks: resident step (decode + merge, and for
+    the split context the all-gather) with CUDA events, median over repeats, plus a parity sample."""
+    from cuda_b200 import ops, sharding
+    wl, scaling, parallelism, split_ctx = build_leg(B, cfg_id, args)
+    STABLE = ops.L.FLAG_STABLE_METADATA
+    need = ops.L.load().cuda_llm_paged_decode_workspace_bytes(
+        wl.num_seqs, wl.num_q_heads, wl.num_kv_heads, wl.head_dim, wl.page_size, wl.max_q_len, 0)
+    ws = torch.zeros(need, dtype=torch.uint8, device=B.dev)
+    out = torch.empty_like(wl.query)
+    rec = {}
+    if split_ctx:
+        dec = sharding.SplitContextDecoder(wl)
+        step = lambda: dec(wl, flags=STABLE)
+        part = torch.empty(wl.query.shape, dtype=torch.float32, device=B.dev)
+        local_only = lambda: ops.run_workload(wl, return_lse=True, out=part, workspace=ws, flags=STABLE)
+    else:
+        step = lambda: ops.run_workload(wl, out=out, workspace=ws, flags=STABLE)
+        local_only = None
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    steps = max(5, min(args.steps, 100))
+    ms = median(B.timed_blocks(step, steps))
+    if local_only is not None:
+        for _ in range(3):
+            local_only()
+        ms_local = median(B.timed_blocks(local_only, steps))
+        rec["split_context_ms"] = {"local_decode_and_split_merge": ms_local, "all_gather_and_merge": ms - ms_local,
+                                   "collective_share": (ms - ms_local) / ms,
+                                   "all_gather_bytes_per_rank": wl.query.shape[0] * wl.num_q_heads * (wl.head_dim + 1) * 4}
+    st = ops.decode_status(dec.workspace if split_ctx else ws)
+    kv_bytes = wl.kv_bytes()
+    tot_bytes, tot_q = B.sum_over_ranks(kv_bytes, wl.query.shape[0] if not split_ctx else
+                                        (wl.query.shape[0] if B.rank == 0 else 0))
+    # parity of one sampled sequence (per rank; the worst rank is reported)
+    result = step()
+    torch.cuda.synchronize()
+    if split_ctx:
+        import torch.distributed as dist
+        ro, rl, got, s = sample_parity(wl, result, kv_heads=1, want_partial=True)
+        po = [torch.empty_like(ro, device=B.dev) for _ in range(B.world)]
+        pl = [torch.empty_like(rl, device=B.dev) for _ in range(B.world)]
+        dist.all_gather(po, ro.to(B.dev))
+        dist.all_gather(pl, rl.to(B.dev))
+        from oracle import paged_decode_oracle as O
+        ref, _ = O.merge_partials(torch.stack([x.cpu() for x in po]), torch.stack([x.cpu() for x in pl]))
+        err = (got - ref).abs()
+        mx, mean, tokens = float(err.max()), float(err.mean()), int(wl.context_lens[s]) * B.world
+        note = "; per-rank oracle partials of KV head 0, all-gathered and merged by the oracle"
+    else:
+        mx, mean, s, tokens = sample_parity(wl, result, kv_heads=(1 if cfg_id == 4 else None))
+        note = " (KV head 0 only)" if cfg_id == 4 else ""
+    if B.world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([mx, mean, float(st)], device=B.dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        mx, mean, st = float(t[0]), float(t[1]), int(t[2])
+    peak, _ = measured_peak()
+    value = tot_bytes / (ms * 1e-3) / 1e12
+    rec.update({
+        "workload": wl.name, "ms_per_step": ms, "kv_tbps": value, "frac_of_measured_peak": value * 1e3 / (peak * B.world),
+        "pct_of_nominal_8TBs": 100.0 * value * 1e3 / (NOMINAL_HBM_GBS * B.world),
+        "tokens_per_s": tot_q / (ms * 1e-3), "scaling": scaling, "parallelism": parallelism,
+        "kv_bytes_per_rank": kv_bytes, "kv_bytes_total": tot_bytes, "batch_per_rank": wl.num_seqs,
+        "steps_per_block": steps, "device_status": st,
+        "parity": parity_record(mx, mean, s, tokens, note),
+    })
+    return rec
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + list(AUX_WORKLOADS))
@@ -207,6 +425,8 @@ def main():
     ap.add_argument("--ctx-scale", type=float, default=1.0)
     ap.add_argument("--cpu-budget-s", type=float, default=15.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra-workloads", action="store_true",
+                    help="skip the cfg3 / cfg4 / cfg5 legs that follow the headline workload")
     ap.add_argument("--kernel-only", action="store_true", help="only the attention-kernel loop (ncu)")
     args = ap.parse_args()
     rank, world, local = dist_env()
@@ -255,103 +475,62 @@ def main():
     # ------------------------------------------------------------------ our arm (GPU)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
     torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+    B = Bench(args, rank, world, local)
+    dev = B.dev
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    from cuda_b200 import ops
+    from cuda_b200 import ops, sharding
     ops.L.load()
 
-    # How the workload spreads over N GPUs (north star): cfg2 one batch per rank (weak scaling);
-    # cfg3 KV-head shards, cfg5 the batch dealt over the ranks, cfg4 KV ranges of the same
-    # contexts with an all-gather + merge (strong scaling: total work fixed).
-    scaling, parallelism = "weak", f"sequence-sharded x{world}: {world} batches dealt longest-first by context length"
-    kw = dict(batch=args.batch, ctx_scale=args.ctx_scale, seed=seed, poison=False)
-    if cfg_id == 2 and world > 1:
-        # weak scaling: the job holds `world` batches; every rank draws the same length list and
-        # keeps the sequences the balancer deals to it (its own pages and tables, no collective)
-        kw.update(batch=(args.batch or 64) * world, len_seed=1002, deal=(world, rank))
-    split_ctx = False
-    if cfg_id == 3:
-        scaling, parallelism = "strong", f"KV-head-sharded x{world}"
-        kw.update(head_shards=world, len_seed=1003)
-    elif cfg_id == 4:
-        scaling, parallelism = "strong", f"KV-range-sharded x{world}, all-gather + merge"
-        kw.update(ctx_scale=args.ctx_scale / world)
-        split_ctx = world > 1
-    elif cfg_id == 5:
-        scaling, parallelism = "strong", f"sequence-sharded x{world}, dealt longest-first by context length"
-        if world > 1:
-            kw.update(batch=(args.batch or 256), len_seed=1005, deal=(world, rank))
-    wl = workloads.make_config(cfg_id, dev, **kw)
+    wl, scaling, parallelism, split_ctx = build_leg(B, cfg_id, args, batch=args.batch, ctx_scale=args.ctx_scale)
     kv_bytes = wl.kv_bytes()
     q_tokens = wl.query.shape[0]
     need = ops.L.load().cuda_llm_paged_decode_workspace_bytes(
         wl.num_seqs, wl.num_q_heads, wl.num_kv_heads, wl.head_dim, wl.page_size, wl.max_q_len, 0)
     ws = torch.zeros(need, dtype=torch.uint8, device=dev)
     out = torch.empty_like(wl.query)
-    from cuda_b200 import sharding
+    dec = sharding.SplitContextDecoder(wl) if split_ctx else None
 
     # In the resident loops the step inputs (lengths, block tables) are not rewritten between calls,
     # which is what a model does across its layers within one step: the library may then plan
-    # while the previous kernel drains (CUDA_LLM_FLAG_STABLE_METADATA).  The end-to-end legs copy
-    # fresh inputs every step and do not make that promise.
+    # while the previous kernel drains (CUDA_LLM_FLAG_STABLE_METADATA).  The step time without that
+    # promise is measured beside it.  The end-to-end legs copy fresh inputs every step and do not
+    # make the promise.
     STABLE = ops.L.FLAG_STABLE_METADATA
 
-    def step(flags=0):
-        flags |= STABLE
+    def step(flags=STABLE):
         if split_ctx:
-            part = torch.empty(wl.query.shape, dtype=torch.float32, device=dev)
-            return sharding.decode_split_context(
-                wl, partial_fn=lambda w: ops.run_workload(w, return_lse=True, out=part, workspace=ws))
+            return dec(wl, flags=flags)
         return ops.run_workload(wl, out=out, workspace=ws, flags=flags)
-
-    def barrier():
-        if world > 1:
-            import torch.distributed as dist
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, iters):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            import torch.distributed as dist
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
 
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
-    st = ops.decode_status(ws)
+    st = ops.decode_status(dec.workspace if split_ctx else ws)
     assert st == 0, f"device status 0x{st:x}"
 
     if args.kernel_only:
-        ms = timed(lambda: step(ops.L.FLAG_SKIP_MERGE), args.steps)
+        ms = median(B.timed_blocks(lambda: ops.run_workload(wl, out=out, workspace=ws,
+                                                            flags=ops.L.FLAG_SKIP_MERGE | STABLE), args.steps, 0.0))
         if rank == 0:
-            print(json.dumps({"kernel_only_ms": ms / args.steps, "kv_bytes": kv_bytes,
-                              "GBs": kv_bytes / (ms / args.steps) / 1e6}), flush=True)
+            print(json.dumps({"kernel_only_ms": ms, "kv_bytes": kv_bytes, "GBs": kv_bytes / ms / 1e6}), flush=True)
         return
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    # (1) whole step resident in HBM: attention kernel + split merge
-    ms_total = timed(step, args.steps)
+    # (1) whole step resident in HBM: attention kernel + split merge (+ all-gather and merge when split)
+    blocks_total = B.timed_blocks(step, args.steps)
+    ms_step = median(blocks_total)
     # (2) the dominant kernel alone (roofline numerator / denominator)
-    ms_kernel = timed(lambda: ops.run_workload(wl, out=out, workspace=ws, flags=ops.L.FLAG_SKIP_MERGE | STABLE),
-                      args.steps) / args.steps
+    ms_kernel = median(B.timed_blocks(
+        lambda: ops.run_workload(wl, out=out, workspace=ws, flags=ops.L.FLAG_SKIP_MERGE | STABLE), args.steps))
     step()
+    # (2b) the same whole step without the stable-metadata promise
+    ms_step_unflagged = median(B.timed_blocks(lambda: step(0), args.steps))
     # (3) end to end through the public op with host buffers: the step's inputs (query, block
-    #     tables, context lengths, query offsets) come from pinned host memory, the result goes back
+    #     tables, context lengths, query offsets) come from pinned host memory, the result goes back.
     #     The inputs sit in ONE pinned staging buffer and go over in one copy per step (a serving
     #     loop assembles its step inputs in such a buffer anyway); the device tensors are views.
     srcs = [wl.query, wl.block_tables, wl.context_lens] + ([wl.cu_q_lens] if wl.cu_q_lens is not None else [])
@@ -373,10 +552,7 @@ def main():
         dev_stage.copy_(host_stage, non_blocking=True)
         if split_ctx:
             import dataclasses
-            lw = dataclasses.replace(wl, query=dev_in[0], block_tables=dev_in[1], context_lens=dev_in[2])
-            part = torch.empty(wl.query.shape, dtype=torch.float32, device=dev)
-            o = sharding.decode_split_context(
-                lw, partial_fn=lambda w: ops.run_workload(w, return_lse=True, out=part, workspace=ws))
+            o = dec(dataclasses.replace(wl, query=dev_in[0], block_tables=dev_in[1], context_lens=dev_in[2]))
         else:
             o = ops.fp8_paged_attention_forward(dev_in[0], wl.key_cache, wl.value_cache, wl.k_scale, wl.v_scale,
                                                 dev_in[1], dev_in[2], wl.softmax_scale, cu_q_lens=dev_cu,
@@ -385,7 +561,7 @@ def main():
 
     for _ in range(3):
         e2e_step()
-    ms_e2e = timed(e2e_step, args.steps)
+    ms_e2e = median(B.timed_blocks(e2e_step, args.steps))
 
     # (4) the same end-to-end step double-buffered, as a serving loop with two batches in flight
     #     runs it: the copies of step i+1 (other staging buffer, copy streams) overlap the kernels
@@ -437,18 +613,49 @@ def main():
         for _ in range(4):
             e2e_pipe_step()
         torch.cuda.synchronize()
-        ms_e2e_pipe = timed(e2e_pipe_run, 1)
+        ms_e2e_pipe = median(B.timed_blocks(e2e_pipe_run, 1)) / args.steps
     clocks = sampler.stop() if rank == 0 else None
-    st = ops.decode_status(ws)
+    st = ops.decode_status(dec.workspace if split_ctx else ws)
     assert st == 0, f"device status 0x{st:x}"
 
-    # totals over ranks
-    tot_bytes, tot_q = float(kv_bytes), float(q_tokens)
-    if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([tot_bytes, tot_q], device=dev, dtype=torch.float64)
-        dist.all_reduce(t)
-        tot_bytes, tot_q = float(t[0]), float(t[1])
+    # parity gate of the headline workload: one sampled sequence against the CPU oracle
+    result = step()
+    torch.cuda.synchronize()
+    if split_ctx:
+        parity = None                                  # covered by the cfg4 leg's own record
+    else:
+        mx, mean, s_id, tokens = sample_parity(wl, result, kv_heads=(1 if cfg_id == 4 else None))
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([mx, mean], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            mx, mean = float(t[0]), float(t[1])
+        parity = parity_record(mx, mean, s_id, tokens)
+        assert parity["ok"], f"parity gate failed: {parity}"
+
+    tot_bytes, tot_q = B.sum_over_ranks(kv_bytes, q_tokens if not (split_ctx and rank) else 0)
+    meta = {"name": wl.name, "batch": wl.num_seqs, "heads": f"{wl.num_q_heads}q/{wl.num_kv_heads}kv",
+            "head_dim": wl.head_dim, "page_size": wl.page_size, "kv_tokens": int(wl.context_lens.sum().item()),
+            "pool_pages": wl.meta["pool_pages"]}
+    cpu_baseline = None
+    if not args.no_cpu_baseline and world == 1:
+        torch.set_num_threads(os.cpu_count() or 1)
+        t, b, q, n = cpu_reference_run(wl.to("cpu"), args.cpu_budget_s)
+        cpu_baseline = {"value": b / t / 1e12, "unit": "TB/s", "cores": torch.get_num_threads(),
+                        "kind": "port", "tokens_per_s": q / t,
+                        "sample": f"{n} sequence passes over the same batch of {wl.num_seqs} ({n / wl.num_seqs:.1f} batches), {t:.1f} s"}
+
+    # the other sharded configurations on the same ranks
+    extra = {}
+    if cfg_id == 2 and not args.no_extra_workloads and args.batch is None and args.ctx_scale == 1.0:
+        del wl, out, ws, result
+        torch.cuda.empty_cache()
+        for other in (3, 4, 5):
+            rec = run_extra_leg(B, other, args)
+            extra[rec.pop("workload")] = rec
+            torch.cuda.empty_cache()
+        wl = None
+
     if rank != 0:
         if world > 1:
             import torch.distributed as dist
@@ -456,9 +663,9 @@ def main():
         return
 
     peak, peak_src = measured_peak()
-    ms_step = ms_total / args.steps
     value = tot_bytes / (ms_step * 1e-3) / 1e12
     achieved = kv_bytes / (ms_kernel * 1e-3) / 1e9
+    name = meta["name"]
     line = {
         "metric": "paged_fp8_decode_kv_hbm_throughput", "value": value, "unit": "TB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -466,37 +673,45 @@ def main():
         "data": "synthetic", "tokens_per_s": tot_q / (ms_step * 1e-3),
         "pct_of_nominal_8TBs": 100.0 * value * 1e3 / (NOMINAL_HBM_GBS * world),
         "pct_of_measured_copy_peak": 100.0 * value * 1e3 / (peak * world),
-        "config": {"workload": wl.name, "batch_per_gpu": wl.num_seqs, "heads": f"{wl.num_q_heads}q/{wl.num_kv_heads}kv",
-                   "head_dim": wl.head_dim, "page_size": wl.page_size,
-                   "kv_tokens_per_gpu": int(wl.context_lens.sum().item()), "kv_bytes_per_gpu": kv_bytes,
-                   "pool_pages": wl.meta["pool_pages"], "parallelism": parallelism,
+        "timing": {"method": "CUDA events around blocks of `steps` back-to-back steps, barrier + synchronize on both "
+                             "sides of every block, max over ranks per block, median over blocks",
+                   "blocks": len(blocks_total), "min_timed_ms": MIN_TIMED_MS,
+                   "ms_per_step_min": min(blocks_total), "ms_per_step_max": max(blocks_total)},
+        "stable_metadata": {"resident_loops_set_CUDA_LLM_FLAG_STABLE_METADATA": True,
+                            "ms_per_step_with_flag": ms_step, "ms_per_step_without_flag": ms_step_unflagged,
+                            "value_without_flag": tot_bytes / (ms_step_unflagged * 1e-3) / 1e12,
+                            "note": "opt-in promise that the kernel in front of the call does not write lengths or "
+                                    "block tables (true across the layers of one model step); `value` and `roofline` "
+                                    "are measured with it, the end-to-end legs without it"},
+        "config": {"workload": name, "batch_per_gpu": meta["batch"], "heads": meta["heads"],
+                   "head_dim": meta["head_dim"], "page_size": meta["page_size"],
+                   "kv_tokens_per_gpu": meta["kv_tokens"], "kv_bytes_per_gpu": kv_bytes,
+                   "pool_pages": meta["pool_pages"], "parallelism": parallelism,
                    "l2": "inputs larger than L2 (KV working set per step >> 126 MB), no flush needed"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src, "kernel": "paged_decode_kernel", "kernel_ms": ms_kernel,
                      "traffic": None},
-        "e2e": {"value": tot_bytes / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TB/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps,
+        "e2e": {"value": tot_bytes / (ms_e2e * 1e-3) / 1e12, "unit": "TB/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
                 "note": "KV cache resident in HBM (it is decode state, like weights); per-step inputs "
                         "(query, block tables, context lengths) from pinned host memory, output read back; "
                         "value = copy, kernels, copy back strictly one after the other on one stream",
                 "double_buffered": (None if ms_e2e_pipe is None else
-                                    {"value": tot_bytes / (ms_e2e_pipe / args.steps * 1e-3) / 1e12, "unit": "TB/s",
-                                     "ms_per_step": ms_e2e_pipe / args.steps,
+                                    {"value": tot_bytes / (ms_e2e_pipe * 1e-3) / 1e12, "unit": "TB/s",
+                                     "ms_per_step": ms_e2e_pipe,
                                      "note": "same copies every step, two staging buffers and copy streams: "
                                              "the copies of step i+1 overlap the kernels of step i"})},
-        "gpu_launches": (3 if split_ctx else 2) * args.steps,
+        "gpu_launches": (4 if split_ctx else 2) * args.steps,
+        "parity": parity,
+        "workloads": extra,
         "clocks": clocks,
     }
-    ratio = DRAM_TRAFFIC_PER_KV_BYTE.get(wl.name)
+    ratio = DRAM_TRAFFIC_PER_KV_BYTE.get(name)
     if ratio is not None:
         line["roofline"]["traffic"] = ratio * kv_bytes
         line["roofline"]["traffic_source"] = "ncu dram__bytes_read+write of a batch-16 launch, scaled by KV bytes"
-    if not args.no_cpu_baseline:
-        torch.set_num_threads(os.cpu_count() or 1)
-        t, b, q, n = cpu_reference_run(wl.to("cpu"), args.cpu_budget_s)
-        line["cpu_baseline"] = {"value": b / t / 1e12, "unit": "TB/s", "cores": torch.get_num_threads(),
-                                "kind": "port", "tokens_per_s": q / t,
-                                "sample": f"{n} sequence passes over the same batch of {wl.num_seqs} ({n / wl.num_seqs:.1f} batches), {t:.1f} s"}
+    if cpu_baseline is not None:
+        line["cpu_baseline"] = cpu_baseline
     print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist

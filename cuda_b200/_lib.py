@@ -52,6 +52,9 @@ SYMBOLS = {
     "cuda_llm_decode_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]),
     "cuda_llm_merge_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
                                           C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
+    "cuda_llm_split_context_exchange_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
+    "cuda_llm_split_context_decode": (C.c_int, [C.POINTER(PagedDecodeParams), C.c_void_p, C.c_int32, C.c_int32,
+                                                C.c_void_p, C.c_size_t, C.c_void_p]),
     "cuda_llm_dequant_pages": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                          C.c_void_p]),

@@ -83,13 +83,64 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
     objs = [os.path.join(OBJ, u[:-3] + ".o") for u in units]
     if jobs or not os.path.exists(LIB):
         cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
-                                                     "-lcudart"]
+                                                     "-lcudart", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     return LIB
 
 
+EXT_SRC = os.path.join(HERE, "ext", "fused_online_softmax_cuda.cpp")
+EXT_DIR = os.path.join(HERE, "compat")
+
+
+def extension_path() -> str:
+    import sysconfig
+    return os.path.join(EXT_DIR, "fused_online_softmax_cuda" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_extension(verbose: bool = False, force: bool = False) -> str:
+    """Compile the PyTorch extension ``fused_online_softmax_cuda`` (the reference's module name,
+    ``setup.py:128`` in the reference project) from ``ext/fused_online_softmax_cuda.cpp`` with the host
+    compiler and link it against ``libcuda_llm_b200.so`` (found at run time through an ``$ORIGIN``
+    rpath).  The product lands in ``cuda_b200/compat``, the directory a caller puts on ``sys.path``."""
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as C
+    lib = build(verbose=verbose)
+    out = extension_path()
+    stamp = out + ".stamp"
+    want = _digest([EXT_SRC, os.path.join(ROOT, "include", "cuda_llm_b200.h")]) + torch.__version__
+    if not force and os.path.exists(out) and os.path.exists(stamp) and open(stamp).read() == want:
+        return out
+    try:
+        inc = C.include_paths(device_type="cuda")
+        libdirs = C.library_paths(device_type="cuda")
+    except TypeError:                              # older signature
+        inc, libdirs = C.include_paths(cuda=True), C.library_paths(cuda=True)
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-DTORCH_EXTENSION_NAME=fused_online_softmax_cuda", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           "-I", os.path.join(ROOT, "include"), "-I", sysconfig.get_paths()["include"]]
+    for i in inc:
+        cmd += ["-isystem", i]
+    cmd += [EXT_SRC, "-o", out, "-L", LIBDIR, "-lcuda_llm_b200", "-Wl,-rpath,$ORIGIN/../lib"]
+    for d in libdirs:
+        cmd += ["-L", d]
+    cmd += ["-Wl,-rpath," + libdirs[0], "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+            "-lcudart"]
+    if verbose:
+        print("[build] fused_online_softmax_cuda extension", flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"extension build failed:\n{r.stdout}\n{r.stderr[-4000:]}")
+    with open(stamp, "w") as f:
+        f.write(want)
+    return out
+
+
 if __name__ == "__main__":
     path = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
     print(path)
+    if "--no-extension" not in sys.argv:
+        print(build_extension(verbose=True, force="--force" in sys.argv))

@@ -32,6 +32,8 @@ static int fail(int code, const char* msg) {
   return code;
 }
 
+void set_error_message(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct Layout {

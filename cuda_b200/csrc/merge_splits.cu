@@ -26,18 +26,20 @@ cudaError_t launch_merge_splits(const DecodeArgs& a, int page, int decode_grid, 
 template cudaError_t launch_merge_splits<64>(const DecodeArgs&, int, int, cudaStream_t);
 template cudaError_t launch_merge_splits<128>(const DecodeArgs&, int, int, cudaStream_t);
 
-// parts_out [P, rows, D] fp32, parts_lse [P, rows] natural log.  One warp per row.
+// Part p holds out [rows, D] fp32 at parts_out + p * part_stride and lse [rows] (natural log) at
+// parts_lse + p * part_stride (strides in floats).  One warp per row.
 template <int D>
 __global__ void __launch_bounds__(128)
 merge_partials_kernel(const float* __restrict__ parts_out, const float* __restrict__ parts_lse,
-                      int num_parts, long long rows, void* out, int out_dtype, float* lse) {
+                      size_t out_stride, size_t lse_stride, int num_parts, long long rows, void* out,
+                      int out_dtype, float* lse) {
   const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   constexpr int VPL = D / 32;
   constexpr float LOG2E = 1.4426950408889634f;
   float mx = -__builtin_huge_valf();
-  for (int p = lane; p < num_parts; p += 32) mx = fmaxf(mx, parts_lse[(size_t)p * rows + row]);
+  for (int p = lane; p < num_parts; p += 32) mx = fmaxf(mx, parts_lse[(size_t)p * lse_stride + row]);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   const float mu = (mx == -__builtin_huge_valf()) ? 0.f : mx;
@@ -48,13 +50,13 @@ merge_partials_kernel(const float* __restrict__ parts_out, const float* __restri
   // weights 32 parts at a time (one per lane), then independent row loads
   for (int base = 0; base < num_parts; base += 32) {
     const int mine = base + lane;
-    const float wl = mine < num_parts ? fast_exp2((parts_lse[(size_t)mine * rows + row] - mu) * LOG2E) : 0.f;
+    const float wl = mine < num_parts ? fast_exp2((parts_lse[(size_t)mine * lse_stride + row] - mu) * LOG2E) : 0.f;
     const int cnt = min(32, num_parts - base);
 #pragma unroll 4
     for (int j = 0; j < cnt; ++j) {
       const float w = __shfl_sync(0xffffffffu, wl, j);
       wsum += w;
-      const float* po = parts_out + ((size_t)(base + j) * rows + row) * D + lane * VPL;
+      const float* po = parts_out + (size_t)(base + j) * out_stride + (size_t)row * D + lane * VPL;
 #pragma unroll
       for (int v = 0; v < VPL; ++v) acc[v] = fmaf(w, po[v], acc[v]);
     }
@@ -66,16 +68,31 @@ merge_partials_kernel(const float* __restrict__ parts_out, const float* __restri
   if (lse && lane == 0) lse[row] = wsum > 0.f ? mu + logf(wsum) : -__builtin_huge_valf();
 }
 
+cudaError_t launch_merge_partials_strided(const float* parts_out, const float* parts_lse, size_t part_stride,
+                                          int num_parts, long long rows, int head_dim, void* out, int out_dtype,
+                                          float* lse, cudaStream_t st) {
+  if (rows == 0) return cudaSuccess;
+  const int grid = (int)((rows + 3) / 4);
+  if (head_dim == 64)
+    merge_partials_kernel<64><<<grid, 128, 0, st>>>(parts_out, parts_lse, part_stride, part_stride, num_parts,
+                                                    rows, out, out_dtype, lse);
+  else
+    merge_partials_kernel<128><<<grid, 128, 0, st>>>(parts_out, parts_lse, part_stride, part_stride, num_parts,
+                                                     rows, out, out_dtype, lse);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_merge_partials(const float* parts_out, const float* parts_lse, int num_parts,
                                   long long rows, int head_dim, void* out, int out_dtype,
                                   float* lse, cudaStream_t st) {
   if (rows == 0) return cudaSuccess;
   const int grid = (int)((rows + 3) / 4);
+  const size_t os = (size_t)rows * head_dim, ls = (size_t)rows;  // dense [P, rows, D] and [P, rows]
   if (head_dim == 64)
-    merge_partials_kernel<64><<<grid, 128, 0, st>>>(parts_out, parts_lse, num_parts, rows, out,
+    merge_partials_kernel<64><<<grid, 128, 0, st>>>(parts_out, parts_lse, os, ls, num_parts, rows, out,
                                                     out_dtype, lse);
   else
-    merge_partials_kernel<128><<<grid, 128, 0, st>>>(parts_out, parts_lse, num_parts, rows, out,
+    merge_partials_kernel<128><<<grid, 128, 0, st>>>(parts_out, parts_lse, os, ls, num_parts, rows, out,
                                                      out_dtype, lse);
   return cudaGetLastError();
 }

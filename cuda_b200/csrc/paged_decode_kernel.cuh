@@ -111,7 +111,7 @@ struct DecodeArgs {
   int n_stages;
   int grid, n_slots;    // CTAs of the decode launch; partial-result slots in the workspace
   int short_waits;      // every mbarrier wait gives up after kShortPolls polls instead of kMaxPolls
-  int stall_test;       // failure-path test: CTA 0 arms its first stage but issues no copies for it
+  int stall_test;       // failure-path test: the first stage of the launch is armed but no copies are issued for it
   uint32_t stage_bytes, off_v, off_ks, off_vs;
   uint32_t k_page_stride, v_page_stride, ks_page_stride, vs_page_stride;  // smem, per page
   uint32_t k_chunk, v_chunk, ks_chunk, vs_chunk;                          // bytes per page copy
@@ -487,7 +487,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       seg_fresh = false;
       const uint32_t fb = full_bar + 8 * slot;
       // failure-path test: the bytes are announced but never sent, so the consumers' wait runs out
-      const bool stalled = a.stall_test && blockIdx.x == 0 && it == 0;
+      // (the very first unit of the launch: its cost position is the gap in front of it)
+      const bool stalled = a.stall_test && ic.pos == kSegGap;
       const bool no_copy = B200_DIAG((a.debug & 2) != 0);  // diagnostics: math on whatever shared memory holds
       // the query rows of a new (sequence, head group) travel with its first stage, so that the
       // consumers find them in shared memory instead of waiting for a global load with the ring full
@@ -1014,8 +1015,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             // va[0], va[1]: rows g, g+8 of O m-tile 2dp; va[2], va[3]: of m-tile 2dp+1 (one scale block)
             uint32_t s02 = 0u, s13 = 0u;
             if (MX) {
-              // E8M0 of tokens 4t..4t+3, block dp (a dead slot gives a finite factor; its P is 0)
-              const uint32_t e = lds32(sb + vs_mx[mt] + dp * PAGE);
+              // E8M0 of tokens 4t..4t+3, block dp.  A dead slot may hold any byte: it takes its token's
+              // reference exponent (127), or the 16-bit lane beside it would be overrun
+              uint32_t e = lds32(sb + vs_mx[mt] + dp * PAGE);
+              if (tail) e = (e & vmask[mt]) | (0x7f7f7f7fu & ~vmask[mt]);
               s02 = e8m0_rel_pair_to_f16x2(prmt(e, 0u, 0x4140), c02[MX ? mt : 0]);  // tokens 4t, 4t+1
               s13 = e8m0_rel_pair_to_f16x2(prmt(e, 0u, 0x4342), c13[MX ? mt : 0]);  // tokens 4t+2, 4t+3
             }
@@ -1041,7 +1044,8 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             // m-tiles 4dp, 4dp+1 share scale block 2dp, m-tiles 4dp+2, 4dp+3 share block 2dp+1
 #pragma unroll
             for (int bb = 0; bb < 2; ++bb) {
-              const uint32_t e = lds32(sb + vs_mx[mt] + (2 * dp + bb) * PAGE);
+              uint32_t e = lds32(sb + vs_mx[mt] + (2 * dp + bb) * PAGE);
+              if (tail) e = (e & vmask[mt]) | (0x7f7f7f7fu & ~vmask[mt]);
               const uint32_t s02 = e8m0_rel_pair_to_f16x2(prmt(e, 0u, 0x4240), c02[MX ? mt : 0]);
               const uint32_t s13 = e8m0_rel_pair_to_f16x2(prmt(e, 0u, 0x4341), c13[MX ? mt : 0]);
               // the block scale multiplies P; the codes go to the tensor core as placed (value * 2^-14)

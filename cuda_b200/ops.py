@@ -87,7 +87,7 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
                                 return_lse: bool = False, out: Optional[torch.Tensor] = None,
                                 workspace: Optional[torch.Tensor] = None, num_ctas: int = 0,
                                 check_status: bool = False, flags: int = 0,
-                                kv_format: Optional[str] = None):
+                                kv_format: Optional[str] = None, split_context=None):
     """Decode attention over a paged FP8 / MXFP8 / MXFP4 KV cache.
 
     query ``[total_q, Hq, D]``; caches ``[num_blocks, Hkv, D, page]`` bytes (V may be packed
@@ -99,6 +99,12 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
     ``torch.uint8`` or ``torch.float8_e4m3fn`` cache is read that way; a ``torch.int8`` cache is
     refused unless ``kv_format="fp8_e4m3"`` says that its bytes are E4M3 codes too, because a caller
     of the reference with real int8 data would otherwise get different numbers without a word.
+
+    ``split_context=(nccl_comm_ptr, nranks, rank, exchange)``: the cache, tables and lengths describe
+    this rank's KV range of a context sharded over ``nranks`` GPUs; the call then runs the local
+    decode, one NCCL all-gather of the fp32 (out | lse) blocks and the merge from a single C++ entry
+    point (``cuda_llm_split_context_decode``) and returns the merged result on every rank.
+    ``exchange`` is a uint8 CUDA tensor of ``cuda_llm_split_context_exchange_bytes`` bytes.
     """
     if not (query.is_cuda and key_cache_fp8.is_cuda and value_cache_fp8.is_cuda):
         raise RuntimeError("Inputs must be on CUDA")
@@ -168,12 +174,32 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
             max_blocks_per_seq=block_tables.shape[1], num_blocks=nb, max_q_len=max_q_len,
             q_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[out.dtype], k_format=k_format,
             v_format=v_format, scale_mode=mode, softmax_scale=scale, num_ctas=num_ctas, flags=flags)
-        L.check(lib.cuda_llm_paged_decode(C.byref(p), _stream_ptr(query.device)), "cuda_llm_paged_decode")
+        if split_context is not None:
+            comm, nranks, rank, exch = split_context
+            L.check(lib.cuda_llm_split_context_decode(C.byref(p), comm, nranks, rank, exch.data_ptr(), exch.numel(),
+                                                      _stream_ptr(query.device)), "cuda_llm_split_context_decode")
+        else:
+            L.check(lib.cuda_llm_paged_decode(C.byref(p), _stream_ptr(query.device)), "cuda_llm_paged_decode")
         if check_status:
             st = decode_status(ws, query.device)
             if st:
                 raise RuntimeError(f"paged decode reported device status 0x{st:x}")
     return (out, lse) if return_lse else out
+
+
+def nccl_comm_ptr(group=None, device=None) -> int:
+    """The ncclComm_t torch.distributed uses for ``group`` on ``device`` (an integer address), for
+    ``split_context=``.  The communicator exists once the group has run a collective on that device."""
+    import torch.distributed as dist
+    pg = group if group is not None else dist.distributed_c10d._get_default_group()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    return int(pg._get_backend(dev)._comm_ptr())
+
+
+def split_context_exchange(rows: int, head_dim: int, nranks: int, device) -> torch.Tensor:
+    """The exchange buffer of the split-context mode: ``nranks`` blocks of fp32 out [rows, D] + lse [rows]."""
+    n = L.load().cuda_llm_split_context_exchange_bytes(rows, head_dim, nranks)
+    return torch.empty(n, dtype=torch.uint8, device=device)
 
 
 def paged_attention_forward(query, key_cache, value_cache, block_tables, context_lens, softmax_scale=None, *,
@@ -353,10 +379,10 @@ _MODE = {"per_head": L.SCALE_PER_HEAD, "per_block": L.SCALE_PER_BLOCK, "per_toke
 
 
 def run_workload(wl, *, return_lse=False, out=None, num_ctas=0, check_status=False, workspace=None,
-                 flags=0):
+                 flags=0, split_context=None):
     """Run a ``workloads.DecodeWorkload`` through ``fp8_paged_attention_forward``."""
     return fp8_paged_attention_forward(
         wl.query, wl.key_cache, wl.value_cache, wl.k_scale, wl.v_scale, wl.block_tables,
         wl.context_lens, wl.softmax_scale, cu_q_lens=wl.cu_q_lens, max_q_len=wl.max_q_len,
         return_lse=return_lse, out=out, num_ctas=num_ctas, check_status=check_status,
-        workspace=workspace, flags=flags)
+        workspace=workspace, flags=flags, split_context=split_context)

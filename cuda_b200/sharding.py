@@ -148,6 +148,38 @@ def decode_split_context(local: DecodeWorkload, group: Optional[dist.ProcessGrou
     return merge_fn(g_out, g_lse, out_dtype or local.query.dtype)
 
 
+class SplitContextDecoder:
+    """Split-context decode with everything issued from one C++ call per step
+    (``cuda_llm_split_context_decode``): local partial, ONE NCCL all-gather of the fp32 (out | lse)
+    blocks, merge.  The exchange buffer, the output and the workspace are allocated once here and
+    reused by every call, so a step allocates nothing and runs no Python between the kernels."""
+
+    def __init__(self, local: DecodeWorkload, group: Optional[dist.ProcessGroup] = None):
+        from . import ops
+        self.ops = ops
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        dev = local.query.device
+        if self.world > 1:
+            if dist.get_backend(group) != "nccl":
+                raise RuntimeError("SplitContextDecoder needs an NCCL group (CPU ranks use decode_split_context)")
+            dist.barrier(group)                       # makes sure the communicator exists on this device
+            self.comm = ops.nccl_comm_ptr(group, dev)
+        else:
+            self.comm = None
+        rows = local.query.shape[0] * local.num_q_heads
+        self.exchange = ops.split_context_exchange(rows, local.head_dim, self.world, dev)
+        self.out = torch.empty_like(local.query)
+        need = ops.L.load().cuda_llm_paged_decode_workspace_bytes(
+            local.num_seqs, local.num_q_heads, local.num_kv_heads, local.head_dim, local.page_size, 1, 0)
+        self.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+
+    def __call__(self, local: DecodeWorkload, flags: int = 0, check_status: bool = False) -> torch.Tensor:
+        return self.ops.run_workload(local, out=self.out, workspace=self.workspace, flags=flags,
+                                     check_status=check_status,
+                                     split_context=(self.comm, self.world, self.rank, self.exchange))
+
+
 def gather_head_shards(local_out: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """KV-head sharding produces final rows for a slice of the query heads; this concatenates the
     slices (checking / a consumer that needs the full tensor).  Not on the attention data path."""

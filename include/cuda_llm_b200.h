@@ -54,8 +54,8 @@ extern "C" {
                                             outputs are not touched before it has finished either way
                                             (a finding of the plan, such as CUDA_LLM_ST_BAD_CTX, may be
                                             OR-ed into the status word early). */
-#define CUDA_LLM_FLAG_TEST_STALL 128 /* failure-path test: the first CTA announces the bytes of its first
-                                        stage but never sends them, and every wait gives up after a few
+#define CUDA_LLM_FLAG_TEST_STALL 128 /* failure-path test: the CTA that owns the first stage of the
+                                        launch announces its bytes but never sends them, and every wait gives up after a few
                                         thousand polls instead of seconds.  The waits run out, all warps
                                         return, CUDA_LLM_ST_TIMEOUT (and CUDA_LLM_ST_INCOMPLETE for the rows
                                         left without a result) is set; nothing faults or hangs.          */
@@ -198,6 +198,21 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
 int cuda_llm_merge_partials(const float* parts_out, const float* parts_lse, int32_t num_parts,
                             int64_t rows, int32_t head_dim, void* out, int32_t out_dtype,
                             float* lse, void* stream);
+
+/* ---- split-context decode over several GPUs -------------------------------------------- */
+/* No counterpart in the reference (it has no distributed code).  One context sharded by KV range
+ * over `nranks` processes, one per GPU: every rank passes the cache, block tables and context
+ * lengths of ITS token range in `params` (q_len 1 only; params->out / params->lse receive the final,
+ * merged result in out_dtype on every rank).  The call issues, on `stream` and with no host work in
+ * between: the paged decode over the local range into this rank's block of `exchange` (fp32 out
+ * [rows, D] followed by lse [rows], rows = num_seqs * num_q_heads), ONE in-place ncclAllGather of
+ * those blocks over `nccl_comm` (an ncclComm_t created by the caller on this device, e.g. the one
+ * torch.distributed uses; ncclAllGather is taken from the libnccl.so.2 already loaded in the
+ * process), and the partial merge.  `exchange`: cuda_llm_split_context_exchange_bytes() bytes,
+ * 16-byte aligned.  nranks == 1 needs no communicator. */
+size_t cuda_llm_split_context_exchange_bytes(int64_t rows, int32_t head_dim, int32_t nranks);
+int cuda_llm_split_context_decode(const CudaLlmPagedDecodeParams* params, void* nccl_comm, int32_t nranks,
+                                  int32_t rank, void* exchange, size_t exchange_bytes, void* stream);
 
 /* Write n_tokens new K/V vectors ([n_tokens, Hkv, D] of in_dtype) into the paged quantised cache
  * at (slot_block[i], slot_offset[i]), quantising on the fly with the reference test's recipe

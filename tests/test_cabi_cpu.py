@@ -129,21 +129,44 @@ def test_reference_cxx_dispatchers_are_exported(lib):
 
 
 def test_reference_module_names_import():
-    """The shims under the reference's module names expose the decode entry points (no compute)."""
+    """The compiled extension under the reference's module name loads without a GPU, exposes the three
+    decode entry points with the reference's argument names and defaults (fused_softmax_binding.cpp
+    :733-741, :759-763, :800-807 in the reference project), and the cuda_llm package re-exports them."""
     import importlib
     import sys
-    from cuda_b200 import compat, ops
+    import torch
+    from cuda_b200 import build, compat
+    if not os.path.exists(build.extension_path()):
+        build.build_extension()
     sys.path.insert(0, compat.PATH)
     try:
         ext = importlib.import_module("fused_online_softmax_cuda")
         pkg = importlib.import_module("cuda_llm")
     finally:
         sys.path.remove(compat.PATH)
-    assert ext.paged_attention_forward is ops.paged_attention_forward
-    assert ext.fp8_paged_attention_forward is ops.fp8_paged_attention_forward
-    assert ext.async_flash_decode is ops.async_flash_decode
-    assert pkg.flash_decode is ops.async_flash_decode
-    assert pkg.paged_attention is ops.paged_attention_forward
-    assert pkg.fp8_paged_attention is ops.fp8_paged_attention_forward
+    assert ext.__file__.endswith(".so")                    # a compiled module, not a Python shim
+    sig = ext.paged_attention_forward.__doc__
+    for name in ("query", "key_cache", "value_cache", "block_tables", "context_lens", "softmax_scale"):
+        assert name in sig
+    sig = ext.fp8_paged_attention_forward.__doc__
+    for name in ("query", "key_cache_fp8", "value_cache_fp8", "k_scale", "v_scale", "block_tables", "context_lens",
+                 "softmax_scale", "cu_q_lens", "max_q_len", "return_lse", "kv_format"):
+        assert name in sig
+    for name in ("q:", "k:", "v:", "softmax_scale"):
+        assert name in ext.async_flash_decode.__doc__
+    assert pkg.flash_decode is ext.async_flash_decode
+    assert pkg.paged_attention is ext.paged_attention_forward
+    assert pkg.fp8_paged_attention is ext.fp8_paged_attention_forward
+    # the reference's TORCH_CHECK messages, reached before any device work
+    q = torch.zeros(2, 4, 64)
+    c = torch.zeros(4, 4, 64, 16)
+    bt = torch.zeros(2, 2, dtype=torch.int32)
+    cl = torch.ones(2, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="Inputs must be on CUDA"):
+        ext.paged_attention_forward(q, c, c, bt, cl)
+    with pytest.raises(RuntimeError, match="Inputs must be on CUDA"):
+        ext.fp8_paged_attention_forward(q, c.to(torch.uint8), c.to(torch.uint8), cl.float(), cl.float(), bt, cl)
+    with pytest.raises(RuntimeError, match="Inputs must be on CUDA"):
+        ext.async_flash_decode(q[:, :, None], q[:, :, None], q[:, :, None])
     for mod in ("fused_online_softmax_cuda", "cuda_llm"):
         sys.modules.pop(mod, None)
