@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libcuda_llm_b200.so")
 
 OK, EINVAL, EALIGN, EWORKSPACE, ECUDA, EDEVICE = 0, -1, -2, -3, -4, -5
-ST_BAD_BLOCK, ST_BAD_CTX, ST_TIMEOUT, ST_BAD_QLEN, ST_SCALE_RANGE, ST_INCOMPLETE = 1, 2, 4, 8, 16, 32
+ST_BAD_BLOCK, ST_BAD_CTX, ST_TIMEOUT, ST_BAD_QLEN, ST_SCALE_RANGE, ST_INCOMPLETE, ST_BAD_POSITION = 1, 2, 4, 8, 16, 32, 64
 F32, F16, BF16 = 0, 1, 2
 KV_FP8_E4M3, KV_FP4_E2M1, KV_INT8, KV_F16, KV_BF16 = 0, 1, 2, 3, 4
 SCALE_PER_HEAD, SCALE_PER_BLOCK, SCALE_PER_TOKEN, SCALE_MX_E8M0 = 0, 1, 2, 3
@@ -32,6 +32,8 @@ class PagedDecodeParams(C.Structure):
         ("out_dtype", C.c_int32), ("k_format", C.c_int32), ("v_format", C.c_int32),
         ("scale_mode", C.c_int32), ("softmax_scale", C.c_float), ("num_ctas", C.c_int32),
         ("flags", C.c_int32),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p), ("rope_positions", C.c_void_p),
+        ("rope_num_positions", C.c_int32),
     ]
 
 

@@ -304,6 +304,15 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
     a.q_smem_bytes = L.q_smem_bytes;
     a.q_smem_tokens = L.q_smem_tokens;
   }
+  if (p->rope_cos || p->rope_sin) {
+    if (!p->rope_cos || !p->rope_sin || p->rope_num_positions <= 0)
+      return fail(CUDA_LLM_EINVAL, "rotary embedding needs both tables and rope_num_positions > 0");
+    if (((uintptr_t)p->rope_cos | (uintptr_t)p->rope_sin) & 7) return fail(CUDA_LLM_EALIGN, "rotary tables must be 8-byte aligned");
+    a.rope_cos = p->rope_cos;
+    a.rope_sin = p->rope_sin;
+    a.rope_pos = p->rope_positions;
+    a.rope_positions = p->rope_num_positions;
+  }
   a.early_plan = (p->flags & CUDA_LLM_FLAG_STABLE_METADATA) ? 1 : 0;
   a.grid = L.grid;
   a.n_slots = p->num_seqs * L.n_hg + L.grid;

@@ -110,6 +110,10 @@ struct DecodeArgs {
   float scale_log2;
   int n_stages;
   int grid, n_slots;    // CTAs of the decode launch; partial-result slots in the workspace
+  const float* rope_cos;     // optional rotary tables [rope_positions][D] fp32 (rotate-half convention); null: none
+  const float* rope_sin;
+  const int32_t* rope_pos;   // optional position of every query token [total_q]; null: ctx - q_len + j
+  int rope_positions;        // rows of the tables (positions are clamped to them, with a status bit)
   int short_waits;      // every mbarrier wait gives up after kShortPolls polls instead of kMaxPolls
   int stall_test;       // failure-path test: the first stage of the launch is armed but no copies are issued for it
   uint32_t stage_bytes, off_v, off_ks, off_vs;
@@ -651,7 +655,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
       // Common case, kept small because this code runs once per (sequence, head group) and is cold
       // in the instruction cache every time: 16-bit query rows, from this slot's shared-memory area
       // when there is one, one 32-bit load and a branch-free conversion per fragment register.
-      const bool q_fast = !PRECISE && a.q_dtype != CUDA_LLM_F32;
+      const bool q_fast = !PRECISE && a.q_dtype != CUDA_LLM_F32 && a.rope_cos == nullptr;
       if (q_fast) {
         const bool q_in_smem = (flags & FLAG_QSMEM) != 0;
         const uint32_t qrow = smem_base + a.q_smem_off + slot * a.q_smem_bytes +
@@ -675,14 +679,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
             qf[kt][hf] = row_live ? pk : 0u;
           }
       }
-      if (!q_fast)
-#pragma unroll
-      for (int kt = 0; kt < KT; ++kt)
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          // token-major K: the thread's 16-byte chunk (t + 4*(kt/2)) holds the columns of two k-tiles
-          const int d = TM ? 8 * (t + 4 * (kt >> 1)) + 4 * (kt & 1) + 2 * hf : 16 * kt + 8 * hf + 2 * t;
-          float lo = 0.f, hi = 0.f;
+      if (!q_fast) {
+        // general path: any query dtype, shared-memory or global source, optional rotary embedding
+        auto load_pair = [&](int d, float& lo, float& hi) {  // elements d, d + 1 of this thread's query row
+          lo = 0.f; hi = 0.f;
           if (row_live && (flags & FLAG_QSMEM)) {
             // row (jq, h, iq) of this slot's query area
             const uint32_t el = (uint32_t)((jq * a.HG + h) * a.group + iq) * D + d;
@@ -708,10 +708,53 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
               lo = __low2float(v); hi = __high2float(v);
             }
           }
+        };
+        auto store_frag = [&](int kt, int hf, float lo, float hi) {
           const uint32_t pk = BF ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
           qf[kt][hf] = pk;
           if (PRECISE) ql[PRECISE ? kt : 0][hf] = pack_f16x2(lo - f16x2_lo(pk), hi - f16x2_hi(pk));
+        };
+        // token-major K: the thread's 16-byte chunk (t + 4*(kt/2)) holds the columns of two k-tiles
+        auto frag_d = [&](int kt, int hf) {
+          return TM ? 8 * (t + 4 * (kt >> 1)) + 4 * (kt & 1) + 2 * hf : 16 * kt + 8 * hf + 2 * t;
+        };
+        if (a.rope_cos != nullptr) {
+          // Rotary embedding of the query (rotate-half: q' = q * cos + rot(q) * sin with
+          // rot(q) = [-q[D/2:], q[:D/2]], fused_rope_flash_attention_kernel.cuh:56-74 in the reference
+          // project), in fp32 before the rounding to the MMA operand type.  Element d and its partner
+          // d + D/2 belong to k-tiles kt and kt + KT/2 of the same thread.
+          int pos = a.rope_pos ? (row_live ? a.rope_pos[qbase + jq] : 0) : ctx - qlen + jq;
+          if (pos < 0 || pos >= a.rope_positions) {
+            if (row_live) atomicOr(a.status, CUDA_LLM_ST_BAD_POSITION);
+            pos = max(0, min(pos, a.rope_positions - 1));
+          }
+          const float* ct = a.rope_cos + (size_t)pos * D;
+          const float* st = a.rope_sin + (size_t)pos * D;
+#pragma unroll
+          for (int kt = 0; kt < KT / 2; ++kt)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              const int d = frag_d(kt, hf);
+              float x0, x1, y0, y1;
+              load_pair(d, x0, x1);
+              load_pair(d + D / 2, y0, y1);
+              const float2 c_lo = *reinterpret_cast<const float2*>(ct + d), s_lo = *reinterpret_cast<const float2*>(st + d);
+              const float2 c_hi = *reinterpret_cast<const float2*>(ct + d + D / 2),
+                           s_hi = *reinterpret_cast<const float2*>(st + d + D / 2);
+              store_frag(kt, hf, x0 * c_lo.x - y0 * s_lo.x, x1 * c_lo.y - y1 * s_lo.y);
+              store_frag(kt + KT / 2, hf, y0 * c_hi.x + x0 * s_hi.x, y1 * c_hi.y + x1 * s_hi.y);
+            }
+        } else {
+#pragma unroll
+          for (int kt = 0; kt < KT; ++kt)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              float lo, hi;
+              load_pair(frag_d(kt, hf), lo, hi);
+              store_frag(kt, hf, lo, hi);
+            }
         }
+      }
       // a finite floor instead of -inf: max - max never becomes inf - inf, no special case below
       m_run[0] = m_run[1] = kMaxFloor;
       l_run[0] = l_run[1] = 0.f;

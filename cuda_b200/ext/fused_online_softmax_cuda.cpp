@@ -6,7 +6,7 @@
 // :800-807), same TORCH_CHECK messages.  Differences, all additive: a device guard taken from the
 // query tensor (the reference has none), GQA inferred from the cache's head count, page sizes 32 and
 // 64, per-token and E8M0 scales, packed FP4 V, and keyword-only extensions (cu_q_lens, max_q_len,
-// return_lse, kv_format).  Every call goes straight to the C ABI of libcuda_llm_b200.so on the
+// return_lse, kv_format, rope_cos / rope_sin / rope_positions).  Every call goes straight to the C ABI of libcuda_llm_b200.so on the
 // current stream; torch supplies tensors, the stream and the scratch buffer.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -127,7 +127,10 @@ pybind11::object fp8_paged_attention_forward(torch::Tensor query, torch::Tensor 
                                              torch::Tensor v_scale, torch::Tensor block_tables,
                                              torch::Tensor context_lens, c10::optional<double> softmax_scale_opt,
                                              c10::optional<torch::Tensor> cu_q_lens, int64_t max_q_len,
-                                             bool return_lse, c10::optional<std::string> kv_format) {
+                                             bool return_lse, c10::optional<std::string> kv_format,
+                                             c10::optional<torch::Tensor> rope_cos,
+                                             c10::optional<torch::Tensor> rope_sin,
+                                             c10::optional<torch::Tensor> rope_positions) {
   TORCH_CHECK(query.is_cuda() && key_cache_fp8.is_cuda() && value_cache_fp8.is_cuda(), "Inputs must be on CUDA");
   TORCH_CHECK(k_scale.is_cuda() && v_scale.is_cuda(), "Scale tensors must be on CUDA");
   TORCH_CHECK(block_tables.is_cuda() && context_lens.is_cuda(), "Metadata tensors must be on CUDA");
@@ -221,6 +224,21 @@ pybind11::object fp8_paged_attention_forward(torch::Tensor query, torch::Tensor 
   p.v_format = v_format;
   p.scale_mode = scale_mode;
   p.softmax_scale = scale_or_default(softmax_scale_opt, head_dim);
+  torch::Tensor rc_t, rs_t, rp_t;  // keep the converted rotary tensors alive until the launch is queued
+  if (rope_cos.has_value()) {
+    TORCH_CHECK(rope_sin.has_value() && rope_cos->dim() == 2 && rope_cos->sizes() == rope_sin->sizes() &&
+                    rope_cos->size(1) == head_dim, "rope_cos / rope_sin must both be [positions, head_dim]");
+    rc_t = rope_cos->to(query.device(), torch::kFloat32).contiguous();
+    rs_t = rope_sin->to(query.device(), torch::kFloat32).contiguous();
+    p.rope_cos = rc_t.data_ptr<float>();
+    p.rope_sin = rs_t.data_ptr<float>();
+    p.rope_num_positions = (int)rc_t.size(0);
+    if (rope_positions.has_value()) {
+      rp_t = rope_positions->to(query.device(), torch::kInt32).contiguous();
+      TORCH_CHECK(rp_t.numel() == total_q, "rope_positions must have one entry per query token");
+      p.rope_positions = rp_t.data_ptr<int32_t>();
+    }
+  }
   check_rc(cuda_llm_paged_decode(&p, stream), "cuda_llm_paged_decode");
   if (return_lse) return pybind11::cast(std::make_tuple(output, lse));
   return pybind11::cast(output);
@@ -242,5 +260,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("k_scale"), pybind11::arg("v_scale"), pybind11::arg("block_tables"),
         pybind11::arg("context_lens"), pybind11::arg("softmax_scale") = pybind11::none(),
         pybind11::kw_only(), pybind11::arg("cu_q_lens") = pybind11::none(), pybind11::arg("max_q_len") = 1,
-        pybind11::arg("return_lse") = false, pybind11::arg("kv_format") = pybind11::none());
+        pybind11::arg("return_lse") = false, pybind11::arg("kv_format") = pybind11::none(),
+        pybind11::arg("rope_cos") = pybind11::none(), pybind11::arg("rope_sin") = pybind11::none(),
+        pybind11::arg("rope_positions") = pybind11::none());
 }

@@ -87,7 +87,9 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
                                 return_lse: bool = False, out: Optional[torch.Tensor] = None,
                                 workspace: Optional[torch.Tensor] = None, num_ctas: int = 0,
                                 check_status: bool = False, flags: int = 0,
-                                kv_format: Optional[str] = None, split_context=None):
+                                kv_format: Optional[str] = None, split_context=None,
+                                rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None,
+                                rope_positions: Optional[torch.Tensor] = None):
     """Decode attention over a paged FP8 / MXFP8 / MXFP4 KV cache.
 
     query ``[total_q, Hq, D]``; caches ``[num_blocks, Hkv, D, page]`` bytes (V may be packed
@@ -99,6 +101,11 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
     ``torch.uint8`` or ``torch.float8_e4m3fn`` cache is read that way; a ``torch.int8`` cache is
     refused unless ``kv_format="fp8_e4m3"`` says that its bytes are E4M3 codes too, because a caller
     of the reference with real int8 data would otherwise get different numbers without a word.
+
+    ``rope_cos`` / ``rope_sin`` (fp32 ``[positions, D]``, the tables of the reference's
+    ``tests/_utils.py:75-81``): the query is rotated (rotate-half convention,
+    ``fused_rope_flash_attention_kernel.cuh:56-74`` in the reference project) as it is loaded, at
+    ``rope_positions`` (int32 ``[total_q]``) or, by default, at ``context_len - q_len + j``.
 
     ``split_context=(nccl_comm_ptr, nranks, rank, exchange)``: the cache, tables and lengths describe
     this rank's KV range of a context sharded over ``nranks`` GPUs; the call then runs the local
@@ -174,6 +181,15 @@ def fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, 
             max_blocks_per_seq=block_tables.shape[1], num_blocks=nb, max_q_len=max_q_len,
             q_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[out.dtype], k_format=k_format,
             v_format=v_format, scale_mode=mode, softmax_scale=scale, num_ctas=num_ctas, flags=flags)
+        if rope_cos is not None:
+            if rope_sin is None or rope_cos.shape != rope_sin.shape or rope_cos.dim() != 2 or rope_cos.shape[1] != d:
+                raise RuntimeError("rope_cos / rope_sin must both be [positions, head_dim]")
+            rope_cos = rope_cos.to(device=query.device, dtype=torch.float32).contiguous()
+            rope_sin = rope_sin.to(device=query.device, dtype=torch.float32).contiguous()
+            if rope_positions is not None:
+                rope_positions = rope_positions.to(device=query.device, dtype=torch.int32).contiguous()
+            p.rope_cos, p.rope_sin = rope_cos.data_ptr(), rope_sin.data_ptr()
+            p.rope_positions, p.rope_num_positions = _ptr(rope_positions), rope_cos.shape[0]
         if split_context is not None:
             comm, nranks, rank, exch = split_context
             L.check(lib.cuda_llm_split_context_decode(C.byref(p), comm, nranks, rank, exch.data_ptr(), exch.numel(),

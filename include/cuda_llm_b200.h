@@ -37,6 +37,7 @@ extern "C" {
 #define CUDA_LLM_ST_TIMEOUT 4u     /* a bounded wait gave up                                 */
 #define CUDA_LLM_ST_BAD_QLEN 8u    /* group * q_len exceeds the rows the launch was sized for */
 #define CUDA_LLM_ST_SCALE_RANGE 16u /* an E8M0 V scale byte of a live token is outside [32, 223] */
+#define CUDA_LLM_ST_BAD_POSITION 64u /* a rotary position outside [0, rope_num_positions)         */
 #define CUDA_LLM_ST_INCOMPLETE 32u /* a (sequence, head group) was left without a result: its rows
                                       are zeros (follows CUDA_LLM_ST_TIMEOUT)                     */
 
@@ -127,6 +128,18 @@ typedef struct CudaLlmPagedDecodeParams {
   float softmax_scale;
   int32_t num_ctas;            /* 0 = one per SM                                             */
   int32_t flags;               /* CUDA_LLM_FLAG_* bits, normally 0                          */
+
+  /* Optional rotary embedding fused into the query load (math of the reference's
+   * fused_rope_flash_attention_kernel.cuh:56-74, rotate-half convention, tables as its
+   * tests/_utils.py:75-81 builds them): q' = q * cos[pos] + rot_half(q) * sin[pos], in fp32, before
+   * the dot products.  K in the cache is expected to be rotated already (it was when it was
+   * appended).  All NULL / 0: no rotation. */
+  const float* rope_cos;          /* [rope_num_positions, head_dim] fp32, or NULL             */
+  const float* rope_sin;          /* [rope_num_positions, head_dim] fp32                      */
+  const int32_t* rope_positions;  /* [total_q] position of every query token, or NULL: query
+                                     token j of a sequence sits at context_len - q_len + j    */
+  int32_t rope_num_positions;     /* rows of the tables (a position outside them is clamped
+                                     and reported as CUDA_LLM_ST_BAD_POSITION)                */
 } CudaLlmPagedDecodeParams;
 
 /* Bytes of workspace cuda_llm_paged_decode needs for these dimensions on the current device. */

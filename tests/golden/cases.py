@@ -59,3 +59,19 @@ def decode_inputs(dtype, head_dim, kv_len):
     k = torch.randn(2, 4, kv_len, head_dim, dtype=dtype)
     v = torch.randn(2, 4, kv_len, head_dim, dtype=dtype)
     return q, k, v
+
+
+def rope_cases():
+    for dn, dt in DTYPES.items():
+        for hd in (64, 128):
+            yield f"rope_{dn}_d{hd}", dt, hd, 200
+
+
+def rope_inputs(dtype, head_dim, seq_len):
+    """q, k, v [B, H, S, D] of a causal RoPE attention (``tests/test_attention.py`` of the reference
+    builds its RoPE case the same way): the last query row is a decode step over the S cached tokens."""
+    torch.manual_seed(0)
+    q = torch.randn(2, 4, seq_len, head_dim, dtype=dtype)
+    k = torch.randn(2, 4, seq_len, head_dim, dtype=dtype)
+    v = torch.randn(2, 4, seq_len, head_dim, dtype=dtype)
+    return q, k, v

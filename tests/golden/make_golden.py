@@ -7,7 +7,8 @@ Run in a container where the reference checkout is mounted:
 It imports the reference's ``tests/_utils.py`` (``make_paged_cache``, ``ref_decode``,
 ``ref_attention``) and replays the reference's own test cases
 (``tests/test_kernels_misc.py:26-35`` paged, ``:42-64`` E4M3 paged,
-``tests/test_attention.py:76-86`` decode) on the CPU with the same seed rule
+``tests/test_attention.py:76-86`` decode, ``ref_rope_attention`` of ``tests/_utils.py:91-93`` for the
+rotary case) on the CPU with the same seed rule
 (``tests/conftest.py:31-33``: ``torch.manual_seed(0)`` before every case).  Inputs are
 regenerated from the seed by ``tests/golden/cases.py`` at test time; the fixture keeps the
 reference outputs, the block tables the reference drew, and CRC32s of the paged caches so
@@ -64,6 +65,15 @@ def main(ref_root: str):
     v = torch.randn(2, 2, 77, 64)
     out["gqa_decode/out"] = ref.ref_gqa(q, k, v, is_causal=False).numpy()
     out["gqa_decode/crc"] = np.array([crc(q), crc(k), crc(v)], dtype=np.uint32)
+
+    # ---- rotary embedding: last row of the reference's causal RoPE attention = one decode step ----
+    for name, dtype, head_dim, seq_len in cases.rope_cases():
+        q, k, v = cases.rope_inputs(dtype, head_dim, seq_len)
+        cos, sin = ref.rope_tables(seq_len, head_dim, "cpu")
+        o = ref.ref_rope_attention(q, k, v, cos, sin, is_causal=True)
+        out[f"{name}/out_last"] = o[:, :, -1, :].contiguous().numpy()          # [B, H, D]
+        k_rot = ref.apply_rope(k, cos, sin).to(dtype)                           # what the cache holds
+        out[f"{name}/crc"] = np.array([crc(q), crc(k), crc(v), crc(cos), crc(sin), crc(k_rot)], dtype=np.uint32)
 
     path = os.path.join(HERE, "reference_cases.npz")
     np.savez_compressed(path, **out)

@@ -147,7 +147,9 @@ def test_scale_byte_outside_supported_range_sets_status(ops):
                                 q_dtype=torch.bfloat16)
     wl.v_scale[int(wl.block_tables[3, 0]), 2, :, 0] = 10
     g = wl.to("cuda")
-    ws = torch.zeros(1 << 22, dtype=torch.uint8, device="cuda")
+    need = ops.L.load().cuda_llm_paged_decode_workspace_bytes(wl.num_seqs, wl.num_q_heads, wl.num_kv_heads,
+                                                              wl.head_dim, wl.page_size, 1, 0)
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
     ops.run_workload(g, workspace=ws)
     assert ops.decode_status(ws) & ops.L.ST_SCALE_RANGE
     wl.v_scale[int(wl.block_tables[3, 0]), 2, :, 0] = 127

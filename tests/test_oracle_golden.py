@@ -132,3 +132,23 @@ def test_configs_small_are_finite_and_causal(cfg):
     out = O.ref_paged_decode(wl.query, kv, wl.softmax_scale, wl.cu_q_lens)
     assert torch.isfinite(out).all()        # poisoned tails / unused pages are never read
     assert out.shape == wl.query.shape
+
+
+@pytest.mark.parametrize("case", list(cases.rope_cases()), ids=lambda c: c[0])
+def test_rope_oracle_matches_reference(golden, case):
+    """rope_tables / apply_rope of the oracle reproduce the reference's (tests/_utils.py:75-88 there)
+    bit for bit, and rotating only the last query row and attending over the rotated keys gives the
+    last row of the reference's causal ref_rope_attention."""
+    import zlib
+    name, dtype, hd, seq = case
+    q, k, v = cases.rope_inputs(dtype, hd, seq)
+    cos, sin = O.rope_tables(seq, hd)
+    crc = lambda t: zlib.crc32(t.contiguous().view(torch.uint8).numpy().tobytes())
+    want = golden[f"{name}/crc"]
+    k_rot = O.apply_rope(k, cos, sin).to(dtype)
+    assert [crc(q), crc(k), crc(v), crc(cos), crc(sin), crc(k_rot)] == want.tolist()
+    ctx = torch.full((2,), seq, dtype=torch.int32)
+    q_last = q[:, :, -1, :]                                                     # [B, H, D]
+    q_rot = O.rope_query(q_last, cos, sin, ctx)
+    out = O.ref_flash_decode(q_rot[:, :, None, :], O.apply_rope(k, cos, sin), v)[:, :, 0]
+    assert torch.allclose(out, torch.from_numpy(golden[f"{name}/out_last"]), atol=1e-5, rtol=1e-5)
