@@ -1,5 +1,5 @@
 """Two NCCL ranks on two GPUs: the split-context mode (local partial, all-gather over NVLink, merge
-kernel) and KV-head sharding against the oracle.  Skipped on a box with one GPU."""
+kernel; from Python and from the single C++ entry point) and KV-head sharding against the oracle.  Skipped on a box with one GPU."""
 import os
 import socket
 
@@ -26,8 +26,14 @@ def _worker(rank, world, port, q):
         wl = W.make_config(4, batch=2, ctx_scale=1 / 64)           # 2 x 2048 tokens, page 64
         ref = oracle_out(wl)
         g = wl.to(f"cuda:{rank}")
-        out = S.decode_split_context(S.slice_context(g, world, rank))
+        local = S.slice_context(g, world, rank)
+        out = S.decode_split_context(local)
         e_ctx = (out.float().cpu() - ref).abs()
+        # the same exchange issued from one C++ call (decode, one ncclAllGather, merge)
+        dec = S.SplitContextDecoder(local)
+        for _ in range(3):
+            fused = dec(local, check_status=True)
+        e_ctx = torch.maximum(e_ctx, (fused.float().cpu() - ref).abs())
         lo, hi = S.shard_kv_heads(wl.num_kv_heads, world, rank)
         from cuda_b200 import ops
         lout = ops.run_workload(S.slice_kv_heads(g, lo, hi))
