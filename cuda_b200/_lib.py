@@ -37,6 +37,14 @@ class PagedDecodeParams(C.Structure):
     ]
 
 
+class KvCacheTarget(C.Structure):
+    _fields_ = [
+        ("key_cache", C.c_void_p), ("value_cache", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
+        ("slot_block", C.c_void_p), ("slot_offset", C.c_void_p), ("status", C.c_void_p),
+        ("page_size", C.c_int32), ("num_blocks", C.c_int32), ("v_format", C.c_int32), ("scale_mode", C.c_int32),
+    ]
+
+
 # name -> (restype, argtypes): every symbol include/cuda_llm_b200.h declares
 SYMBOLS = {
     "cuda_llm_paged_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 7),
@@ -57,6 +65,8 @@ SYMBOLS = {
     "cuda_llm_split_context_exchange_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
     "cuda_llm_split_context_decode": (C.c_int, [C.POINTER(PagedDecodeParams), C.c_void_p, C.c_int32, C.c_int32,
                                                 C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cuda_llm_gqa_prefill": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 5 + [C.c_float, C.c_int32, C.c_int32,
+                                                                    C.POINTER(KvCacheTarget), C.c_void_p]),
     "cuda_llm_dequant_pages": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                          C.c_void_p]),

@@ -16,6 +16,10 @@ cudaError_t launch_merge_partials(const float*, const float*, int, long long, in
 cudaError_t launch_dequant_pages(const void*, const void*, const int32_t*, int, int, int, int, int,
                                  int, float*, cudaStream_t);
 
+cudaError_t run_gqa_prefill(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hkv, int S,
+                            int D, float softmax_scale, bool causal, int dtype, cudaStream_t st);
+cudaError_t run_kv_append_prefill(const void* k, const void* v, const CudaLlmKvCacheTarget& c, int B, int Hkv, int S,
+                                  int D, int in_dtype, cudaStream_t st);
 size_t dense_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens);
 cudaError_t run_dense_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
                              const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int page,
@@ -578,6 +582,41 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
   cudaError_t e = run_dense_decode(false, q, k, v, nullptr, nullptr, o, batch_size, num_heads, num_kv_heads, head_dim,
                                    1, 1, 1, seq_len, softmax_scale, dtype, workspace, reinterpret_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "flash_decode launch");
+}
+
+int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out, int32_t batch_size,
+                         int32_t num_q_heads, int32_t num_kv_heads, int32_t seq_len, int32_t head_dim,
+                         float softmax_scale, int32_t is_causal, int32_t dtype,
+                         const CudaLlmKvCacheTarget* cache, void* stream) {
+  if (batch_size == 0 || seq_len == 0) return CUDA_LLM_OK;
+  if (!q || !k || !v || !out) return fail(CUDA_LLM_EINVAL, "a required tensor pointer is null");
+  if (batch_size < 0 || seq_len < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads)
+    return fail(CUDA_LLM_EINVAL, "num_q_heads must be divisible by num_kv_heads");
+  if (head_dim != 64 && head_dim != 128) return fail(CUDA_LLM_EINVAL, "Only head_dim 64 and 128 supported");
+  if (dtype < 0 || dtype > CUDA_LLM_BF16) return fail(CUDA_LLM_EINVAL, "unknown dtype");
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
+    return fail(CUDA_LLM_EALIGN, "q, k, v and out must be 16-byte aligned");
+  if (cache) {
+    if (!cache->key_cache || !cache->value_cache || !cache->k_scale || !cache->v_scale || !cache->slot_block ||
+        !cache->slot_offset)
+      return fail(CUDA_LLM_EINVAL, "cache target: a required pointer is null");
+    if (cache->page_size <= 0 || cache->num_blocks <= 0 || cache->scale_mode < 0 ||
+        cache->scale_mode > CUDA_LLM_SCALE_MX_E8M0 ||
+        (cache->v_format != CUDA_LLM_KV_FP8_E4M3 && cache->v_format != CUDA_LLM_KV_FP4_E2M1) ||
+        (cache->v_format == CUDA_LLM_KV_FP4_E2M1 && cache->scale_mode != CUDA_LLM_SCALE_MX_E8M0))
+      return fail(CUDA_LLM_EINVAL, "cache target: unsupported page size, format or scale mode");
+  }
+  const int rc = check_device();
+  if (rc != CUDA_LLM_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = run_gqa_prefill(q, k, v, out, batch_size, num_q_heads, num_kv_heads, seq_len, head_dim,
+                                  softmax_scale, is_causal != 0, dtype, st);
+  if (e != cudaSuccess) return fail_cuda(e, "gqa_prefill_kernel launch");
+  if (cache) {
+    e = run_kv_append_prefill(k, v, *cache, batch_size, num_kv_heads, seq_len, head_dim, dtype, st);
+    if (e != cudaSuccess) return fail_cuda(e, "kv_append_kernel launch");
+  }
+  return CUDA_LLM_OK;
 }
 
 int cuda_llm_merge_partials(const float* parts_out, const float* parts_lse, int32_t num_parts,

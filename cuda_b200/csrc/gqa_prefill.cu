@@ -240,6 +240,71 @@ static cudaError_t launch_prefill(const PrefillArgs& a, cudaStream_t st) {
   return cudaGetLastError();
 }
 
+// fp32 tensors: a plain SIMT kernel (no tensor-core operand form keeps fp32 accuracy without a
+// three-way split).  One warp per query row, four rows of one (batch, query head) per CTA; K/V
+// tiles of 32 tokens in shared memory; lane = token for Q.K, lane = head_dim slice for P.V.
+template <int D>
+__global__ void __launch_bounds__(128) gqa_prefill_f32_kernel(const PrefillArgs a) {
+  constexpr int E = D / 32;
+  constexpr float NEG_INF = -__builtin_huge_valf();
+  __shared__ float sK[32][D + 1];
+  __shared__ float sV[32][D + 1];
+  __shared__ float sQ[4][D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, qh = blockIdx.y, kvh = qh / a.group;
+  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * 4, qpos = q0 + warp;
+  const float* qg = reinterpret_cast<const float*>(a.q) + (((size_t)b * a.Hq + qh) * (size_t)a.S) * D;
+  const float* kg = reinterpret_cast<const float*>(a.k) + (((size_t)b * a.Hkv + kvh) * (size_t)a.S) * D;
+  const float* vg = reinterpret_cast<const float*>(a.v) + (((size_t)b * a.Hkv + kvh) * (size_t)a.S) * D;
+  const bool row_ok = qpos < a.S;
+#pragma unroll
+  for (int e = 0; e < E; ++e) sQ[warp][lane + 32 * e] = row_ok ? qg[(size_t)qpos * D + lane + 32 * e] : 0.f;
+  float m = -1.0e30f, l = 0.f, acc[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+  const int last_q = min(a.S, q0 + 4) - 1;
+  const int n_keys = a.causal ? min(a.S, last_q + 1) : a.S;
+  for (int kv0 = 0; kv0 < n_keys; kv0 += 32) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * D; i += 128) {
+      const int r = i / D, c = i - r * D;
+      const bool ok = kv0 + r < a.S;
+      sK[r][c] = ok ? kg[(size_t)(kv0 + r) * D + c] : 0.f;
+      sV[r][c] = ok ? vg[(size_t)(kv0 + r) * D + c] : 0.f;
+    }
+    __syncthreads();
+    const int key = kv0 + lane;
+    float s = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < D; ++d) s = fmaf(sQ[warp][d], sK[lane][d], s);
+    s *= a.scale_log2;
+    if (!row_ok || key >= a.S || (a.causal && key > qpos)) s = NEG_INF;
+    float mx = s;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float mn = fmaxf(m, mx);
+    const float al = exp2f(m - mn);
+    const float p = exp2f(s - mn);
+    m = mn;
+    float ps = p;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+    l = l * al + ps;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] *= al;
+    for (int j = 0; j < 32; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = fmaf(pj, sV[j][lane + 32 * e], acc[e]);
+    }
+  }
+  if (!row_ok) return;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  float* og = reinterpret_cast<float*>(a.out) + (((size_t)b * a.Hq + qh) * (size_t)a.S + qpos) * D;
+#pragma unroll
+  for (int e = 0; e < E; ++e) og[lane + 32 * e] = acc[e] * inv;
+}
+
 cudaError_t run_gqa_prefill(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hkv, int S,
                             int D, float softmax_scale, bool causal, int dtype, cudaStream_t st) {
   PrefillArgs a;
@@ -249,6 +314,12 @@ cudaError_t run_gqa_prefill(const void* q, const void* k, const void* v, void* o
   a.causal = causal ? 1 : 0;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   if (B == 0 || S == 0) return cudaSuccess;
+  if (dtype == CUDA_LLM_F32) {
+    dim3 grid((S + 3) / 4, Hq, B);
+    if (D == 64) gqa_prefill_f32_kernel<64><<<grid, 128, 0, st>>>(a);
+    else gqa_prefill_f32_kernel<128><<<grid, 128, 0, st>>>(a);
+    return cudaGetLastError();
+  }
   if (dtype == CUDA_LLM_BF16) return D == 64 ? launch_prefill<64, true>(a, st) : launch_prefill<128, true>(a, st);
   return D == 64 ? launch_prefill<64, false>(a, st) : launch_prefill<128, false>(a, st);
 }

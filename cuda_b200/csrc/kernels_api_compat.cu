@@ -1,4 +1,5 @@
-// Definitions of the reference's three decode dispatchers on top of the C ABI.
+// Definitions of the reference's three decode dispatchers and of its GQA prefill dispatcher on top
+// of the C ABI.
 //
 // The reference signatures carry neither the number of pages in the pool nor a workspace, so:
 //  * block-table entries are bounds-checked against INT32_MAX only (the reference does not check
@@ -54,6 +55,15 @@ void dispatch_async_flash_decode(const T* q, const T* k, const T* v, T* o, int b
   if (ws) cudaFreeAsync(ws, stream);
 }
 
+template <typename T>
+void dispatch_fused_gqa(const T* q, const T* k, const T* v, T* o, int batch_size, int num_q_heads,
+                        int num_kv_heads, int seq_len, int head_dim, float softmax_scale, bool is_causal,
+                        cudaStream_t stream) {
+  report("dispatch_fused_gqa",
+         cuda_llm_gqa_prefill(q, k, v, o, batch_size, num_q_heads, num_kv_heads, seq_len, head_dim, softmax_scale,
+                              is_causal ? 1 : 0, dtype_of<T>(), nullptr, stream));
+}
+
 template <typename T_OUT, typename T_Q>
 void dispatch_fp8_paged_attention(const T_Q* query, const int8_t* key_cache_fp8,
                                   const int8_t* value_cache_fp8, const float* k_scale,
@@ -95,6 +105,8 @@ void dispatch_fp8_paged_attention(const T_Q* query, const int8_t* key_cache_fp8,
                                             int, int, int, int, float, cudaStream_t);                         \
   template void dispatch_async_flash_decode<T>(const T*, const T*, const T*, T*, int, int, int, int, float,   \
                                                cudaStream_t);                                                 \
+  template void dispatch_fused_gqa<T>(const T*, const T*, const T*, T*, int, int, int, int, int, float, bool,           \
+                                      cudaStream_t);                                                          \
   template void dispatch_fp8_paged_attention<T, T>(const T*, const int8_t*, const int8_t*, const float*,      \
                                                    const float*, const int32_t*, const int32_t*, T*, int, int, \
                                                    int, int, int, float, bool, cudaStream_t);

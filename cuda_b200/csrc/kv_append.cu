@@ -21,6 +21,7 @@ struct AppendArgs {
   void* vs;
   uint32_t* status;  // may be null
   int n, Hkv, page, num_blocks, in_dtype, v_format, scale_mode;
+  int seq_len;  // 0: source rows are [n, Hkv, D]; > 0: source is [n / seq_len, Hkv, seq_len, D] (prefill layout)
 };
 
 __device__ __forceinline__ uint32_t quant_e4m3_byte(float y) { return f32x2_to_e4m3x2(y, 0.f) & 0xffu; }
@@ -55,8 +56,10 @@ __global__ void __launch_bounds__(128) kv_append_kernel(const AppendArgs a) {
   }
   const void* src = is_v ? a.v_new : a.k_new;
   float x[E];
+  const size_t src_row = a.seq_len > 0 ? ((size_t)(tok / a.seq_len) * a.Hkv + h) * a.seq_len + (tok % a.seq_len)
+                                       : (size_t)tok * a.Hkv + h;
 #pragma unroll
-  for (int e = 0; e < E; ++e) x[e] = load_q_elem(src, a.in_dtype, ((size_t)tok * a.Hkv + h) * D + lane * E + e);
+  for (int e = 0; e < E; ++e) x[e] = load_q_elem(src, a.in_dtype, src_row * D + lane * E + e);
   float amax = 0.f;
 #pragma unroll
   for (int e = 0; e < E; ++e) amax = fmaxf(amax, fabsf(x[e]));
@@ -112,6 +115,17 @@ cudaError_t launch_kv_append(const AppendArgs& a, int D, cudaStream_t st) {
   return cudaGetLastError();
 }
 
+cudaError_t run_kv_append_prefill(const void* k, const void* v, const CudaLlmKvCacheTarget& c, int B, int Hkv, int S,
+                                  int D, int in_dtype, cudaStream_t st) {
+  AppendArgs a;
+  a.k_new = k; a.v_new = v; a.slot_block = c.slot_block; a.slot_offset = c.slot_offset;
+  a.kc = (uint8_t*)c.key_cache; a.vc = (uint8_t*)c.value_cache; a.ks = c.k_scale; a.vs = c.v_scale; a.status = c.status;
+  a.n = B * S; a.Hkv = Hkv; a.page = c.page_size; a.num_blocks = c.num_blocks; a.in_dtype = in_dtype;
+  a.v_format = c.v_format; a.scale_mode = c.scale_mode;
+  a.seq_len = S;
+  return launch_kv_append(a, D, st);
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -133,6 +147,7 @@ extern "C" int cuda_llm_kv_append(const void* k_new, const void* v_new, const in
   a.kc = (uint8_t*)key_cache; a.vc = (uint8_t*)value_cache; a.ks = k_scale; a.vs = v_scale; a.status = status;
   a.n = n_tokens; a.Hkv = num_kv_heads; a.page = page_size; a.num_blocks = num_blocks; a.in_dtype = in_dtype;
   a.v_format = v_format; a.scale_mode = scale_mode;
+  a.seq_len = 0;
   return launch_kv_append(a, head_dim, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? CUDA_LLM_OK
                                                                                               : CUDA_LLM_ECUDA;
 }

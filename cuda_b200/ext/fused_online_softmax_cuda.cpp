@@ -1,9 +1,9 @@
-// PyTorch extension `fused_online_softmax_cuda`, decode path only.
+// PyTorch extension `fused_online_softmax_cuda`: the decode path and the GQA prefill in front of it.
 //
 // Same module name, function names, argument names and defaults as the reference binding
 // (fused_softmax_binding.cpp in the reference project: paged_attention_forward :109-173 / m.def
 // :733-741, async_flash_decode :308-360 / :759-763, fp8_paged_attention_forward :634-718 /
-// :800-807), same TORCH_CHECK messages.  Differences, all additive: a device guard taken from the
+// :800-807, fused_gqa_forward :246-302 / :751-756), same TORCH_CHECK messages.  Differences, all additive: a device guard taken from the
 // query tensor (the reference has none), GQA inferred from the cache's head count, page sizes 32 and
 // 64, per-token and E8M0 scales, packed FP4 V, and keyword-only extensions (cu_q_lens, max_q_len,
 // return_lse, kv_format, rope_cos / rope_sin / rope_positions).  Every call goes straight to the C ABI of libcuda_llm_b200.so on the
@@ -119,6 +119,32 @@ torch::Tensor async_flash_decode_forward(torch::Tensor q, torch::Tensor k, torch
                                  num_kv_heads, seq_len, head_dim, scale_or_default(softmax_scale_opt, head_dim), dt,
                                  ws.data_ptr(), (size_t)ws.numel(), stream),
            "cuda_llm_flash_decode");
+  return output;
+}
+
+torch::Tensor fused_gqa_forward(torch::Tensor q, torch::Tensor k, torch::Tensor v, bool is_causal,
+                                c10::optional<double> softmax_scale_opt) {
+  TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "Inputs must be on CUDA");
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "Inputs must be 4D [batch, heads, seq, dim]");
+  TORCH_CHECK(k.sizes() == v.sizes(), "K and V must have identical shapes");
+  const int batch = q.size(0), num_q_heads = q.size(1), seq_len = q.size(2), head_dim = q.size(3);
+  const int num_kv_heads = k.size(1);
+  TORCH_CHECK(num_q_heads % num_kv_heads == 0, "num_q_heads must be divisible by num_kv_heads");
+  TORCH_CHECK(head_dim == 64 || head_dim == 128, "Only head_dim 64 and 128 supported");
+  const int dt = dtype_code(q, "Unsupported scalar type for GQA. Supported: Float32, Float16, BFloat16.");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type() && k.size(0) == batch &&
+                  k.size(2) == seq_len && k.size(3) == head_dim,
+              "q, k and v must share dtype, batch, sequence length and head_dim");
+  q = q.contiguous();
+  k = k.contiguous();
+  v = v.contiguous();
+  c10::cuda::CUDAGuard guard(q.device());
+  auto output = torch::empty_like(q);
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  check_rc(cuda_llm_gqa_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(), batch, num_q_heads,
+                                num_kv_heads, seq_len, head_dim, scale_or_default(softmax_scale_opt, head_dim),
+                                is_causal ? 1 : 0, dt, nullptr, stream),
+           "cuda_llm_gqa_prefill");
   return output;
 }
 
@@ -253,6 +279,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("softmax_scale") = pybind11::none());
   m.def("async_flash_decode", &async_flash_decode_forward, "Flash-Decoding over contiguous K/V",
         pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"),
+        pybind11::arg("softmax_scale") = pybind11::none());
+  m.def("fused_gqa_forward", &fused_gqa_forward, "Grouped-query attention forward over a whole prompt",
+        pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("is_causal") = true,
         pybind11::arg("softmax_scale") = pybind11::none());
   m.def("fp8_paged_attention_forward", &fp8_paged_attention_forward,
         "PagedAttention forward over a paged FP8-E4M3 / MXFP8 / MXFP4 KV cache",

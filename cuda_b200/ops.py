@@ -8,6 +8,8 @@ Signatures follow the reference binding (module ``fused_online_softmax_cuda``,
 * ``fp8_paged_attention_forward(query, key_cache_fp8, value_cache_fp8, k_scale, v_scale,
   block_tables, context_lens, softmax_scale=None)``                 binding ``:634-718``
 * ``async_flash_decode(q, k, v, softmax_scale=None)``               binding ``:308-360``
+* ``fused_gqa_forward(q, k, v, is_causal=True, softmax_scale=None)``  binding ``:246-302`` (the prefill
+  that fills the cache the decode path reads)
 
 and raise ``RuntimeError`` with the reference's messages where the reference's ``TORCH_CHECK``s
 fire.  Capabilities the reference does not have (GQA at decode, per-token / microscaling
@@ -323,6 +325,55 @@ def async_flash_decode(q, k, v, softmax_scale=None):
         L.check(lib.cuda_llm_flash_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), b, h, hkv, s, d,
                                           scale, _DTYPE[q.dtype], ws.data_ptr(), ws.numel(),
                                           _stream_ptr(q.device)), "cuda_llm_flash_decode")
+    return out
+
+
+def fused_gqa_forward(q, k, v, is_causal=True, softmax_scale=None, *, paged_kv=None):
+    """Grouped-query attention over a whole prompt: signature of the reference binding
+    ``fused_gqa_forward`` (``fused_softmax_binding.cpp:246-302``, ``m.def`` ``:751-756`` in the
+    reference project): q ``[B, Hq, S, D]``, k / v ``[B, Hkv, S, D]`` -> ``[B, Hq, S, D]``.
+
+    ``paged_kv=(key_cache, value_cache, k_scale, v_scale, slot_block, slot_offset)``: the same call
+    also quantises K / V into the paged cache (formats inferred from the tensors as in
+    ``fp8_paged_attention_forward``; ``slot_block`` / ``slot_offset`` int32 ``[B * S]``), so that the
+    prompt's KV is ready for the decode entry points."""
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("Inputs must be on CUDA")
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise RuntimeError("Inputs must be 4D [batch, heads, seq, dim]")
+    if k.shape != v.shape:
+        raise RuntimeError("K and V must have identical shapes")
+    b, hq, s, d = q.shape
+    hkv = k.shape[1]
+    if hq % hkv:
+        raise RuntimeError("num_q_heads must be divisible by num_kv_heads")
+    if d not in (64, 128):
+        raise RuntimeError("Only head_dim 64 and 128 supported")
+    if q.dtype not in _DTYPE:
+        raise RuntimeError("Unsupported scalar type for GQA. Supported: Float32, Float16, BFloat16.")
+    if k.dtype != q.dtype or v.dtype != q.dtype or k.shape[0] != b or k.shape[2] != s or k.shape[3] != d:
+        raise RuntimeError("q, k and v must share dtype, batch, sequence length and head_dim")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    scale = 1.0 / math.sqrt(d) if softmax_scale is None else float(softmax_scale)
+    target = None
+    if paged_kv is not None:
+        kc, vc, ks, vs, slot_block, slot_offset = paged_kv
+        mode = _scale_mode(ks)
+        v_format = L.KV_FP8_E4M3 if vc.shape[2] == d else L.KV_FP4_E2M1
+        slot_block = slot_block.to(device=q.device, dtype=torch.int32).contiguous()
+        slot_offset = slot_offset.to(device=q.device, dtype=torch.int32).contiguous()
+        if slot_block.numel() != b * s or slot_offset.numel() != b * s:
+            raise RuntimeError("slot_block / slot_offset need one entry per (batch, position)")
+        target = L.KvCacheTarget(key_cache=kc.data_ptr(), value_cache=vc.data_ptr(), k_scale=ks.data_ptr(),
+                                 v_scale=vs.data_ptr(), slot_block=slot_block.data_ptr(),
+                                 slot_offset=slot_offset.data_ptr(), status=None, page_size=kc.shape[3],
+                                 num_blocks=kc.shape[0], v_format=v_format, scale_mode=mode)
+    with torch.cuda.device(q.device):
+        out = torch.empty_like(q)
+        L.check(L.load().cuda_llm_gqa_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), b, hq, hkv, s, d,
+                                              scale, 1 if is_causal else 0, _DTYPE[q.dtype],
+                                              C.byref(target) if target is not None else None,
+                                              _stream_ptr(q.device)), "cuda_llm_gqa_prefill")
     return out
 
 

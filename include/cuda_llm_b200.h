@@ -238,6 +238,36 @@ int cuda_llm_kv_append(const void* k_new, const void* v_new, const int32_t* slot
                        int32_t page_size, int32_t num_blocks, int32_t in_dtype, int32_t v_format,
                        int32_t scale_mode, uint32_t* status, void* stream);
 
+/* ---- prefill ------------------------------------------------------------------------- */
+/* Where a prefill writes its K / V: the paged, quantised cache the decode entry points read.  Token
+ * s of batch row b goes to page slot_block[b * seq_len + s], offset slot_offset[b * seq_len + s];
+ * formats and scale modes as in cuda_llm_kv_append.  `status` may be NULL. */
+typedef struct CudaLlmKvCacheTarget {
+  void* key_cache;
+  void* value_cache;
+  void* k_scale;
+  void* v_scale;
+  const int32_t* slot_block;
+  const int32_t* slot_offset;
+  uint32_t* status;
+  int32_t page_size;
+  int32_t num_blocks;
+  int32_t v_format;   /* CudaLlmKvFormat: CUDA_LLM_KV_FP8_E4M3 or CUDA_LLM_KV_FP4_E2M1 */
+  int32_t scale_mode; /* CudaLlmScaleMode */
+} CudaLlmKvCacheTarget;
+
+/* Replaces dispatch_fused_gqa<T> (kernels_api.h:52-56; kernel fused_gqa_kernel.cuh:22-212):
+ * grouped-query attention over a whole prompt.  q, out [batch, num_q_heads, seq_len, head_dim],
+ * k, v [batch, num_kv_heads, seq_len, head_dim], one dtype (fp16 / bf16 run on the tensor cores,
+ * fp32 on a plain fp32 kernel), kv_head = q_head / (num_q_heads / num_kv_heads), causal mask
+ * "key position <= query position".  With `cache` not
+ * NULL the same call also quantises K and V into the paged cache (the prompt's KV is then ready
+ * for the decode entry points); the reference has no such output. */
+int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out, int32_t batch_size,
+                         int32_t num_q_heads, int32_t num_kv_heads, int32_t seq_len, int32_t head_dim,
+                         float softmax_scale, int32_t is_causal, int32_t dtype,
+                         const CudaLlmKvCacheTarget* cache, void* stream);
+
 /* Bit-exact dequantisation of whole pages to fp32 (test and debugging aid):
  * out [n_pages, Hkv, D, page] fp32 for the pages listed in `pages`. */
 int cuda_llm_dequant_pages(const void* cache, const void* scale, const int32_t* pages,

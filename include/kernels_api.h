@@ -1,10 +1,11 @@
 #pragma once
-// Host-side C++ entry points of the decode path, with the exact signatures the reference declares
-// for them (kernels_api.h:35-41, 58-62, 94-101 in the reference project), so that the reference's
+// Host-side C++ entry points of the decode path and of the prefill that fills its cache, with the
+// exact signatures the reference declares for them (kernels_api.h:35-41, 52-56, 58-62, 94-101 in
+// the reference project), so that the reference's
 // PyTorch binding (fused_softmax_binding.cpp) links against libcuda_llm_b200.so unchanged.  They are
 // explicitly instantiated for float, __half and __nv_bfloat16 as in the reference
-// (paged_attention_instantiations.cu, async_flash_decode_instantiations.cu,
-// fp8_paged_attention_instantiations.cu).  No default arguments: the caller always passes the stream.
+// (paged_attention_instantiations.cu, fused_gqa_instantiations.cu,
+// async_flash_decode_instantiations.cu, fp8_paged_attention_instantiations.cu).  No default arguments: the caller always passes the stream.
 //
 // Differences in behaviour, all on the side of saying more: the 8-bit cache bytes are E4M3 codes;
 // page sizes 32 and 64 work; an unsupported shape or a CUDA error is reported on stderr instead of
@@ -20,6 +21,11 @@ void dispatch_paged_attention(const T* query, const T* key_cache, const T* value
                               const int32_t* block_tables, const int32_t* context_lens, T* out,
                               int num_seqs, int num_heads, int head_dim, int max_blocks_per_seq,
                               float softmax_scale, cudaStream_t stream);
+
+template <typename T>
+void dispatch_fused_gqa(const T* q, const T* k, const T* v, T* o, int batch_size, int num_q_heads,
+                        int num_kv_heads, int seq_len, int head_dim, float softmax_scale,
+                        bool is_causal, cudaStream_t stream);
 
 template <typename T>
 void dispatch_async_flash_decode(const T* q, const T* k, const T* v, T* o, int batch_size,

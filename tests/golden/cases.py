@@ -75,3 +75,23 @@ def rope_inputs(dtype, head_dim, seq_len):
     k = torch.randn(2, 4, seq_len, head_dim, dtype=dtype)
     v = torch.randn(2, 4, seq_len, head_dim, dtype=dtype)
     return q, k, v
+
+
+GQA_ROWS = (0, 37, 99)      # query positions whose reference output rows the fixture keeps
+
+
+def gqa_cases():
+    """The reference's own GQA test grid (``tests/test_attention.py:43-54`` there)."""
+    for dn, dt in DTYPES.items():
+        for hd in (64, 128):
+            for hq, hkv in ((8, 2), (8, 8), (4, 1)):
+                for causal in (False, True):
+                    yield f"gqa_{dn}_d{hd}_h{hq}_{hkv}_{'c' if causal else 'n'}", dt, hd, hq, hkv, causal
+
+
+def gqa_inputs(dtype, head_dim, hq, hkv, seq_len=100):
+    torch.manual_seed(0)
+    q = torch.randn(1, hq, seq_len, head_dim, dtype=dtype)
+    k = torch.randn(1, hkv, seq_len, head_dim, dtype=dtype)
+    v = torch.randn(1, hkv, seq_len, head_dim, dtype=dtype)
+    return q, k, v

@@ -8,7 +8,7 @@ It imports the reference's ``tests/_utils.py`` (``make_paged_cache``, ``ref_deco
 ``ref_attention``) and replays the reference's own test cases
 (``tests/test_kernels_misc.py:26-35`` paged, ``:42-64`` E4M3 paged,
 ``tests/test_attention.py:76-86`` decode, ``ref_rope_attention`` of ``tests/_utils.py:91-93`` for the
-rotary case) on the CPU with the same seed rule
+rotary case, ``ref_gqa`` ``:67-72`` on the grid of ``tests/test_attention.py:43-54`` for the prefill) on the CPU with the same seed rule
 (``tests/conftest.py:31-33``: ``torch.manual_seed(0)`` before every case).  Inputs are
 regenerated from the seed by ``tests/golden/cases.py`` at test time; the fixture keeps the
 reference outputs, the block tables the reference drew, and CRC32s of the paged caches so
@@ -74,6 +74,13 @@ def main(ref_root: str):
         out[f"{name}/out_last"] = o[:, :, -1, :].contiguous().numpy()          # [B, H, D]
         k_rot = ref.apply_rope(k, cos, sin).to(dtype)                           # what the cache holds
         out[f"{name}/crc"] = np.array([crc(q), crc(k), crc(v), crc(cos), crc(sin), crc(k_rot)], dtype=np.uint32)
+
+    # ---- GQA prefill: the reference's own test grid, sampled output rows --------------------------
+    for name, dtype, head_dim, hq, hkv, causal in cases.gqa_cases():
+        q, k, v = cases.gqa_inputs(dtype, head_dim, hq, hkv)
+        o = ref.ref_gqa(q, k, v, is_causal=causal)                              # [1, Hq, S, D] fp32
+        out[f"{name}/rows"] = o[:, :, list(cases.GQA_ROWS), :].contiguous().numpy()
+        out[f"{name}/crc"] = np.array([crc(q), crc(k), crc(v), crc(o)], dtype=np.uint32)
 
     path = os.path.join(HERE, "reference_cases.npz")
     np.savez_compressed(path, **out)

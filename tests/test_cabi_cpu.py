@@ -118,6 +118,9 @@ CXX_SYMBOLS = {
     ("fp8", "f32"): "_Z28dispatch_fp8_paged_attentionIffEvPKT0_PKaS4_PKfS6_PKiS8_PT_iiiiifbP11CUstream_st",
     ("fp8", "f16"): "_Z28dispatch_fp8_paged_attentionI6__halfS0_EvPKT0_PKaS5_PKfS7_PKiS9_PT_iiiiifbP11CUstream_st",
     ("fp8", "bf16"): "_Z28dispatch_fp8_paged_attentionI13__nv_bfloat16S0_EvPKT0_PKaS5_PKfS7_PKiS9_PT_iiiiifbP11CUstream_st",
+    ("gqa", "f32"): "_Z18dispatch_fused_gqaIfEvPKT_S2_S2_PS0_iiiiifbP11CUstream_st",
+    ("gqa", "f16"): "_Z18dispatch_fused_gqaI6__halfEvPKT_S3_S3_PS1_iiiiifbP11CUstream_st",
+    ("gqa", "bf16"): "_Z18dispatch_fused_gqaI13__nv_bfloat16EvPKT_S3_S3_PS1_iiiiifbP11CUstream_st",
 }
 
 

@@ -1,0 +1,97 @@
+"""GQA prefill (the reference's fused_gqa_forward) and its paged-KV output."""
+import pytest
+import torch
+
+import cases
+from oracle import paged_decode_oracle as O
+
+pytestmark = pytest.mark.gpu
+REF_TOL = {torch.float16: (2e-2, 2e-2), torch.bfloat16: (4e-2, 4e-2), torch.float32: (1e-4, 1e-4)}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cuda_b200 import ops as _ops
+    _ops.L.load()
+    return _ops
+
+
+@pytest.mark.parametrize("case", list(cases.gqa_cases()), ids=lambda c: c[0])
+def test_reference_gqa_cases(ops, golden, case):
+    """The reference's own test grid (tests/test_attention.py:43-54 there): sampled rows against the
+    outputs of its ref_gqa, every row against the oracle (which reproduces ref_gqa bit for bit)."""
+    name, dtype, hd, hq, hkv, causal = case
+    q, k, v = cases.gqa_inputs(dtype, hd, hq, hkv)
+    out = ops.fused_gqa_forward(q.cuda(), k.cuda(), v.cuda(), is_causal=causal)
+    atol, rtol = REF_TOL[dtype]
+    assert out.dtype == dtype and out.shape == q.shape and torch.isfinite(out).all()
+    rows = torch.from_numpy(golden[f"{name}/rows"])
+    assert torch.allclose(out[:, :, list(cases.GQA_ROWS), :].float().cpu(), rows, atol=atol, rtol=rtol)
+    assert torch.allclose(out.float().cpu(), O.ref_gqa(q, k, v, causal), atol=atol, rtol=rtol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("b,hq,hkv,s,d,causal", [(2, 32, 8, 300, 128, True), (1, 12, 4, 129, 64, True),
+                                                 (3, 16, 1, 64, 128, False), (1, 6, 2, 1, 64, True),
+                                                 (2, 5, 5, 77, 128, True), (1, 24, 2, 200, 64, False)])
+def test_gqa_shapes(ops, dtype, b, hq, hkv, s, d, causal):
+    """Group sizes 1..16 (more than eight heads per KV head are split over CTAs), ragged lengths, all
+    three dtypes of the reference's instantiations."""
+    g = torch.Generator().manual_seed(b * 1000 + s)
+    q = torch.randn(b, hq, s, d, generator=g).to(dtype)
+    k = torch.randn(b, hkv, s, d, generator=g).to(dtype)
+    v = torch.randn(b, hkv, s, d, generator=g).to(dtype)
+    out = ops.fused_gqa_forward(q.cuda(), k.cuda(), v.cuda(), is_causal=causal)
+    atol, rtol = REF_TOL[dtype]
+    assert torch.allclose(out.float().cpu(), O.ref_gqa(q, k, v, causal), atol=atol, rtol=rtol)
+
+
+@pytest.mark.parametrize("mode,vfmt", [("per_token", "fp8_e4m3"), ("mx_e8m0", "fp8_e4m3"), ("mx_e8m0", "fp4_e2m1")])
+def test_prefill_fills_the_paged_cache_for_decode(ops, mode, vfmt):
+    """Prefill with a paged-KV target, then one decode step over the cache it wrote: the cache bytes and
+    scales equal the host recipe bit for bit, and the decode output matches the oracle on that cache."""
+    from cuda_b200 import workloads as W
+    from helpers import assert_parity
+    b, hq, hkv, s, d, page = 2, 16, 4, 150, 128, 16
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(b, hq, s, d, generator=g).to(torch.bfloat16)
+    k = torch.randn(b, hkv, s, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(b, hkv, s, d, generator=g).to(torch.bfloat16)
+    n_pages = (s + page - 1) // page
+    pool = b * n_pages + 3
+    perm = torch.randperm(pool, generator=g)[: b * n_pages]
+    bt = perm.view(b, n_pages).to(torch.int32)
+    pos = torch.arange(s)
+    slot_block = bt[:, pos // page].reshape(-1)
+    slot_offset = (pos % page).repeat(b).to(torch.int32)
+    dv = d if vfmt == "fp8_e4m3" else d // 2
+    kc = torch.zeros(pool, hkv, d, page, dtype=torch.uint8, device="cuda")
+    vc = torch.zeros(pool, hkv, dv, page, dtype=torch.uint8, device="cuda")
+    if mode == "per_token":
+        ks = torch.ones(pool, hkv, page, device="cuda")
+        vs = torch.ones(pool, hkv, page, device="cuda")
+    else:
+        ks = torch.full((pool, hkv, d // 32, page), 127, dtype=torch.uint8, device="cuda")
+        vs = torch.full((pool, hkv, d // 32, page), 127, dtype=torch.uint8, device="cuda")
+    out = ops.fused_gqa_forward(q.cuda(), k.cuda(), v.cuda(), is_causal=True,
+                                paged_kv=(kc, vc, ks, vs, slot_block, slot_offset))
+    assert torch.allclose(out.float().cpu(), O.ref_gqa(q, k, v, True), atol=4e-2, rtol=4e-2)
+    # the cache against the host statement of the write recipe, token by token
+    kt = k.permute(0, 2, 1, 3).reshape(b * s, hkv, d).float()
+    vt = v.permute(0, 2, 1, 3).reshape(b * s, hkv, d).float()
+    kq, ksc = W.quantize_tokens(kt, "fp8_e4m3", mode)
+    vq, vsc = W.quantize_tokens(vt, vfmt, mode)
+    sb, so = slot_block.long(), slot_offset.long()
+    assert torch.equal(kc.cpu()[sb, :, :, so], kq)
+    assert torch.equal(vc.cpu()[sb, :, :, so], vq)
+    if mode == "per_token":
+        assert torch.equal(ks.cpu()[sb, :, so], ksc) and torch.equal(vs.cpu()[sb, :, so], vsc)
+    else:
+        assert torch.equal(ks.cpu()[sb, :, :, so], ksc) and torch.equal(vs.cpu()[sb, :, :, so], vsc)
+    # one decode step over what the prefill wrote
+    ctx = torch.full((b,), s, dtype=torch.int32)
+    qd = torch.randn(b, hq, d, generator=g).to(torch.bfloat16)
+    kv = O.PagedKV(kc.cpu(), vc.cpu(), bt, ctx, page, d, "fp8_e4m3", vfmt, mode, mode, ks.cpu(), vs.cpu())
+    ref = O.ref_paged_decode(qd, kv)
+    dec = ops.fp8_paged_attention_forward(qd.cuda(), kc, vc, ks, vs, bt.cuda(), ctx.cuda(), check_status=True)
+    assert_parity(dec, ref, torch.bfloat16, "decode after prefill")

@@ -152,3 +152,16 @@ def test_rope_oracle_matches_reference(golden, case):
     q_rot = O.rope_query(q_last, cos, sin, ctx)
     out = O.ref_flash_decode(q_rot[:, :, None, :], O.apply_rope(k, cos, sin), v)[:, :, 0]
     assert torch.allclose(out, torch.from_numpy(golden[f"{name}/out_last"]), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("case", list(cases.gqa_cases()), ids=lambda c: c[0])
+def test_gqa_oracle_matches_reference(golden, case):
+    """ref_gqa of the oracle reproduces the reference's ref_gqa on its own test grid: same inputs (CRC),
+    the whole output tensor bit for bit (CRC) and the sampled rows the fixture keeps."""
+    import zlib
+    name, dtype, hd, hq, hkv, causal = case
+    q, k, v = cases.gqa_inputs(dtype, hd, hq, hkv)
+    o = O.ref_gqa(q, k, v, is_causal=causal)
+    crc = lambda t: zlib.crc32(t.contiguous().view(torch.uint8).numpy().tobytes())
+    assert [crc(q), crc(k), crc(v), crc(o)] == golden[f"{name}/crc"].tolist()
+    assert torch.equal(o[:, :, list(cases.GQA_ROWS), :], torch.from_numpy(golden[f"{name}/rows"]))

@@ -1,5 +1,5 @@
 """The reference's own binding TU (fused_softmax_binding.cpp, compiled unchanged with the three decode
-entry points switched on) linked against libcuda_llm_b200.so: its Python functions replay the
+entry points and the GQA prefill switched on) linked against libcuda_llm_b200.so: its Python functions replay the
 reference's test cases on this library's kernels.  Built by `make -C oracle refbinding` where the
 reference checkout is mounted; the test is skipped where that build is absent.  Runs in a child
 process because the module carries the same name as this repository's own extension."""
@@ -46,6 +46,12 @@ for name, dtype, hd, kv_len in cases.decode_cases():
     q, k, v = cases.decode_inputs(dtype, hd, kv_len)
     out = ext.async_flash_decode(q.cuda(), k.cuda(), v.cuda())
     assert torch.allclose(out.float().cpu(), torch.from_numpy(golden[f"{name}/out"]), atol=TOL[dtype][0], rtol=TOL[dtype][1]), name
+    n += 1
+for name, dtype, hd, hq, hkv, causal in cases.gqa_cases():
+    q, k, v = cases.gqa_inputs(dtype, hd, hq, hkv)
+    out = ext.fused_gqa_forward(q.cuda(), k.cuda(), v.cuda(), is_causal=causal)
+    rows = torch.from_numpy(golden[f"{name}/rows"])
+    assert torch.allclose(out[:, :, list(cases.GQA_ROWS), :].float().cpu(), rows, atol=TOL[dtype][0], rtol=TOL[dtype][1]), name
     n += 1
 print("REFERENCE BINDING OK", n)
 '''
