@@ -18,6 +18,9 @@ cudaError_t launch_dequant_pages(const void*, const void*, const int32_t*, int, 
 
 cudaError_t run_gqa_prefill(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hkv, int S,
                             int D, float softmax_scale, bool causal, int dtype, cudaStream_t st);
+cudaError_t run_mx_attention(const void* q, const float* qs, const void* k, const float* ks, const void* v,
+                             const float* vs, void* out, int B, int Hq, int Hkv, int S, int D, float softmax_scale,
+                             bool causal, int out_dtype, cudaStream_t st);
 cudaError_t run_kv_append_prefill(const void* k, const void* v, const CudaLlmKvCacheTarget& c, int B, int Hkv, int S,
                                   int D, int in_dtype, cudaStream_t st);
 size_t dense_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens);
@@ -617,6 +620,26 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
     if (e != cudaSuccess) return fail_cuda(e, "kv_append_kernel launch");
   }
   return CUDA_LLM_OK;
+}
+
+int cuda_llm_mx_attention(const void* q, const float* q_scale, const void* k, const float* k_scale, const void* v,
+                          const float* v_scale, void* out, int32_t batch_size, int32_t num_q_heads,
+                          int32_t num_kv_heads, int32_t seq_len, int32_t head_dim, float softmax_scale,
+                          int32_t is_causal, int32_t out_dtype, void* stream) {
+  if (batch_size == 0 || seq_len == 0) return CUDA_LLM_OK;
+  if (!q || !k || !v || !q_scale || !k_scale || !v_scale || !out) return fail(CUDA_LLM_EINVAL, "a required tensor pointer is null");
+  if (batch_size < 0 || seq_len < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads)
+    return fail(CUDA_LLM_EINVAL, "num_q_heads must be divisible by num_kv_heads");
+  if (head_dim != 64 && head_dim != 128) return fail(CUDA_LLM_EINVAL, "Only head_dim 64 and 128 supported");
+  if (out_dtype < 0 || out_dtype > CUDA_LLM_BF16) return fail(CUDA_LLM_EINVAL, "unknown dtype");
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
+    return fail(CUDA_LLM_EALIGN, "q, k, v and out must be 16-byte aligned");
+  const int rc = check_device();
+  if (rc != CUDA_LLM_OK) return rc;
+  cudaError_t e = run_mx_attention(q, q_scale, k, k_scale, v, v_scale, out, batch_size, num_q_heads, num_kv_heads,
+                                   seq_len, head_dim, softmax_scale, is_causal != 0, out_dtype,
+                                   reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "gqa_prefill_kernel (microscaled) launch");
 }
 
 int cuda_llm_merge_partials(const float* parts_out, const float* parts_lse, int32_t num_parts,

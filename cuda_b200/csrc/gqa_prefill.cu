@@ -25,6 +25,11 @@ struct PrefillArgs {
   int B, Hq, Hkv, S, group, n_chunks;
   int causal;
   float scale_log2;
+  // microscaled inputs (MXQ kernels): q / k / v are E4M3 bytes, one fp32 scale per 32 elements of head_dim
+  const float* qs;  // [B, Hq, S, D/32]
+  const float* ks;  // [B, Hkv, S, D/32]
+  const float* vs;
+  int out_dtype;    // CudaLlmDType of `out` (MXQ kernels; the 16-bit kernels write their input dtype)
 };
 
 constexpr int kPfWarps = 8;
@@ -35,7 +40,23 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool 
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
 }
 
-template <int D, bool BF>
+// 16 E4M3 codes (one 16-byte load) times their block scale -> 16 f16 values (two 16-byte chunks).
+// E4M3 -> f16 is exact; the product is rounded to f16 once.
+__device__ __forceinline__ void dequant16(const uint4 codes, float scale, uint4& lo, uint4& hi) {
+  auto two = [&](uint32_t h2) -> uint32_t { return pack_f16x2(f16x2_lo(h2) * scale, f16x2_hi(h2) * scale); };
+  lo.x = two(e4m3x2_to_f16x2_lo(codes.x)); lo.y = two(e4m3x2_to_f16x2_hi(codes.x));
+  lo.z = two(e4m3x2_to_f16x2_lo(codes.y)); lo.w = two(e4m3x2_to_f16x2_hi(codes.y));
+  hi.x = two(e4m3x2_to_f16x2_lo(codes.z)); hi.y = two(e4m3x2_to_f16x2_hi(codes.z));
+  hi.z = two(e4m3x2_to_f16x2_lo(codes.w)); hi.w = two(e4m3x2_to_f16x2_hi(codes.w));
+}
+__device__ __forceinline__ void sts128u(uint32_t addr, const uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// MXQ: the tensors are E4M3 bytes with fp32 block scales; tiles are dequantised to f16 on their way
+// into shared memory (dispatch_fused_microscaled_attention, kernels_api.h:103-108 in the reference
+// project, declared there without a definition).
+template <int D, bool BF, bool MXQ>
 __global__ void __launch_bounds__(kPfWarps * 32) gqa_prefill_kernel(const PrefillArgs a) {
   constexpr int PITCH = D * 2;          // bytes per row
   constexpr int CHUNKS = PITCH / 16;    // 16-byte chunks per row
@@ -63,15 +84,35 @@ __global__ void __launch_bounds__(kPfWarps * 32) gqa_prefill_kernel(const Prefil
   const int qh = kvh * a.group + chunk * 8 + (active ? hi : 0);
   const int qrow0 = q0 + 16 * jw;                           // first query position of this warp
 
+  constexpr int EB = MXQ ? 1 : 2;                           // bytes per element in global memory
   const size_t kv_base = ((size_t)b * a.Hkv + kvh) * (size_t)a.S * D;
-  const uint8_t* kg = reinterpret_cast<const uint8_t*>(a.k) + kv_base * 2;
-  const uint8_t* vg = reinterpret_cast<const uint8_t*>(a.v) + kv_base * 2;
+  const uint8_t* kg = reinterpret_cast<const uint8_t*>(a.k) + kv_base * EB;
+  const uint8_t* vg = reinterpret_cast<const uint8_t*>(a.v) + kv_base * EB;
+  const float* ksg = MXQ ? a.ks + kv_base / 32 : nullptr;
+  const float* vsg = MXQ ? a.vs + kv_base / 32 : nullptr;
 
   const int last_q = min(a.S, q0 + BQ) - 1;
   const int n_tiles = a.causal ? min((a.S + kPfBc - 1) / kPfBc, last_q / kPfBc + 1) : (a.S + kPfBc - 1) / kPfBc;
 
   auto load_tile = [&](int tile, int stage) {
     const int kv0 = tile * kPfBc;
+    if (MXQ) {
+      // 16 codes per thread and step: one 16-byte load, one scale, two swizzled 16-byte stores
+      for (int i = tid; i < kPfBc * (D / 16); i += kPfWarps * 32) {
+        const int r = i / (D / 16), c16 = i - r * (D / 16);
+        uint4 klo = make_uint4(0, 0, 0, 0), khi = klo, vlo = klo, vhi = klo;
+        if (kv0 + r < a.S) {
+          const size_t row = (size_t)(kv0 + r);
+          dequant16(*reinterpret_cast<const uint4*>(kg + row * D + c16 * 16), ksg[row * (D / 32) + (c16 >> 1)], klo, khi);
+          dequant16(*reinterpret_cast<const uint4*>(vg + row * D + c16 * 16), vsg[row * (D / 32) + (c16 >> 1)], vlo, vhi);
+        }
+        sts128u(sK + stage * (kPfBc * PITCH) + swz(r, 2 * c16), klo);
+        sts128u(sK + stage * (kPfBc * PITCH) + swz(r, 2 * c16 + 1), khi);
+        sts128u(sV + stage * (kPfBc * PITCH) + swz(r, 2 * c16), vlo);
+        sts128u(sV + stage * (kPfBc * PITCH) + swz(r, 2 * c16 + 1), vhi);
+      }
+      return;
+    }
     for (int i = tid; i < kPfBc * CHUNKS; i += kPfWarps * 32) {
       const int r = i / CHUNKS, c = i - r * CHUNKS;
       const bool ok = kv0 + r < a.S;
@@ -82,7 +123,20 @@ __global__ void __launch_bounds__(kPfWarps * 32) gqa_prefill_kernel(const Prefil
   };
 
   // Q rows of this warp -> shared memory -> A fragments (kept in registers for the whole CTA)
-  {
+  if (MXQ) {
+    const size_t qb = ((size_t)b * a.Hq + qh) * (size_t)a.S;
+    const uint8_t* qg = reinterpret_cast<const uint8_t*>(a.q) + qb * D;
+    for (int i = lane; i < 16 * (D / 16); i += 32) {
+      const int r = i / (D / 16), c16 = i - r * (D / 16);
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+      if (active && qrow0 + r < a.S) {
+        const size_t row = (size_t)(qrow0 + r);
+        dequant16(*reinterpret_cast<const uint4*>(qg + row * D + c16 * 16), a.qs[(qb + row) * (D / 32) + (c16 >> 1)], lo, hi);
+      }
+      sts128u(sQ + warp * (16 * PITCH) + swz(r, 2 * c16), lo);
+      sts128u(sQ + warp * (16 * PITCH) + swz(r, 2 * c16 + 1), hi);
+    }
+  } else {
     const uint8_t* qg = reinterpret_cast<const uint8_t*>(a.q) + (((size_t)b * a.Hq + qh) * (size_t)a.S) * D * 2;
     for (int i = lane; i < 16 * CHUNKS; i += 32) {
       const int r = i / CHUNKS, c = i - r * CHUNKS;
@@ -207,6 +261,7 @@ __global__ void __launch_bounds__(kPfWarps * 32) gqa_prefill_kernel(const Prefil
   }
   const float inv[2] = {l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, l_run[1] > 0.f ? 1.f / l_run[1] : 0.f};
   uint32_t* og = reinterpret_cast<uint32_t*>(a.out);
+  const int odt = MXQ ? a.out_dtype : (BF ? CUDA_LLM_BF16 : CUDA_LLM_F16);
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int qpos = qrow0 + g + 8 * r;
@@ -215,14 +270,16 @@ __global__ void __launch_bounds__(kPfWarps * 32) gqa_prefill_kernel(const Prefil
 #pragma unroll
     for (int i = 0; i < DT; ++i) {
       const float x0 = oacc[i][2 * r] * inv[r], x1 = oacc[i][2 * r + 1] * inv[r];
-      og[(row + 8 * i + 2 * t) >> 1] = BF ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
+      const size_t e = row + 8 * i + 2 * t;
+      if (odt == CUDA_LLM_F32) *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + e) = make_float2(x0, x1);
+      else og[e >> 1] = (odt == CUDA_LLM_BF16) ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
     }
   }
 }
 
-template <int D, bool BF>
+template <int D, bool BF, bool MXQ = false>
 static cudaError_t launch_prefill(const PrefillArgs& a, cudaStream_t st) {
-  auto kern = gqa_prefill_kernel<D, BF>;
+  auto kern = gqa_prefill_kernel<D, BF, MXQ>;
   constexpr int smem = (kPfWarps * 16 + 4 * kPfBc) * D * 2;
   static int configured[64] = {0};
   int dev = 0;
@@ -309,6 +366,7 @@ cudaError_t run_gqa_prefill(const void* q, const void* k, const void* v, void* o
                             int D, float softmax_scale, bool causal, int dtype, cudaStream_t st) {
   PrefillArgs a;
   a.q = q; a.k = k; a.v = v; a.out = out;
+  a.qs = a.ks = a.vs = nullptr; a.out_dtype = dtype;
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.group = Hq / Hkv;
   a.n_chunks = (a.group + 7) / 8;
   a.causal = causal ? 1 : 0;
@@ -322,6 +380,20 @@ cudaError_t run_gqa_prefill(const void* q, const void* k, const void* v, void* o
   }
   if (dtype == CUDA_LLM_BF16) return D == 64 ? launch_prefill<64, true>(a, st) : launch_prefill<128, true>(a, st);
   return D == 64 ? launch_prefill<64, false>(a, st) : launch_prefill<128, false>(a, st);
+}
+
+cudaError_t run_mx_attention(const void* q, const float* qs, const void* k, const float* ks, const void* v,
+                             const float* vs, void* out, int B, int Hq, int Hkv, int S, int D, float softmax_scale,
+                             bool causal, int out_dtype, cudaStream_t st) {
+  PrefillArgs a;
+  a.q = q; a.k = k; a.v = v; a.out = out;
+  a.qs = qs; a.ks = ks; a.vs = vs; a.out_dtype = out_dtype;
+  a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.group = Hq / Hkv;
+  a.n_chunks = (a.group + 7) / 8;
+  a.causal = causal ? 1 : 0;
+  a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  if (B == 0 || S == 0) return cudaSuccess;
+  return D == 64 ? launch_prefill<64, false, true>(a, st) : launch_prefill<128, false, true>(a, st);
 }
 
 }  // namespace b200

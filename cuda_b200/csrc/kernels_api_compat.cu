@@ -100,6 +100,16 @@ void dispatch_fp8_paged_attention(const T_Q* query, const int8_t* key_cache_fp8,
   if (p.workspace) cudaFreeAsync(p.workspace, stream);
 }
 
+template <typename T_OUT>
+void dispatch_fused_microscaled_attention(const int8_t* q, const float* q_scale, const int8_t* k,
+                                          const float* k_scale, const int8_t* v, const float* v_scale, T_OUT* out,
+                                          int batch_size, int num_heads, int seq_len, int head_dim,
+                                          float softmax_scale, bool is_causal, cudaStream_t stream) {
+  report("dispatch_fused_microscaled_attention",
+         cuda_llm_mx_attention(q, q_scale, k, k_scale, v, v_scale, out, batch_size, num_heads, num_heads, seq_len,
+                               head_dim, softmax_scale, is_causal ? 1 : 0, dtype_of<T_OUT>(), stream));
+}
+
 #define INSTANTIATE(T)                                                                                        \
   template void dispatch_paged_attention<T>(const T*, const T*, const T*, const int32_t*, const int32_t*, T*, \
                                             int, int, int, int, float, cudaStream_t);                         \
@@ -107,6 +117,9 @@ void dispatch_fp8_paged_attention(const T_Q* query, const int8_t* key_cache_fp8,
                                                cudaStream_t);                                                 \
   template void dispatch_fused_gqa<T>(const T*, const T*, const T*, T*, int, int, int, int, int, float, bool,           \
                                       cudaStream_t);                                                          \
+  template void dispatch_fused_microscaled_attention<T>(const int8_t*, const float*, const int8_t*, const float*,   \
+                                                        const int8_t*, const float*, T*, int, int, int, int, float, \
+                                                        bool, cudaStream_t);                                        \
   template void dispatch_fp8_paged_attention<T, T>(const T*, const int8_t*, const int8_t*, const float*,      \
                                                    const float*, const int32_t*, const int32_t*, T*, int, int, \
                                                    int, int, int, float, bool, cudaStream_t);

@@ -377,6 +377,45 @@ def fused_gqa_forward(q, k, v, is_causal=True, softmax_scale=None, *, paged_kv=N
     return out
 
 
+def fused_microscaled_attention(q, q_scale, k, k_scale, v, v_scale, is_causal=True, softmax_scale=None, *,
+                                out_dtype=torch.bfloat16):
+    """Dense attention over microscaled FP8 tensors (the reference declares
+    ``dispatch_fused_microscaled_attention``, ``kernels_api.h:103-108`` in the reference project,
+    without a definition or a binding): q ``[B, Hq, S, D]``, k / v ``[B, Hkv, S, D]`` E4M3 codes
+    (uint8 / float8_e4m3fn), ``*_scale [B, H, S, D/32]`` fp32, one per 32 elements of head_dim."""
+    for t_ in (q, k, v, q_scale, k_scale, v_scale):
+        if not t_.is_cuda:
+            raise RuntimeError("Inputs must be on CUDA")
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise RuntimeError("Inputs must be 4D [batch, heads, seq, dim]")
+    if k.shape != v.shape:
+        raise RuntimeError("K and V must have identical shapes")
+    for t_ in (q, k, v):
+        if t_.dtype not in (torch.uint8, torch.float8_e4m3fn):
+            raise RuntimeError("q, k and v must hold E4M3 codes (uint8 or float8_e4m3fn)")
+    b, hq, s, d = q.shape
+    hkv = k.shape[1]
+    if hq % hkv:
+        raise RuntimeError("num_q_heads must be divisible by num_kv_heads")
+    if d not in (64, 128):
+        raise RuntimeError("Only head_dim 64 and 128 supported")
+    if tuple(q_scale.shape) != (b, hq, s, d // 32) or tuple(k_scale.shape) != (b, hkv, s, d // 32) \
+            or tuple(v_scale.shape) != (b, hkv, s, d // 32):
+        raise RuntimeError("scales must be [batch, heads, seq, head_dim/32]")
+    if out_dtype not in _DTYPE:
+        raise RuntimeError("Unsupported output scalar type. Supported: Float32, Float16, BFloat16.")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    qs, ks, vs = (x.to(torch.float32).contiguous() for x in (q_scale, k_scale, v_scale))
+    scale = 1.0 / math.sqrt(d) if softmax_scale is None else float(softmax_scale)
+    with torch.cuda.device(q.device):
+        out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
+        L.check(L.load().cuda_llm_mx_attention(q.data_ptr(), qs.data_ptr(), k.data_ptr(), ks.data_ptr(), v.data_ptr(),
+                                               vs.data_ptr(), out.data_ptr(), b, hq, hkv, s, d, scale,
+                                               1 if is_causal else 0, _DTYPE[out_dtype], _stream_ptr(q.device)),
+                "cuda_llm_mx_attention")
+    return out
+
+
 flash_decode = async_flash_decode      # the name the reference's README gives the Python-level call
 
 

@@ -268,6 +268,18 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
                          float softmax_scale, int32_t is_causal, int32_t dtype,
                          const CudaLlmKvCacheTarget* cache, void* stream);
 
+/* Replaces dispatch_fused_microscaled_attention<T_OUT> (kernels_api.h:103-108; the reference declares
+ * it and ships no definition, test or Python binding, so the semantics are fixed here): dense
+ * attention over microscaled FP8 tensors.  q [batch, num_q_heads, seq_len, head_dim] and k, v
+ * [batch, num_kv_heads, seq_len, head_dim] hold E4M3 codes, *_scale [batch, heads, seq_len,
+ * head_dim/32] one fp32 scale per 32 consecutive elements of head_dim; out [batch, num_q_heads,
+ * seq_len, head_dim] of out_dtype = softmax(Q K^T * softmax_scale [+ causal mask]) V over the
+ * dequantised tensors. */
+int cuda_llm_mx_attention(const void* q, const float* q_scale, const void* k, const float* k_scale, const void* v,
+                          const float* v_scale, void* out, int32_t batch_size, int32_t num_q_heads,
+                          int32_t num_kv_heads, int32_t seq_len, int32_t head_dim, float softmax_scale,
+                          int32_t is_causal, int32_t out_dtype, void* stream);
+
 /* Bit-exact dequantisation of whole pages to fp32 (test and debugging aid):
  * out [n_pages, Hkv, D, page] fp32 for the pages listed in `pages`. */
 int cuda_llm_dequant_pages(const void* cache, const void* scale, const int32_t* pages,

@@ -1,6 +1,6 @@
 #pragma once
 // Host-side C++ entry points of the decode path and of the prefill that fills its cache, with the
-// exact signatures the reference declares for them (kernels_api.h:35-41, 52-56, 58-62, 94-101 in
+// exact signatures the reference declares for them (kernels_api.h:35-41, 52-56, 58-62, 94-101, 103-108 in
 // the reference project), so that the reference's
 // PyTorch binding (fused_softmax_binding.cpp) links against libcuda_llm_b200.so unchanged.  They are
 // explicitly instantiated for float, __half and __nv_bfloat16 as in the reference
@@ -39,3 +39,12 @@ void dispatch_fp8_paged_attention(const T_Q* query, const int8_t* key_cache_fp8,
                                   const int32_t* context_lens, T_OUT* out, int num_seqs,
                                   int num_heads, int head_dim, int max_blocks_per_seq, int page_size,
                                   float softmax_scale, bool per_block_scales, cudaStream_t stream);
+
+// Declared by the reference (kernels_api.h:103-108) without a definition; here: E4M3 codes with one
+// fp32 scale per 32 elements of head_dim, scales laid out [batch, heads, seq_len, head_dim / 32].
+template <typename T_OUT>
+void dispatch_fused_microscaled_attention(const int8_t* q, const float* q_scale, const int8_t* k,
+                                          const float* k_scale, const int8_t* v, const float* v_scale,
+                                          T_OUT* out, int batch_size, int num_heads, int seq_len,
+                                          int head_dim, float softmax_scale, bool is_causal,
+                                          cudaStream_t stream);

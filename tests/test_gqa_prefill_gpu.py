@@ -95,3 +95,37 @@ def test_prefill_fills_the_paged_cache_for_decode(ops, mode, vfmt):
     ref = O.ref_paged_decode(qd, kv)
     dec = ops.fp8_paged_attention_forward(qd.cuda(), kc, vc, ks, vs, bt.cuda(), ctx.cuda(), check_status=True)
     assert_parity(dec, ref, torch.bfloat16, "decode after prefill")
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("b,hq,hkv,s,d,causal", [(2, 8, 8, 200, 128, True), (1, 16, 4, 77, 64, False),
+                                                 (1, 4, 4, 1, 128, True)])
+def test_microscaled_attention(ops, out_dtype, b, hq, hkv, s, d, causal):
+    """Dense attention over E4M3 tensors with one fp32 scale per 32 elements of head_dim (the entry
+    point the reference declares and never defines), against the oracle's dequantise-then-attend."""
+    g = torch.Generator().manual_seed(s + d)
+
+    def quant(h):
+        x = torch.randn(b, h, s, d, generator=g) * torch.exp(torch.randn(b, h, s, 1, generator=g))
+        sc = (x.view(b, h, s, d // 32, 32).abs().amax(-1) / 448.0).clamp_min(1e-8)
+        codes = (x.view(b, h, s, d // 32, 32) / sc.unsqueeze(-1)).to(torch.float8_e4m3fn).view(torch.uint8)
+        return codes.view(b, h, s, d), sc
+
+    (q8, qs), (k8, ks), (v8, vs) = quant(hq), quant(hkv), quant(hkv)
+    ref = O.ref_mx_attention(q8, qs, k8, ks, v8, vs, causal)
+    out = ops.fused_microscaled_attention(q8.cuda(), qs.cuda(), k8.cuda(), ks.cuda(), v8.cuda(), vs.cuda(),
+                                          is_causal=causal, out_dtype=out_dtype)
+    assert out.dtype == out_dtype and torch.isfinite(out).all()
+    scale = ref.abs().amax().clamp_min(1.0)
+    err = (out.float().cpu() - ref).abs() / scale
+    tol = {torch.float32: 4e-3, torch.float16: 5e-3, torch.bfloat16: 2e-2}[out_dtype]   # f16 operands (P, Q K V rounded once)
+    assert err.max().item() <= tol, err.max().item()
+
+
+def test_microscaled_dispatcher_symbol(ops):
+    """dispatch_fused_microscaled_attention<T_OUT> exists under the reference's mangled names."""
+    lib = ops.L.load()
+    for sym in ("_Z36dispatch_fused_microscaled_attentionIfEvPKaPKfS1_S3_S1_S3_PT_iiiifbP11CUstream_st",
+                "_Z36dispatch_fused_microscaled_attentionI6__halfEvPKaPKfS2_S4_S2_S4_PT_iiiifbP11CUstream_st",
+                "_Z36dispatch_fused_microscaled_attentionI13__nv_bfloat16EvPKaPKfS2_S4_S2_S4_PT_iiiifbP11CUstream_st"):
+        assert hasattr(lib, sym), sym
