@@ -38,7 +38,7 @@ if ROOT not in sys.path:
 
 WORKLOADS = {"cfg1": 1, "cfg2": 2, "cfg3": 3, "cfg4": 4, "cfg5": 5}
 # secondary lines for the unquantised entry points (same Llama-3-8B head shape, bf16 K/V)
-AUX_WORKLOADS = ("pa16", "fd16")
+AUX_WORKLOADS = ("pa16", "fd16", "prefill", "mxattn")
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode-kernel launch,
@@ -162,16 +162,61 @@ def aux_workload(args, rank, world, local):
     from cuda_b200 import ops, workloads
     batch = args.batch or 64
     g = torch.Generator().manual_seed(2000 + rank)
+    if args.workload in ("prefill", "mxattn"):
+        # GQA prefill over a whole prompt (fused_gqa_forward) / dense attention over microscaled FP8 tensors:
+        # Llama-3-8B head shape, causal; tensor-core bound, so the roofline is the measured bf16 GEMM rate
+        bsz, seq = args.batch or 4, int(4096 * args.ctx_scale)
+        flops = 4.0 * bsz * 32 * seq * seq * 128 / 2            # causal: half of the score matrix
+        if args.workload == "prefill":
+            q = torch.randn(bsz, 32, seq, 128, generator=g).to(torch.bfloat16).to(dev)
+            k = torch.randn(bsz, 8, seq, 128, generator=g).to(torch.bfloat16).to(dev)
+            v = torch.randn(bsz, 8, seq, 128, generator=g).to(torch.bfloat16).to(dev)
+            fn = lambda: ops.fused_gqa_forward(q, k, v, is_causal=True)
+        else:
+            mk = lambda h: (torch.randint(0, 0x7E, (bsz, h, seq, 128), generator=g, dtype=torch.uint8).to(dev),
+                            (torch.rand(bsz, h, seq, 4, generator=g) * 0.01 + 0.001).to(dev))
+            (q, qs), (k, ks), (v, vs) = mk(32), mk(8), mk(8)
+            fn = lambda: ops.fused_microscaled_attention(q, qs, k, ks, v, vs, is_causal=True)
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        steps = min(args.steps, 50)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        tf_peak = None
+        try:
+            tf_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
+        except Exception:
+            pass
+        tf = flops / (ms * 1e-3) / 1e12
+        if rank == 0:
+            print(json.dumps({"metric": f"{args.workload}_attention_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
+                              "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                              "dtype": "bf16 mma.sync, f32 acc" if args.workload == "prefill" else "e4m3 -> f16 mma.sync, f32 acc",
+                              "data": "synthetic",
+                              "config": {"workload": args.workload, "batch": bsz, "heads": "32q/8kv", "seq_len": seq,
+                                         "head_dim": 128, "causal": True},
+                              "roofline": {"bound": "tensor", "achieved": tf, "peak": tf_peak or 1400.0,
+                                           "unit": "TFLOP/s", "frac": tf / (tf_peak or 1400.0),
+                                           "peak_source": "measured (sustained cuBLAS bf16)" if tf_peak else "fallback",
+                                           "kernel": "gqa_prefill_kernel", "traffic": None},
+                              "gpu_launches": steps}), flush=True)
+        return
     if args.workload == "pa16":
         ctx = torch.randint(int(1024 * args.ctx_scale), int(4096 * args.ctx_scale) + 1, (batch,), generator=g).tolist()
         wl = workloads.build_workload("pa16_llama8b_bf16", context_lens=ctx, q_lens=None, num_q_heads=32,
-                                      num_kv_heads=8, head_dim=128, page_size=16, q_dtype=torch.bfloat16,
+                                      num_kv_heads=8, head_dim=128, page_size=args.page_size, q_dtype=torch.bfloat16,
                                       scale_mode="none", pool_factor=1.25, seed=2000 + rank,
                                       cache_dtype=torch.bfloat16).to(dev)
         kv_bytes = sum(ctx) * 8 * 128 * 2 * 2
         fn = lambda: ops.paged_attention_forward(wl.query, wl.key_cache, wl.value_cache, wl.block_tables,
                                                  wl.context_lens)
-        cfg = {"workload": wl.name, "batch_per_gpu": batch, "kv_tokens_per_gpu": sum(ctx), "page_size": 16}
+        cfg = {"workload": wl.name, "batch_per_gpu": batch, "kv_tokens_per_gpu": sum(ctx), "page_size": args.page_size}
     else:
         seq = int(2560 * args.ctx_scale)
         q = torch.randn(batch, 32, 1, 128, generator=g).to(torch.bfloat16).to(dev)
@@ -423,6 +468,7 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + list(AUX_WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the batch (smaller ncu captures)")
     ap.add_argument("--ctx-scale", type=float, default=1.0)
+    ap.add_argument("--page-size", type=int, default=16, help="page size of the pa16 workload (16, 32 or 64)")
     ap.add_argument("--cpu-budget-s", type=float, default=15.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra-workloads", action="store_true",

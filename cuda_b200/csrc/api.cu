@@ -85,6 +85,43 @@ static int check_device() {
   return CUDA_LLM_OK;
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point look-up (libcuda is not linked).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Tensor map of a 16-bit paged cache [num_blocks][Hkv * D][page]: boxes of `box_rows` head_dim lines of
+// one page, swizzled over the 64 or 128 bytes of a line.
+static int encode_cache_map(CUtensorMap* map, const void* cache, int num_blocks, int Hkv, int D, int page, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(CUDA_LLM_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[3] = {(cuuint64_t)page, (cuuint64_t)Hkv * D, (cuuint64_t)num_blocks};
+  const cuuint64_t strides[2] = {(cuuint64_t)page * 2, (cuuint64_t)Hkv * D * page * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)page, (cuuint32_t)box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(cache), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, page >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char msg[96];
+    snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return fail(CUDA_LLM_ECUDA, msg);
+  }
+  return CUDA_LLM_OK;
+}
+
 // Pure arithmetic (no device access when num_ctas > 0): shared-memory stage layout and
 // workspace carving for one problem shape.
 static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, int k_format, int v_format,
@@ -173,7 +210,7 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   return CUDA_LLM_OK;
 }
 
-using LaunchFn = cudaError_t (*)(const DecodeArgs&, int, size_t, cudaStream_t);
+using LaunchFn = cudaError_t (*)(const DecodeArgs&, const KvTensorMaps&, int, size_t, cudaStream_t);
 
 template <int D, int MODE>
 static LaunchFn pick_page_nt(int page, int NT, bool precise) {
@@ -374,7 +411,17 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
 
   rc = check_device();
   if (rc != CUDA_LLM_OK) return rc;
-  cudaError_t e = fn(a, L.grid, L.smem_bytes, st);
+  KvTensorMaps tm;
+  memset(&tm, 0, sizeof(tm));
+  if (kv16 && page >= 32) {
+    // pages of 32 / 64 tokens travel as swizzled TMA boxes (at most 256 head_dim lines each)
+    a.tma_box_rows = L.HG * D < 256 ? L.HG * D : 256;
+    a.tma_boxes = (L.HG * D) / a.tma_box_rows;
+    rc = encode_cache_map(&tm.k, p->key_cache, p->num_blocks, Hkv, D, page, a.tma_box_rows);
+    if (rc == CUDA_LLM_OK) rc = encode_cache_map(&tm.v, p->value_cache, p->num_blocks, Hkv, D, page, a.tma_box_rows);
+    if (rc != CUDA_LLM_OK) return rc;
+  }
+  cudaError_t e = fn(a, tm, L.grid, L.smem_bytes, st);
   if (e != cudaSuccess) return fail_cuda(e, "paged_decode_kernel launch");
   if (p->flags & CUDA_LLM_FLAG_SKIP_MERGE) return CUDA_LLM_OK;
   e = (D == 64) ? launch_merge_splits<64>(a, page, L.grid, st) : launch_merge_splits<128>(a, page, L.grid, st);
@@ -577,7 +624,9 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
     LaunchFn fn;
     if (dtype == CUDA_LLM_BF16) fn = head_dim == 64 ? launch_paged_decode<64, 16, MODE_KV_BF16_TM, 1, false> : launch_paged_decode<128, 16, MODE_KV_BF16_TM, 1, false>;
     else fn = head_dim == 64 ? launch_paged_decode<64, 16, MODE_KV_F16_TM, 1, false> : launch_paged_decode<128, 16, MODE_KV_F16_TM, 1, false>;
-    cudaError_t e = fn(a, L.grid, L.smem_bytes, st);
+    KvTensorMaps tm;
+    memset(&tm, 0, sizeof(tm));
+    cudaError_t e = fn(a, tm, L.grid, L.smem_bytes, st);
     if (e != cudaSuccess) return fail_cuda(e, "paged_decode_kernel launch");
     e = (head_dim == 64) ? launch_merge_splits<64>(a, 16, L.grid, st) : launch_merge_splits<128>(a, 16, L.grid, st);
     return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "merge_splits_kernel launch");

@@ -7,14 +7,15 @@ namespace b200 {
 // One explicit instantiation per (D, PAGE, MODE, NT, PRECISE) lives in a paged_decode_inst_*.cu
 // unit; the C ABI only sees these declarations.
 template <int D, int PAGE, int MODE, int NT, bool PRECISE>
-cudaError_t launch_paged_decode(const DecodeArgs& a, int grid, size_t smem, cudaStream_t st);
+cudaError_t launch_paged_decode(const DecodeArgs& a, const KvTensorMaps& tm, int grid, size_t smem, cudaStream_t st);
 
 template <int D>
 cudaError_t launch_merge_splits(const DecodeArgs& a, int page, int decode_grid, cudaStream_t st);
 
 #define B200_DEFINE_DECODE_LAUNCH(D, PAGE, MODE, NT, PRECISE)                                   \
   template <>                                                                                   \
-  cudaError_t launch_paged_decode<D, PAGE, MODE, NT, PRECISE>(const DecodeArgs& a, int grid,    \
+  cudaError_t launch_paged_decode<D, PAGE, MODE, NT, PRECISE>(const DecodeArgs& a,              \
+                                                              const KvTensorMaps& tm, int grid, \
                                                               size_t smem, cudaStream_t st) {   \
     auto kern = paged_decode_kernel<D, PAGE, MODE, NT, PRECISE>;                                \
     static int configured[64] = {0};                                                            \
@@ -37,7 +38,7 @@ cudaError_t launch_merge_splits(const DecodeArgs& a, int page, int decode_grid, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;                                     \
     cfg.attrs = attr;                                                                           \
     cfg.numAttrs = 1;                                                                           \
-    return cudaLaunchKernelEx(&cfg, kern, a);                                                   \
+    return cudaLaunchKernelEx(&cfg, kern, a, tm);                                               \
   }
 
 // every page size and row-tile variant of one (MODE, D)

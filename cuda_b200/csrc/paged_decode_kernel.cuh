@@ -77,7 +77,15 @@ struct StageMeta {  // 32 ints
 
 constexpr uint32_t kMetaOff = 256;
 constexpr uint32_t kBtRingOff = kMetaOff + kMaxStages * sizeof(StageMeta);
-constexpr uint32_t kStagesOff = kBtRingOff + kBtRing * kMaxPagesPerStage * 4;
+// the stages start on a 1024-byte boundary: swizzled TMA boxes repeat their pattern every 1024 bytes
+constexpr uint32_t kStagesOff = (kBtRingOff + kBtRing * kMaxPagesPerStage * 4 + 1023u) / 1024u * 1024u;
+
+// Tensor maps of a 16-bit paged cache viewed as [num_blocks][Hkv * D][page] (innermost last here, first
+// in the map): pages of 32 / 64 tokens are fetched as swizzled boxes so that the eight rows an
+// ldmatrix phase touches fall into different banks.  Unused (zero) for every other mode.
+struct alignas(64) KvTensorMaps {
+  CUtensorMap k, v;
+};
 
 struct DecodeArgs {
   const void* q;
@@ -114,6 +122,8 @@ struct DecodeArgs {
   const float* rope_sin;
   const int32_t* rope_pos;   // optional position of every query token [total_q]; null: ctx - q_len + j
   int rope_positions;        // rows of the tables (positions are clamped to them, with a status bit)
+  int tma_box_rows;     // 16-bit pages of 32 / 64 tokens: rows (head_dim lines) per TMA box, boxes per page
+  int tma_boxes;
   int short_waits;      // every mbarrier wait gives up after kShortPolls polls instead of kMaxPolls
   int stall_test;       // failure-path test: the first stage of the launch is armed but no copies are issued for it
   uint32_t stage_bytes, off_v, off_ks, off_vs;
@@ -195,7 +205,7 @@ struct UnitCursor {
 
 template <int D, int PAGE, int MODE, int NT, bool PRECISE>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
-paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
+paged_decode_kernel(const __grid_constant__ DecodeArgs a, const __grid_constant__ KvTensorMaps tmaps) {
   constexpr int KT = D / 16;                     // k-tiles of QK  == m-tiles of PV
   constexpr bool V4 = (MODE == MODE_MX8K_MX4V);  // V stored as packed E2M1
   constexpr bool MX = (MODE == MODE_MX8 || MODE == MODE_MX8K_MX4V);
@@ -204,6 +214,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
   constexpr bool KV16 = (MODE >= MODE_KV_F16);  // 2-byte elements, no scales
   constexpr bool TM = (MODE >= MODE_KV_F16_TM);  // token-major rows [token][head_dim] instead of pages [head_dim][token]
   constexpr bool BF = (MODE == MODE_KV_BF16 || MODE == MODE_KV_BF16_TM);
+  // 16-bit pages of 32 / 64 tokens: rows of 64 / 128 bytes, loaded as SWIZZLE_64B / SWIZZLE_128B boxes
+  constexpr bool TMA3D = KV16 && !TM && PAGE >= 32;
+  constexpr uint32_t SWZ_MASK = (PAGE >= 64) ? 7u : 3u;  // 16-byte chunk index ^= (address >> 7) & mask
   constexpr int SUB = (KV16 || NT == 1) ? 16 : 32;  // tokens per warp sub-tile
   constexpr int MT = SUB / 16;                   // m-tiles of S^T == k-tiles of PV per sub-tile
   constexpr float NEG_INF = -__builtin_huge_valf();
@@ -522,7 +535,20 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
                                  (a.q_dtype == CUDA_LLM_F32 ? 4 : 2);
         bulk_g2s(smem_base + a.q_smem_off + slot * a.q_smem_bytes + lane * q_row_bytes, src, q_row_bytes, fb);
       }
-      if (!TM && !no_copy && !stalled) {
+      if (TMA3D && !no_copy && !stalled) {
+        // lane (page, box): one swizzled box of K and one of V, tensor-map coordinates
+        // {token 0, row of the head group within the block, block}
+        const uint32_t sb = stage0 + slot * a.stage_bytes;
+        const int pg = lane / a.tma_boxes, bx = lane - pg * a.tma_boxes;
+        const int blk_pg = __shfl_sync(0xffffffffu, c_blk, pg < np ? pg : 0);
+        if (pg < np) {
+          const uint32_t box_bytes = (uint32_t)a.tma_box_rows * (PAGE * 2);
+          const int row = ic.hg * a.HG * D + bx * a.tma_box_rows;
+          tma_load_3d_hint(sb + pg * a.k_page_stride + bx * box_bytes, &tmaps.k, 0, row, blk_pg, fb, stream_policy);
+          tma_load_3d_hint(sb + a.off_v + pg * a.v_page_stride + bx * box_bytes, &tmaps.v, 0, row, blk_pg, fb,
+                           stream_policy);
+        }
+      } else if (!TM && !no_copy && !stalled) {
         const uint32_t sb = stage0 + slot * a.stage_bytes;
         // lane pi issues the copies of page pi
         if (lane < np) {
@@ -597,6 +623,13 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a) {
                  ((lane >> 3) & 1) * 16;
       v_lm[mt] = a.off_v + pi * a.v_page_stride + h * (D * PAGE * 2) +
                  ((((lane >> 3) & 1) * 8 + (lane & 7)) * PAGE + po) * 2 + (lane >> 4) * 16;
+      if (TMA3D) {
+        // the boxes arrive swizzled: the 16-byte chunk index is XORed with the row bits of the
+        // address.  Steps of 16 rows (k-tiles, m-tiles) are multiples of 1024 bytes and leave the
+        // XOR term unchanged, so it is applied once here.
+        k_lm[mt] ^= ((k_lm[mt] >> 7) & SWZ_MASK) << 4;
+        v_lm[mt] ^= ((v_lm[mt] >> 7) & SWZ_MASK) << 4;
+      }
     }
   }
 

@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cuda.h>  // CUtensorMap (type only; no driver-API call is linked)
 
 namespace b200 {
 
@@ -85,6 +86,19 @@ __device__ __forceinline__ void bulk_g2s_hint(uint32_t dst_smem, const void* src
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
       ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
+
+// 3-D tiled TMA copy global -> shared through a tensor map (cuTensorMapEncodeTiled), completion counted
+// on an mbarrier, with an L2 eviction policy.  No cluster multicast: the box lands in this CTA's own
+// shared memory.  The innermost coordinate times the element size must be a multiple of 16 bytes
+// (callers pass 0), the destination aligned to the swizzle pattern of the map.
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
+                                                 uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3, %4}], [%5], %6;"
+      ::"r"(dst_smem), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(bar), "l"(policy)
       : "memory");
 }
 

@@ -2,9 +2,8 @@
 
 The kernel cuts all (sequence, head group, tile) units of a launch into contiguous ranges of equal
 *cost*, one per CTA, with integer arithmetic only (``paged_decode_kernel.cuh``, "plan").  This module
-states the same rules in Python so that their invariants can be checked on the CPU and so that a
-caller can predict which CTAs touch which sequence (e.g. to size logs or to reason about the split
-merge).  It is not on the data path.
+states the same rules in Python so that their invariants can be checked on the CPU and the table the
+kernel writes can be compared with them entry by entry on the GPU.  Test infrastructure only.
 
 Rules (all positions in cost units):
 

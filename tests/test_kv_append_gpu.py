@@ -1,7 +1,10 @@
-"""The cache-append kernel writes exactly the bytes and scales of the host recipe, at the right
-place of the paged layout, and the decode kernel reads them back."""
+"""The cache-append kernel writes exactly the bytes and scales of the oracle's statement of the write
+recipe (torch / ml_dtypes casts), at the right place of the paged layout, and the decode kernel reads
+them back."""
 import pytest
 import torch
+
+from oracle import paged_decode_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -23,8 +26,8 @@ def test_append_is_bit_exact(mode, vfmt, d, page, dtype):
     # per-head scales by the reference recipe (tests/test_kernels_misc.py:51-52): amax / 448 per head
     k_head = (k.float().abs().amax(dim=(0, 2)) / 448.0).clamp_min(1e-8)
     v_head = (v.float().abs().amax(dim=(0, 2)) / 448.0).clamp_min(1e-8)
-    kc_ref, ks_ref = W.quantize_tokens(k.float(), "fp8_e4m3", mode, k_head)
-    vc_ref, vs_ref = W.quantize_tokens(v.float(), vfmt, mode, v_head)
+    kc_ref, ks_ref = O.quantize_tokens(k.float(), "fp8_e4m3", mode, k_head)
+    vc_ref, vs_ref = O.quantize_tokens(v.float(), vfmt, mode, v_head)
     dv = d // 2 if vfmt == "fp4_e2m1" else d
     kc = torch.full((nb, h, d, page), 0xAA, dtype=torch.uint8, device="cuda")
     vc = torch.full((nb, h, dv, page), 0xAA, dtype=torch.uint8, device="cuda")
@@ -71,8 +74,8 @@ def test_append_then_decode_round_trip():
         blk = wl.block_tables[s, pos // 16]
         off = (pos % 16).to(torch.int32)
         ops.kv_cache_append(k.cuda(), v.cuda(), blk.cuda(), off.cuda(), kc, vc, ks, vs)
-        kq, ksc = W.quantize_tokens(k, "fp8_e4m3", "per_token")
-        vq, vsc = W.quantize_tokens(v, "fp8_e4m3", "per_token")
+        kq, ksc = O.quantize_tokens(k, "fp8_e4m3", "per_token")
+        vq, vsc = O.quantize_tokens(v, "fp8_e4m3", "per_token")
         ref_wl.key_cache[blk.long(), :, :, off.long()] = kq
         ref_wl.value_cache[blk.long(), :, :, off.long()] = vq
         ref_wl.k_scale[blk.long(), :, off.long()] = ksc

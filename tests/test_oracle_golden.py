@@ -165,3 +165,26 @@ def test_gqa_oracle_matches_reference(golden, case):
     crc = lambda t: zlib.crc32(t.contiguous().view(torch.uint8).numpy().tobytes())
     assert [crc(q), crc(k), crc(v), crc(o)] == golden[f"{name}/crc"].tolist()
     assert torch.equal(o[:, :, list(cases.GQA_ROWS), :], torch.from_numpy(golden[f"{name}/rows"]))
+
+
+def test_quantisers_pinned_to_library_casts():
+    """The workload generator's quantisers (the write side of the cache formats) agree bit for bit
+    with the oracle's statement of the recipe, which uses torch's float8_e4m3fn cast and ml_dtypes'
+    float4_e2m1fn cast: every rounding tie of E2M1, saturation, and random data in all scale modes."""
+    import ml_dtypes
+    from cuda_b200 import workloads as W
+    ties = torch.tensor([0.0, 0.2, 0.25, 0.26, 0.74, 0.75, 0.76, 1.25, 1.26, 1.75, 2.5, 2.51, 3.5, 5.0, 5.01, 6.0,
+                         7.0, 7.99, 100.0])
+    x = torch.cat([ties, -ties, torch.randn(4096) * 2])
+    want = torch.from_numpy(x.numpy().astype(ml_dtypes.float4_e2m1fn).view(np.uint8))
+    assert torch.equal(W.quant_e2m1(x), want)
+    g = torch.Generator().manual_seed(3)
+    t = torch.randn(37, 3, 128, generator=g) * torch.exp(2 * torch.randn(37, 3, 1, generator=g))
+    for fmt, mode in (("fp8_e4m3", "per_token"), ("fp8_e4m3", "mx_e8m0"), ("fp4_e2m1", "mx_e8m0")):
+        a, sa = W.quantize_tokens(t, fmt, mode)
+        b, sb = O.quantize_tokens(t, fmt, mode)
+        assert torch.equal(a, b) and torch.equal(sa, sb), (fmt, mode)
+    hs = torch.rand(3, generator=g) + 0.5
+    a, _ = W.quantize_tokens(t, "fp8_e4m3", "per_head", hs)
+    b, _ = O.quantize_tokens(t, "fp8_e4m3", "per_head", hs)
+    assert torch.equal(a, b)

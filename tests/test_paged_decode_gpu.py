@@ -391,7 +391,7 @@ def test_reference_cxx_dispatcher_paged_and_decode(ops, golden):
 def test_segment_table_matches_host_plan(ops, hkv, q4, num_ctas):
     """The (first CTA, number of CTAs) the kernel records per (sequence, head group) is exactly what
     the host restatement of the plan predicts: integer parity of the range partition."""
-    from cuda_b200 import partition as P
+    import partition_plan as P
     W = _W()
     g = torch.Generator().manual_seed(51)
     n = 24

@@ -1,7 +1,7 @@
 """Invariants of the unit-range plan (host restatement of the in-kernel integer logic)."""
 import random
 
-from cuda_b200 import partition as P
+import partition_plan as P
 
 
 def _check(ctx, qls, group, n_hg, tok_stage, ctas, weighted):

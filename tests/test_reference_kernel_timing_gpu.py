@@ -1,12 +1,12 @@
-"""TEST INFRASTRUCTURE.  Times the REFERENCE's own CUDA paged-decode kernels (compiled for sm_100a
-into oracle/_ref/libref_paged.so by oracle/Makefile) next to this library's entry points on the
-same inputs, on the shapes the reference supports (MHA, page 16, q_len 1).
+"""Times the REFERENCE's own CUDA paged-decode kernels (compiled for sm_100a into
+oracle/_ref/libref_paged.so by oracle/Makefile) next to this library's entry points on the same
+inputs, on the shapes the reference supports (MHA, page 16, q_len 1), and prints one line per case:
 
-    python oracle/ref_gpu_timing.py            # prints one line per case
+    python -m pytest tests/test_reference_kernel_timing_gpu.py -m gpu -s
 
 The reference's 8-bit kernel reads the cache bytes as int8, so its output differs from the E4M3
 path by design; only its time is compared.  The fp16 kernel's output is also checked against
-this library's paged_attention.
+this library's paged_attention.  Skipped where oracle/_ref was not built.
 """
 import ctypes as C
 import os
@@ -14,9 +14,10 @@ import sys
 
 import torch
 
+import pytest
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-sys.path.insert(0, ROOT)
-from cuda_b200 import ops, workloads as W  # noqa: E402
+pytestmark = pytest.mark.gpu
 
 REF = os.path.join(ROOT, "oracle", "_ref", "libref_paged.so")
 
@@ -34,8 +35,11 @@ def timeit(fn, iters=20, warm=3):
     return e0.elapsed_time(e1) / iters
 
 
-def main():
+@pytest.mark.skipif(not os.path.exists(REF), reason="oracle/_ref not built")
+def test_reference_kernels_are_slower_than_this_library(capsys):
+    from cuda_b200 import ops, workloads as W
     ref = C.CDLL(REF)
+    lines, ratios = [], []
     st = lambda: torch.cuda.current_stream().cuda_stream
     cg = torch.Generator()
     cg.manual_seed(1002)
@@ -59,9 +63,11 @@ def main():
         err = (ours.float() - out_ref.float()).abs().max().item()
         t_ours = timeit(lambda: ops.paged_attention_forward(wl.query, wl.key_cache, wl.value_cache,
                                                             wl.block_tables, wl.context_lens))
-        print(f"fp16 paged  batch {batch} heads {heads}: {nbytes/1e6:8.1f} MB  reference kernel {t_ref*1e3:9.1f} us "
-              f"({nbytes/t_ref/1e9:6.3f} TB/s)  this library {t_ours*1e3:8.1f} us ({nbytes/t_ours/1e9:6.3f} TB/s)  "
-              f"max |diff| {err:.2e}", flush=True)
+        lines.append(f"fp16 paged  batch {batch} heads {heads}: {nbytes/1e6:8.1f} MB  reference kernel {t_ref*1e3:9.1f} us "
+                     f"({nbytes/t_ref/1e9:6.3f} TB/s)  this library {t_ours*1e3:8.1f} us ({nbytes/t_ours/1e9:6.3f} TB/s)  "
+                     f"max |diff| {err:.2e}")
+        ratios.append(t_ref / t_ours)
+        assert err <= 2e-2
         del wl, out_ref, ours
         # ---- 8-bit paged cache, per-head scales, MHA
         wl = W.build_workload("ref_8bit", context_lens=lens, q_lens=None, num_q_heads=heads, num_kv_heads=heads,
@@ -81,11 +87,13 @@ def main():
         ws = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
         out = torch.empty_like(wl.query)
         t_ours = timeit(lambda: ops.run_workload(wl, out=out, workspace=ws))
-        print(f"8-bit paged batch {batch} heads {heads}: {nbytes/1e6:8.1f} MB  reference kernel {t_ref*1e3:9.1f} us "
-              f"({nbytes/t_ref/1e9:6.3f} TB/s, int8 reading)  this library {t_ours*1e3:8.1f} us "
-              f"({nbytes/t_ours/1e9:6.3f} TB/s, E4M3)", flush=True)
+        lines.append(f"8-bit paged batch {batch} heads {heads}: {nbytes/1e6:8.1f} MB  reference kernel {t_ref*1e3:9.1f} us "
+                     f"({nbytes/t_ref/1e9:6.3f} TB/s, int8 reading)  this library {t_ours*1e3:8.1f} us "
+                     f"({nbytes/t_ours/1e9:6.3f} TB/s, E4M3)")
+        ratios.append(t_ref / t_ours)
         del wl, out_ref, out, ws
-
-
-if __name__ == "__main__":
-    main()
+    with capsys.disabled():
+        print()
+        for line in lines:
+            print(line, flush=True)
+    assert min(ratios) > 1.0
