@@ -4,6 +4,7 @@
 // reference project) and turns the dispatcher's silent no-op on an unsupported shape
 // (fp8_paged_attention_kernel.cuh:176-190) into an error code.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <cmath>
 #include <mutex>
@@ -18,6 +19,10 @@ cudaError_t launch_dequant_pages(const void*, const void*, const int32_t*, int, 
 
 cudaError_t run_gqa_prefill(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hkv, int S,
                             int D, float softmax_scale, bool causal, int dtype, cudaStream_t st);
+bool gqa_prefill_sm100_supported(int Hq, int Hkv, int D, int dtype);
+cudaError_t run_gqa_prefill_sm100(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hkv, int S,
+                                  int D, float softmax_scale, bool causal, int dtype, cudaStream_t st);
+cudaError_t prefill_wait_timeouts(unsigned int* count);
 cudaError_t run_mx_attention(const void* q, const float* qs, const void* k, const float* ks, const void* v,
                              const float* vs, void* out, int B, int Hq, int Hkv, int S, int D, float softmax_scale,
                              bool causal, int out_dtype, cudaStream_t st);
@@ -101,6 +106,8 @@ static EncodeTiledFn encode_tiled_fn() {
   });
   return fn;
 }
+
+EncodeTiledFn tensor_map_encoder() { return encode_tiled_fn(); }
 
 // Tensor map of a 16-bit paged cache [num_blocks][Hkv * D][page]: boxes of `box_rows` head_dim lines of
 // one page, swizzled over the 64 or 128 bytes of a line.
@@ -661,13 +668,34 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
   const int rc = check_device();
   if (rc != CUDA_LLM_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  cudaError_t e = run_gqa_prefill(q, k, v, out, batch_size, num_q_heads, num_kv_heads, seq_len, head_dim,
-                                  softmax_scale, is_causal != 0, dtype, st);
+  // 16-bit tensors run on tcgen05 / TMEM when the group size tiles the 128 accumulator rows; the
+  // warp-MMA kernel takes the other group sizes and fp32.  CUDA_LLM_PREFILL_KERNEL=warp_mma forces the
+  // latter (A/B measurements).
+  static const bool force_warp_mma = [] {
+    const char* v = getenv("CUDA_LLM_PREFILL_KERNEL");
+    return v && strcmp(v, "warp_mma") == 0;
+  }();
+  cudaError_t e;
+  if (!force_warp_mma && gqa_prefill_sm100_supported(num_q_heads, num_kv_heads, head_dim, dtype) && encode_tiled_fn())
+    e = run_gqa_prefill_sm100(q, k, v, out, batch_size, num_q_heads, num_kv_heads, seq_len, head_dim, softmax_scale,
+                              is_causal != 0, dtype, st);
+  else
+    e = run_gqa_prefill(q, k, v, out, batch_size, num_q_heads, num_kv_heads, seq_len, head_dim, softmax_scale,
+                        is_causal != 0, dtype, st);
   if (e != cudaSuccess) return fail_cuda(e, "gqa_prefill_kernel launch");
   if (cache) {
     e = run_kv_append_prefill(k, v, *cache, batch_size, num_kv_heads, seq_len, head_dim, dtype, st);
     if (e != cudaSuccess) return fail_cuda(e, "kv_append_kernel launch");
   }
+  return CUDA_LLM_OK;
+}
+
+int cuda_llm_prefill_wait_timeouts(uint32_t* count) {
+  if (!count) return fail(CUDA_LLM_EINVAL, "null argument");
+  unsigned int c = 0;
+  const cudaError_t e = prefill_wait_timeouts(&c);
+  if (e != cudaSuccess) return fail_cuda(e, "reading the prefill time-out counter");
+  *count = c;
   return CUDA_LLM_OK;
 }
 

@@ -1,0 +1,416 @@
+// GQA prefill attention on the 5th-generation tensor cores: tcgen05.mma with TMEM accumulators,
+// TMA (tiled, 128-byte swizzled) operand loads, mbarrier pipelines.
+//
+// Same contract as gqa_prefill_kernel (the reference's fused_gqa_forward, fused_gqa_kernel.cuh:22-212
+// in the reference project): q [B, Hq, S, D], k / v [B, Hkv, S, D], fp16 or bf16, causal mask
+// "key position <= query position", fp32 softmax.
+//
+// One CTA per (batch, KV head, block of query positions).  Its 128 accumulator rows are the query
+// heads that share the KV head (1, 2, 4 or 8 of them) times 128 / heads consecutive query positions,
+// so a K / V tile is fetched once for the whole group.  Roles:
+//   warp 4        TMA producer: Q once, then K / V tiles of 128 tokens into a two-deep ring
+//   warp 5        allocates TMEM, issues S = Q K^T (M 128, N 128, K 16 x D/16) into one of two S
+//                 buffers in TMEM and O += P V (N = D) into the O buffer
+//   warps 0..3    one thread per row = per TMEM lane: read S with tcgen05.ld, online softmax in fp32
+//                 without any shuffle, write P (16-bit) into shared memory in the swizzled K-major
+//                 layout the MMA reads, rescale O in TMEM when a row maximum moved, write the output
+// Shared-memory operand layouts are the canonical 128-byte-swizzle layouts of the matrix
+// descriptors: K-major rows of 64 elements for Q, K and P; MN-major (row = token, 64 head_dim
+// elements per 128-byte line) for V, which is exactly how a [tokens, D] tile lands through TMA.
+// Every wait is bounded; a wait that runs out raises a device-side counter, lets the CTA fall
+// through to the common exit (TMEM is released there) and leaves garbage in that CTA's rows.
+#include "sm100_primitives.cuh"
+#include "cuda_llm_b200.h"
+
+namespace b200 {
+
+struct alignas(64) PrefillMaps {
+  CUtensorMap q, k, v;
+};
+
+struct Prefill100Args {
+  void* out;
+  int B, Hq, Hkv, S, group;
+  int gsz;   // query heads per CTA (1, 2, 4 or 8; divides group)
+  int causal;
+  int bf16;  // operand / output type: 1 bf16, 0 fp16
+  float scale_log2;
+};
+
+__device__ unsigned int g_prefill_wait_timeouts = 0;
+
+constexpr int kP100Threads = 192;
+constexpr int kP100Bc = 128;  // KV tokens per tile
+
+// Bounded wait of this kernel: every event it waits for is microseconds away, so a quarter of a
+// second of polling (2^16 polls) means something is wrong, not slow.
+__device__ __forceinline__ bool p100_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 16); ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst_smem), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// D[tmem] (+)= A[smem desc] * B[smem desc], 16-bit operands, fp32 accumulate; issued by ONE thread
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// the mbarrier receives one arrival when every tcgen05 operation issued so far by this thread is done
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane (base lane + i)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte offsets
+// (all without their 4 low bits), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: fp32 accumulate, A / B format (0 fp16, 1 bf16), B major-ness
+// (0 K-major, 1 MN-major), N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t instr_desc_f16(int fmt, int b_mn_major, int M, int N) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)b_mn_major << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kP100Threads, 1)
+gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_constant__ PrefillMaps maps) {
+  constexpr int NCH = D / 64;                 // 64-element (128-byte) chunks of head_dim
+  constexpr uint32_t QCH = 128 * 128;         // bytes of one [128 rows x 64 elements] swizzled block
+  constexpr uint32_t Q_BYTES = NCH * QCH, KV_BYTES = NCH * QCH, P_BYTES = 2 * QCH;
+  constexpr float NEG_INF = -__builtin_huge_valf();
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base = smem_u32(smem);
+  const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + 2 * KV_BYTES, sP = sV + 2 * KV_BYTES;
+  const uint32_t bars = sP + P_BYTES;  // 8-byte mbarriers
+  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, kv_empty = bars + 40, s_full = bars + 56,
+                 s_empty = bars + 72, p_full = bars + 88, pv_done = bars + 96, tmem_slot = bars + 104;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base));
+  volatile uint32_t* fail_ptr = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base) + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z;
+  const int n_chunks = a.group / a.gsz;
+  const int kvh = blockIdx.y / n_chunks, chunk = blockIdx.y - kvh * n_chunks;
+  const int BQ = 128 / a.gsz;
+  const int qt = (int)(gridDim.x - 1 - blockIdx.x);  // heavy (late) causal blocks first
+  const int q0 = qt * BQ;
+  const int last_q = min(a.S, q0 + BQ) - 1;
+  const int n_tiles = a.causal ? last_q / kP100Bc + 1 : (a.S + kP100Bc - 1) / kP100Bc;
+
+  if (tid == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(k_full + 8 * i, 1);
+      mbar_init(v_full + 8 * i, 1);
+      mbar_init(kv_empty + 8 * i, 1);
+      mbar_init(s_full + 8 * i, 1);
+      mbar_init(s_empty + 8 * i, 4);   // one arrival per softmax warp
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    *fail_ptr = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {  // TMEM: S0 [0,128), S1 [128,256), O [256, 256 + D)
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_ptr;
+  auto give_up = [&]() {
+    *fail_ptr = 1;
+    atomicAdd(&g_prefill_wait_timeouts, 1u);
+  };
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, (uint32_t)a.gsz * BQ * D * 2);
+      for (int i = 0; i < a.gsz; ++i)
+        for (int c = 0; c < NCH; ++c)
+          tma_load_3d(sQ + c * QCH + i * BQ * 128, &maps.q, c * 64, q0, b * a.Hq + kvh * a.group + chunk * a.gsz + i, q_full);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        if (j >= 2 && !p100_wait(kv_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
+        mbar_arrive_expect_tx(k_full + 8 * st, KV_BYTES);
+        for (int c = 0; c < NCH; ++c) tma_load_3d(sK + st * KV_BYTES + c * QCH, &maps.k, c * 64, j * kP100Bc, b * a.Hkv + kvh, k_full + 8 * st);
+        mbar_arrive_expect_tx(v_full + 8 * st, KV_BYTES);
+        for (int c = 0; c < NCH; ++c) tma_load_3d(sV + st * KV_BYTES + c * QCH, &maps.v, c * 64, j * kP100Bc, b * a.Hkv + kvh, v_full + 8 * st);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      const uint32_t idesc_s = instr_desc_f16(a.bf16, 0, 128, kP100Bc);
+      const uint32_t idesc_o = instr_desc_f16(a.bf16, 1, 128, D);
+      bool ok = p100_wait(q_full, 0);
+      auto issue_pv = [&](int j) -> bool {  // O (+)= P_j V_j
+        const int st = j & 1;
+        if (!p100_wait(p_full, j & 1) || !p100_wait(v_full + 8 * st, (j >> 1) & 1)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kP100Bc / 16; ++kk) {
+          const uint64_t ad = smem_desc_sw128(sP + (kk >> 2) * QCH + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = smem_desc_sw128(sV + st * KV_BYTES + kk * 2048, QCH, 1024);
+          umma_f16(tmem + 256, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(pv_done);            // P buffer free, O updated
+        umma_commit(kv_empty + 8 * st);  // K / V stage free
+        return true;
+      };
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int st = j & 1;
+        ok = p100_wait(k_full + 8 * st, (j >> 1) & 1) && (j < 2 || p100_wait(s_empty + 8 * st, ((j >> 1) - 1) & 1));
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t ad = smem_desc_sw128(sQ + (kk >> 2) * QCH + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = smem_desc_sw128(sK + st * KV_BYTES + (kk >> 2) * QCH + (kk & 3) * 32, 16, 1024);
+          umma_f16(tmem + st * 128, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full + 8 * st);
+        if (j >= 1) ok = issue_pv(j - 1);
+      }
+      if (ok) ok = issue_pv(n_tiles - 1);
+      if (!ok) give_up();
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warps: thread = row
+    const int row = tid;                        // TMEM lane
+    const int hi = row / BQ, qpos = q0 + row - hi * BQ;
+    const int qh = kvh * a.group + chunk * a.gsz + hi;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float m_run = -1.0e30f, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1, kv0 = j * kP100Bc;
+      if (!p100_wait(s_full + 8 * st, (j >> 1) & 1)) { ok = false; break; }
+      tc_fence_after();
+      const bool need_mask = (kv0 + kP100Bc > a.S) || (a.causal && kv0 + kP100Bc - 1 > q0);
+      // pass 1: row maximum
+      float mx = NEG_INF;
+#pragma unroll 1
+      for (int c = 0; c < kP100Bc / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + st * 128 + c * 32, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(r[i]) * a.scale_log2;
+          if (need_mask) {
+            const int key = kv0 + c * 32 + i;
+            if (key >= a.S || (a.causal && key > qpos)) x = NEG_INF;
+          }
+          mx = fmaxf(mx, x);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = fast_exp2(m_run - m_new);
+      m_run = m_new;
+      // the previous P V must be done before P is overwritten and before O is rescaled
+      if (j >= 1 && !p100_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
+      tc_fence_after();
+      if (j >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_base + 256 + c * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(tmem + lane_base + 256 + c * 32, r);
+        }
+        tc_wait_st();
+      }
+      // pass 2: P = 2^(s - m), row sum, P (16-bit) into the swizzled K-major operand buffer
+      float ps = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < kP100Bc / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + st * 128 + c * 32, r);
+        tc_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float x0 = fmaf(__uint_as_float(r[i]), a.scale_log2, -m_new), x1 = fmaf(__uint_as_float(r[i + 1]), a.scale_log2, -m_new);
+          if (need_mask) {
+            const int key = kv0 + c * 32 + i;
+            if (key >= a.S || (a.causal && key > qpos)) x0 = NEG_INF;
+            if (key + 1 >= a.S || (a.causal && key + 1 > qpos)) x1 = NEG_INF;
+          }
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          ps += p0 + p1;
+          pk[i >> 1] = a.bf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+        }
+        // columns 32c .. 32c+31 of this row: four 16-byte units of the 128-byte line of chunk c / 2
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int unit = (c & 1) * 4 + u;
+          const uint32_t addr = sP + (c >> 1) * QCH + row * 128 + ((unit ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * u]), "r"(pk[4 * u + 1]),
+                       "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3]) : "memory");
+        }
+      }
+      l_run = l_run * alpha + ps;
+      // S buffer consumed; P written (visible to the async proxy) and O rescaled
+      tc_fence_before();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(s_empty + 8 * st);
+        mbar_arrive(p_full);
+      }
+    }
+    // epilogue: O / l -> out
+    if (ok && !p100_wait(pv_done, (n_tiles - 1) & 1)) ok = false;
+    if (!ok) {
+      if (lane == 0) give_up();
+    } else {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const bool store = hi < a.gsz && qpos < a.S;
+      uint4* og = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (((size_t)b * a.Hq + qh) * (size_t)a.S + (store ? qpos : 0)) * D);
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + 256 + c * 32, r);
+        tc_wait_ld();
+        if (store) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float x0 = __uint_as_float(r[8 * u + 2 * e]) * inv, x1 = __uint_as_float(r[8 * u + 2 * e + 1]) * inv;
+              w[e] = a.bf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
+            }
+            og[c * 4 + u] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  }
+  // common exit: every thread arrives here, also after a wait that ran out
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, 512);
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn tensor_map_encoder();  // api.cu
+
+static bool encode_bhsd(EncodeTiledFn enc, CUtensorMap* m, const void* p, long long bh, int S, int D, int box_rows) {
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)bh};
+  const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(p), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Whether the tcgen05 kernel takes this shape: 16-bit tensors, a group of 1, 2, 4, 8 or a multiple of 8.
+bool gqa_prefill_sm100_supported(int Hq, int Hkv, int D, int dtype) {
+  if (dtype != CUDA_LLM_F16 && dtype != CUDA_LLM_BF16) return false;
+  if (D != 64 && D != 128) return false;
+  const int group = Hq / Hkv;
+  return group == 1 || group == 2 || group == 4 || group % 8 == 0;
+}
+
+cudaError_t run_gqa_prefill_sm100(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hkv, int S,
+                                  int D, float softmax_scale, bool causal, int dtype, cudaStream_t st) {
+  if (B == 0 || S == 0) return cudaSuccess;
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return cudaErrorNotSupported;
+  Prefill100Args a;
+  a.out = out; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.group = Hq / Hkv;
+  a.gsz = a.group < 8 ? a.group : 8;
+  a.causal = causal ? 1 : 0;
+  a.bf16 = dtype == CUDA_LLM_BF16 ? 1 : 0;
+  a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  const int bq = 128 / a.gsz;
+  PrefillMaps maps;
+  if (!encode_bhsd(enc, &maps.q, q, (long long)B * Hq, S, D, bq) || !encode_bhsd(enc, &maps.k, k, (long long)B * Hkv, S, D, kP100Bc) ||
+      !encode_bhsd(enc, &maps.v, v, (long long)B * Hkv, S, D, kP100Bc))
+    return cudaErrorInvalidValue;
+  const int nch = D / 64;
+  size_t smem = (size_t)nch * 16384 * 5 + 2 * 16384 + 128;
+  if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: a CTA allocates all 512 TMEM columns
+  auto kern = D == 64 ? gqa_prefill_sm100_kernel<64> : gqa_prefill_sm100_kernel<128>;
+  static int configured[2][64] = {{0}};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && !configured[D == 128][dev]) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured[D == 128][dev] = 1;
+  }
+  dim3 grid((S + bq - 1) / bq, Hkv * (a.group / a.gsz), B);
+  kern<<<grid, kP100Threads, smem, st>>>(a, maps);
+  return cudaGetLastError();
+}
+
+cudaError_t prefill_wait_timeouts(unsigned int* count) {
+  return cudaMemcpyFromSymbol(count, g_prefill_wait_timeouts, sizeof(unsigned int));
+}
+
+}  // namespace b200

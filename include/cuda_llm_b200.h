@@ -258,8 +258,9 @@ typedef struct CudaLlmKvCacheTarget {
 
 /* Replaces dispatch_fused_gqa<T> (kernels_api.h:52-56; kernel fused_gqa_kernel.cuh:22-212):
  * grouped-query attention over a whole prompt.  q, out [batch, num_q_heads, seq_len, head_dim],
- * k, v [batch, num_kv_heads, seq_len, head_dim], one dtype (fp16 / bf16 run on the tensor cores,
- * fp32 on a plain fp32 kernel), kv_head = q_head / (num_q_heads / num_kv_heads), causal mask
+ * k, v [batch, num_kv_heads, seq_len, head_dim], one dtype (fp16 / bf16 run on the tensor cores:
+ * tcgen05.mma with TMEM accumulators and TMA operand loads when num_q_heads / num_kv_heads is 1, 2, 4
+ * or a multiple of 8, warp-level MMA otherwise; fp32 on a plain fp32 kernel), kv_head = q_head / (num_q_heads / num_kv_heads), causal mask
  * "key position <= query position".  With `cache` not
  * NULL the same call also quantises K and V into the paged cache (the prompt's KV is then ready
  * for the decode entry points); the reference has no such output. */
@@ -267,6 +268,11 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
                          int32_t num_q_heads, int32_t num_kv_heads, int32_t seq_len, int32_t head_dim,
                          float softmax_scale, int32_t is_causal, int32_t dtype,
                          const CudaLlmKvCacheTarget* cache, void* stream);
+
+/* No counterpart in the reference.  Number of bounded waits of the tcgen05 prefill kernel that ran out
+ * since the library was loaded on the current device (0 in a healthy process; a non-zero count means
+ * some prefill outputs are invalid).  Synchronises the device. */
+int cuda_llm_prefill_wait_timeouts(uint32_t* count);
 
 /* Replaces dispatch_fused_microscaled_attention<T_OUT> (kernels_api.h:103-108; the reference declares
  * it and ships no definition, test or Python binding, so the semantics are fixed here): dense

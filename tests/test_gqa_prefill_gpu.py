@@ -132,3 +132,12 @@ def test_microscaled_dispatcher_symbol(ops):
                 "_Z36dispatch_fused_microscaled_attentionI6__halfEvPKaPKfS2_S4_S2_S4_PT_iiiifbP11CUstream_st",
                 "_Z36dispatch_fused_microscaled_attentionI13__nv_bfloat16EvPKaPKfS2_S4_S2_S4_PT_iiiifbP11CUstream_st"):
         assert hasattr(lib, sym), sym
+
+
+def test_no_prefill_wait_ran_out(ops):
+    """Collected after the prefill tests of this file: none of the bounded waits of the tcgen05 kernel
+    gave up."""
+    import ctypes as C
+    n = C.c_uint32(123)
+    ops.L.check(ops.L.load().cuda_llm_prefill_wait_timeouts(C.byref(n)), "cuda_llm_prefill_wait_timeouts")
+    assert n.value == 0
