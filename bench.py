@@ -197,14 +197,17 @@ def aux_workload(args, rank, world, local):
         if rank == 0:
             print(json.dumps({"metric": f"{args.workload}_attention_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
                               "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-                              "dtype": "bf16 mma.sync, f32 acc" if args.workload == "prefill" else "e4m3 -> f16 mma.sync, f32 acc",
+                              "dtype": ("bf16 mma.sync, f32 acc" if os.environ.get("CUDA_LLM_PREFILL_KERNEL") == "warp_mma"
+                                        else "bf16 tcgen05.mma, f32 acc in TMEM") if args.workload == "prefill"
+                                       else "e4m3 -> f16 mma.sync, f32 acc",
                               "data": "synthetic",
                               "config": {"workload": args.workload, "batch": bsz, "heads": "32q/8kv", "seq_len": seq,
                                          "head_dim": 128, "causal": True},
                               "roofline": {"bound": "tensor", "achieved": tf, "peak": tf_peak or 1400.0,
                                            "unit": "TFLOP/s", "frac": tf / (tf_peak or 1400.0),
                                            "peak_source": "measured (sustained cuBLAS bf16)" if tf_peak else "fallback",
-                                           "kernel": "gqa_prefill_kernel", "traffic": None},
+                                           "kernel": "gqa_prefill_sm100_kernel" if (args.workload == "prefill" and os.environ.get("CUDA_LLM_PREFILL_KERNEL") != "warp_mma") else "gqa_prefill_kernel",
+                                           "traffic": None},
                               "gpu_launches": steps}), flush=True)
         return
     if args.workload == "pa16":

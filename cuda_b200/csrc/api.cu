@@ -676,7 +676,9 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
     return v && strcmp(v, "warp_mma") == 0;
   }();
   cudaError_t e;
-  if (!force_warp_mma && gqa_prefill_sm100_supported(num_q_heads, num_kv_heads, head_dim, dtype) && encode_tiled_fn())
+  // (the tcgen05 kernel takes the row maximum before scaling, which needs a positive softmax scale)
+  if (!force_warp_mma && softmax_scale > 0.f && gqa_prefill_sm100_supported(num_q_heads, num_kv_heads, head_dim, dtype) &&
+      encode_tiled_fn())
     e = run_gqa_prefill_sm100(q, k, v, out, batch_size, num_q_heads, num_kv_heads, seq_len, head_dim, softmax_scale,
                               is_causal != 0, dtype, st);
   else

@@ -11,9 +11,9 @@
 //   warp 4        TMA producer: Q once, then K / V tiles of 128 tokens into a two-deep ring
 //   warp 5        allocates TMEM, issues S = Q K^T (M 128, N 128, K 16 x D/16) into one of two S
 //                 buffers in TMEM and O += P V (N = D) into the O buffer
-//   warps 0..3    one thread per row = per TMEM lane: read S with tcgen05.ld, online softmax in fp32
-//                 without any shuffle, write P (16-bit) into shared memory in the swizzled K-major
-//                 layout the MMA reads, rescale O in TMEM when a row maximum moved, write the output
+//   warps 0..3    one thread per row = per TMEM lane: read the S row with tcgen05.ld (one round trip),
+//                 online softmax in fp32 without any shuffle, write P (16-bit) into one of two
+//                 shared-memory buffers in the swizzled K-major layout the MMA reads, rescale O in TMEM when a row maximum moved, write the output
 // Shared-memory operand layouts are the canonical 128-byte-swizzle layouts of the matrix
 // descriptors: K-major rows of 64 elements for Q, K and P; MN-major (row = token, 64 head_dim
 // elements per 128-byte line) for V, which is exactly how a [tokens, D] tile lands through TMA.
@@ -42,11 +42,19 @@ __device__ unsigned int g_prefill_wait_timeouts = 0;
 constexpr int kP100Threads = 192;
 constexpr int kP100Bc = 128;  // KV tokens per tile
 
-// Bounded wait of this kernel: every event it waits for is microseconds away, so a quarter of a
-// second of polling (2^16 polls) means something is wrong, not slow.
+// Bounded wait of this kernel.  The events it waits for are a microsecond away and sit on the critical
+// path of every tile, so it polls with the non-suspending test_wait (a suspending try_wait was measured
+// to add microseconds per wait); 2^22 polls, a good fraction of a second, mean something is wrong.
 __device__ __forceinline__ bool p100_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < (1u << 16); ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
   return false;
 }
 
@@ -133,9 +141,10 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);
   const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + 2 * KV_BYTES, sP = sV + 2 * KV_BYTES;
-  const uint32_t bars = sP + P_BYTES;  // 8-byte mbarriers
-  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, kv_empty = bars + 40, s_full = bars + 56,
-                 s_empty = bars + 72, p_full = bars + 88, pv_done = bars + 96, tmem_slot = bars + 104;
+  const uint32_t bars = sP + 2 * P_BYTES;  // 8-byte mbarriers (P is double-buffered)
+  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, k_empty = bars + 40, s_full = bars + 56,
+                 s_empty = bars + 72, p_full = bars + 88, pv_done = bars + 104, v_empty = bars + 120,
+                 tmem_slot = bars + 136;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base));
   volatile uint32_t* fail_ptr = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base) + 4);
 
@@ -154,12 +163,13 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
     for (int i = 0; i < 2; ++i) {
       mbar_init(k_full + 8 * i, 1);
       mbar_init(v_full + 8 * i, 1);
-      mbar_init(kv_empty + 8 * i, 1);
+      mbar_init(k_empty + 8 * i, 1);
+      mbar_init(v_empty + 8 * i, 1);
       mbar_init(s_full + 8 * i, 1);
       mbar_init(s_empty + 8 * i, 4);   // one arrival per softmax warp
+      mbar_init(p_full + 8 * i, 4);
+      mbar_init(pv_done + 8 * i, 1);
     }
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
     *fail_ptr = 0;
     mbar_fence_init();
   }
@@ -185,9 +195,11 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
           tma_load_3d(sQ + c * QCH + i * BQ * 128, &maps.q, c * 64, q0, b * a.Hq + kvh * a.group + chunk * a.gsz + i, q_full);
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
-        if (j >= 2 && !p100_wait(kv_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
+        // the K slot is free as soon as S of two tiles ago is done, the V slot only after its P V
+        if (j >= 2 && !p100_wait(k_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
         mbar_arrive_expect_tx(k_full + 8 * st, KV_BYTES);
         for (int c = 0; c < NCH; ++c) tma_load_3d(sK + st * KV_BYTES + c * QCH, &maps.k, c * 64, j * kP100Bc, b * a.Hkv + kvh, k_full + 8 * st);
+        if (j >= 2 && !p100_wait(v_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
         mbar_arrive_expect_tx(v_full + 8 * st, KV_BYTES);
         for (int c = 0; c < NCH; ++c) tma_load_3d(sV + st * KV_BYTES + c * QCH, &maps.v, c * 64, j * kP100Bc, b * a.Hkv + kvh, v_full + 8 * st);
       }
@@ -200,16 +212,16 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       bool ok = p100_wait(q_full, 0);
       auto issue_pv = [&](int j) -> bool {  // O (+)= P_j V_j
         const int st = j & 1;
-        if (!p100_wait(p_full, j & 1) || !p100_wait(v_full + 8 * st, (j >> 1) & 1)) return false;
+        if (!p100_wait(p_full + 8 * st, (j >> 1) & 1) || !p100_wait(v_full + 8 * st, (j >> 1) & 1)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < kP100Bc / 16; ++kk) {
-          const uint64_t ad = smem_desc_sw128(sP + (kk >> 2) * QCH + (kk & 3) * 32, 16, 1024);
+          const uint64_t ad = smem_desc_sw128(sP + st * P_BYTES + (kk >> 2) * QCH + (kk & 3) * 32, 16, 1024);
           const uint64_t bd = smem_desc_sw128(sV + st * KV_BYTES + kk * 2048, QCH, 1024);
           umma_f16(tmem + 256, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(pv_done);            // P buffer free, O updated
-        umma_commit(kv_empty + 8 * st);  // K / V stage free
+        umma_commit(pv_done + 8 * st);   // this P buffer free, O updated
+        umma_commit(v_empty + 8 * st);   // V stage free
         return true;
       };
       for (int j = 0; ok && j < n_tiles; ++j) {
@@ -224,6 +236,7 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
           umma_f16(tmem + st * 128, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(s_full + 8 * st);
+        umma_commit(k_empty + 8 * st);   // K stage free once S is done
         if (j >= 1) ok = issue_pv(j - 1);
       }
       if (ok) ok = issue_pv(n_tiles - 1);
@@ -242,30 +255,40 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       if (!p100_wait(s_full + 8 * st, (j >> 1) & 1)) { ok = false; break; }
       tc_fence_after();
       const bool need_mask = (kv0 + kP100Bc > a.S) || (a.causal && kv0 + kP100Bc - 1 > q0);
-      // pass 1: row maximum
-      float mx = NEG_INF;
-#pragma unroll 1
-      for (int c = 0; c < kP100Bc / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + st * 128 + c * 32, r);
-        tc_wait_ld();
+      // the whole S row in one TMEM round trip: four loads in flight, one wait
+      uint32_t sr[4][32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(r[i]) * a.scale_log2;
-          if (need_mask) {
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + st * 128 + c * 32, sr[c]);
+      tc_wait_ld();
+      // S buffer consumed: the next-but-one S may be issued into it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty + 8 * st);
+      if (need_mask) {  // diagonal / last tile only
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
             const int key = kv0 + c * 32 + i;
-            if (key >= a.S || (a.causal && key > qpos)) x = NEG_INF;
+            if (key >= a.S || (a.causal && key > qpos)) sr[c][i] = __float_as_uint(NEG_INF);
           }
-          mx = fmaxf(mx, x);
-        }
       }
-      const float m_new = fmaxf(m_run, mx);
+      // row maximum of the raw scores with eight independent chains (the softmax scale is positive)
+      float mx8[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx8[i] = NEG_INF;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sr[c][i]));
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      const float m_new = fmaxf(m_run, mx * a.scale_log2);
       const float alpha = fast_exp2(m_run - m_new);
       m_run = m_new;
-      // the previous P V must be done before P is overwritten and before O is rescaled
-      if (j >= 1 && !p100_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
-      tc_fence_after();
+      // O is rescaled only when a row maximum of this warp moved, and only after the previous P V is done
       if (j >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        if (!p100_wait(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1)) { ok = false; break; }
+        tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
@@ -277,47 +300,39 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
         }
         tc_wait_st();
       }
-      // pass 2: P = 2^(s - m), row sum, P (16-bit) into the swizzled K-major operand buffer
-      float ps = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kP100Bc / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + st * 128 + c * 32, r);
-        tc_wait_ld();
+      // this P buffer was read by the P V of two tiles ago
+      if (j >= 2 && !p100_wait(pv_done + 8 * st, ((j >> 1) - 1) & 1)) { ok = false; break; }
+      // P = 2^(s - m), row sum, P (16-bit) into the swizzled K-major operand buffer
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m_new;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float x0 = fmaf(__uint_as_float(r[i]), a.scale_log2, -m_new), x1 = fmaf(__uint_as_float(r[i + 1]), a.scale_log2, -m_new);
-          if (need_mask) {
-            const int key = kv0 + c * 32 + i;
-            if (key >= a.S || (a.causal && key > qpos)) x0 = NEG_INF;
-            if (key + 1 >= a.S || (a.causal && key + 1 > qpos)) x1 = NEG_INF;
-          }
-          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-          ps += p0 + p1;
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), a.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), a.scale_log2, neg_m));
+          ps4[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = a.bf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
         // columns 32c .. 32c+31 of this row: four 16-byte units of the 128-byte line of chunk c / 2
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int unit = (c & 1) * 4 + u;
-          const uint32_t addr = sP + (c >> 1) * QCH + row * 128 + ((unit ^ (row & 7)) << 4);
+          const uint32_t addr = sP + st * P_BYTES + (c >> 1) * QCH + row * 128 + ((unit ^ (row & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * u]), "r"(pk[4 * u + 1]),
                        "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3]) : "memory");
         }
       }
-      l_run = l_run * alpha + ps;
-      // S buffer consumed; P written (visible to the async proxy) and O rescaled
+      l_run = l_run * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
+      // P written (made visible to the async proxy) and O rescaled: the P V of this tile may go
       tc_fence_before();
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_empty + 8 * st);
-        mbar_arrive(p_full);
-      }
+      if (lane == 0) mbar_arrive(p_full + 8 * st);
     }
     // epilogue: O / l -> out
-    if (ok && !p100_wait(pv_done, (n_tiles - 1) & 1)) ok = false;
+    if (ok && !p100_wait(pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1)) ok = false;
     if (!ok) {
       if (lane == 0) give_up();
     } else {
@@ -392,7 +407,7 @@ cudaError_t run_gqa_prefill_sm100(const void* q, const void* k, const void* v, v
       !encode_bhsd(enc, &maps.v, v, (long long)B * Hkv, S, D, kP100Bc))
     return cudaErrorInvalidValue;
   const int nch = D / 64;
-  size_t smem = (size_t)nch * 16384 * 5 + 2 * 16384 + 128;
+  size_t smem = (size_t)nch * 16384 * 5 + 4 * 16384 + 256;  // Q, 2 x K, 2 x V, 2 x P, barriers
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: a CTA allocates all 512 TMEM columns
   auto kern = D == 64 ? gqa_prefill_sm100_kernel<64> : gqa_prefill_sm100_kernel<128>;
   static int configured[2][64] = {{0}};
