@@ -268,11 +268,13 @@ class Bench:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed_blocks(self, fn, steps, min_total_ms=MIN_TIMED_MS):
+    def timed_blocks(self, fn, steps, min_total_ms=None):
         """Time blocks of exactly `steps` calls (CUDA events on the launching stream, a barrier and a
         device synchronise on both sides of every block) until `min_total_ms` have been measured,
         three blocks at least; every block's time is the maximum over the ranks.  Returns the
         per-step milliseconds of every block."""
+        if min_total_ms is None:
+            min_total_ms = self.args.min_timed_ms
         blocks, total = [], 0.0
         while len(blocks) < 3 or (total < min_total_ms and len(blocks) < 400):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -477,6 +479,8 @@ def main():
     ap.add_argument("--no-extra-workloads", action="store_true",
                     help="skip the cfg3 / cfg4 / cfg5 legs that follow the headline workload")
     ap.add_argument("--kernel-only", action="store_true", help="only the attention-kernel loop (ncu)")
+    ap.add_argument("--min-timed-ms", type=float, default=MIN_TIMED_MS,
+                    help="repeat every timed loop until this much has been measured (lower it under a profiler)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.warmup < 3:
@@ -724,7 +728,7 @@ def main():
         "pct_of_measured_copy_peak": 100.0 * value * 1e3 / (peak * world),
         "timing": {"method": "CUDA events around blocks of `steps` back-to-back steps, barrier + synchronize on both "
                              "sides of every block, max over ranks per block, median over blocks",
-                   "blocks": len(blocks_total), "min_timed_ms": MIN_TIMED_MS,
+                   "blocks": len(blocks_total), "min_timed_ms": args.min_timed_ms,
                    "ms_per_step_min": min(blocks_total), "ms_per_step_max": max(blocks_total)},
         "stable_metadata": {"resident_loops_set_CUDA_LLM_FLAG_STABLE_METADATA": True,
                             "ms_per_step_with_flag": ms_step, "ms_per_step_without_flag": ms_step_unflagged,

@@ -8,11 +8,13 @@
 // One CTA per (batch, KV head, block of query positions).  Its 128 accumulator rows are the query
 // heads that share the KV head (1, 2, 4 or 8 of them) times 128 / heads consecutive query positions,
 // so a K / V tile is fetched once for the whole group.  Roles:
-//   warp 4        TMA producer: Q once, then K / V tiles of 128 tokens into a two-deep ring
-//   warp 5        allocates TMEM, issues S = Q K^T (M 128, N 128, K 16 x D/16) into one of two S
+//   warp 8        TMA producer: Q once, then K / V tiles of 128 tokens into a two-deep ring
+//   warp 9        allocates TMEM, issues S = Q K^T (M 128, N 128, K 16 x D/16) into one of two S
 //                 buffers in TMEM and O += P V (N = D) into the O buffer
-//   warps 0..3    one thread per row = per TMEM lane: read the S row with tcgen05.ld (one round trip),
-//                 online softmax in fp32 without any shuffle, write P (16-bit) into one of two
+//   warps 0..7    two threads per row = per TMEM lane (warps w and w + 4 share lane quarter w, one takes
+//                 columns 0..63 of the row, the other 64..127): read their half of the S row with
+//                 tcgen05.ld (one round trip), online softmax in fp32 without any shuffle (the two halves
+//                 exchange their maxima through shared memory), write P (16-bit) into one of two
 //                 shared-memory buffers in the swizzled K-major layout the MMA reads, rescale O in TMEM when a row maximum moved, write the output
 // Shared-memory operand layouts are the canonical 128-byte-swizzle layouts of the matrix
 // descriptors: K-major rows of 64 elements for Q, K and P; MN-major (row = token, 64 head_dim
@@ -39,7 +41,7 @@ struct Prefill100Args {
 
 __device__ unsigned int g_prefill_wait_timeouts = 0;
 
-constexpr int kP100Threads = 192;
+constexpr int kP100Threads = 320;  // 8 softmax warps, 1 TMA warp, 1 MMA warp
 constexpr int kP100Bc = 128;  // KV tokens per tile
 
 // Bounded wait of this kernel.  The events it waits for are a microsecond away and sit on the critical
@@ -144,7 +146,9 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
   const uint32_t bars = sP + 2 * P_BYTES;  // 8-byte mbarriers (P is double-buffered)
   const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, k_empty = bars + 40, s_full = bars + 56,
                  s_empty = bars + 72, p_full = bars + 88, pv_done = bars + 104, v_empty = bars + 120,
-                 tmem_slot = bars + 136;
+                 pair_bar = bars + 136, tmem_slot = bars + 168;
+  // row maxima (per tile parity, per column half) and final row sums exchanged between the two threads of a row
+  float* xchg = reinterpret_cast<float*>(smem + (bars - base) + 256);  // [2 parities][2 halves][128 rows]
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base));
   volatile uint32_t* fail_ptr = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base) + 4);
 
@@ -166,14 +170,15 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       mbar_init(k_empty + 8 * i, 1);
       mbar_init(v_empty + 8 * i, 1);
       mbar_init(s_full + 8 * i, 1);
-      mbar_init(s_empty + 8 * i, 4);   // one arrival per softmax warp
-      mbar_init(p_full + 8 * i, 4);
+      mbar_init(s_empty + 8 * i, 8);   // one arrival per softmax warp
+      mbar_init(p_full + 8 * i, 8);
       mbar_init(pv_done + 8 * i, 1);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(pair_bar + 8 * i, 2);  // the two warps that share a lane quarter
     *fail_ptr = 0;
     mbar_fence_init();
   }
-  if (warp == 5) {  // TMEM: S0 [0,128), S1 [128,256), O [256, 256 + D)
+  if (warp == 9) {  // TMEM: S0 [0,128), S1 [128,256), O [256, 256 + D)
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -186,7 +191,7 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
     atomicAdd(&g_prefill_wait_timeouts, 1u);
   };
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, (uint32_t)a.gsz * BQ * D * 2);
@@ -204,7 +209,7 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
         for (int c = 0; c < NCH; ++c) tma_load_3d(sV + st * KV_BYTES + c * QCH, &maps.v, c * 64, j * kP100Bc, b * a.Hkv + kvh, v_full + 8 * st);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer (one thread)
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc_f16(a.bf16, 0, 128, kP100Bc);
@@ -243,22 +248,33 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       if (!ok) give_up();
     }
   } else {
-    // ------------------------------------------------------------------ softmax warps: thread = row
-    const int row = tid;                        // TMEM lane
+    // ------------------------------------------------------------------ softmax warps: two threads per row
+    const int row = tid & 127, half = tid >> 7;  // TMEM lane; which 64 columns of S / which half of O
+    const int quarter = warp & 3;
     const int hi = row / BQ, qpos = q0 + row - hi * BQ;
     const int qh = kvh * a.group + chunk * a.gsz + hi;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    constexpr int OC = D / 2;                     // O columns of this thread
     float m_run = -1.0e30f, l_run = 0.f;
     bool ok = true;
+    uint32_t pair_phase = 0;
+    // both warps of a quarter: write, then meet (bounded) before reading the other's values
+    auto pair_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair_bar + 8 * quarter);
+      const bool done = p100_wait(pair_bar + 8 * quarter, pair_phase);
+      pair_phase ^= 1;
+      return done;
+    };
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1, kv0 = j * kP100Bc;
       if (!p100_wait(s_full + 8 * st, (j >> 1) & 1)) { ok = false; break; }
       tc_fence_after();
       const bool need_mask = (kv0 + kP100Bc > a.S) || (a.causal && kv0 + kP100Bc - 1 > q0);
-      // the whole S row in one TMEM round trip: four loads in flight, one wait
-      uint32_t sr[4][32];
+      // this thread's half of the S row in one TMEM round trip
+      uint32_t sr[2][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + st * 128 + c * 32, sr[c]);
+      for (int c = 0; c < 2; ++c) tmem_ld32(tmem + lane_base + st * 128 + half * 64 + c * 32, sr[c]);
       tc_wait_ld();
       // S buffer consumed: the next-but-one S may be issued into it
       tc_fence_before();
@@ -266,22 +282,26 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       if (lane == 0) mbar_arrive(s_empty + 8 * st);
       if (need_mask) {  // diagonal / last tile only
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int key = kv0 + c * 32 + i;
+            const int key = kv0 + half * 64 + c * 32 + i;
             if (key >= a.S || (a.causal && key > qpos)) sr[c][i] = __float_as_uint(NEG_INF);
           }
       }
-      // row maximum of the raw scores with eight independent chains (the softmax scale is positive)
+      // row maximum of the raw scores with eight independent chains (the softmax scale is positive),
+      // then the maximum of the other half of the row
       float mx8[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) mx8[i] = NEG_INF;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sr[c][i]));
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      xchg[(st * 2 + half) * 128 + row] = mx;
+      if (!pair_sync()) { ok = false; break; }
+      mx = fmaxf(mx, xchg[(st * 2 + (half ^ 1)) * 128 + row]);
       const float m_new = fmaxf(m_run, mx * a.scale_log2);
       const float alpha = fast_exp2(m_run - m_new);
       m_run = m_new;
@@ -290,23 +310,23 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
         if (!p100_wait(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < OC / 32; ++c) {
           uint32_t r[32];
-          tmem_ld32(tmem + lane_base + 256 + c * 32, r);
+          tmem_ld32(tmem + lane_base + 256 + half * OC + c * 32, r);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(tmem + lane_base + 256 + c * 32, r);
+          tmem_st32(tmem + lane_base + 256 + half * OC + c * 32, r);
         }
         tc_wait_st();
       }
       // this P buffer was read by the P V of two tiles ago
       if (j >= 2 && !p100_wait(pv_done + 8 * st, ((j >> 1) - 1) & 1)) { ok = false; break; }
-      // P = 2^(s - m), row sum, P (16-bit) into the swizzled K-major operand buffer
+      // P = 2^(s - m), row sum, P (16-bit) into the swizzled K-major operand buffer (64-token chunk `half`)
       float ps4[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_m = -m_new;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -315,11 +335,11 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
           ps4[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = a.bf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
-        // columns 32c .. 32c+31 of this row: four 16-byte units of the 128-byte line of chunk c / 2
+        // columns 32c .. 32c+31 of this half row: four 16-byte units of the 128-byte line
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const int unit = (c & 1) * 4 + u;
-          const uint32_t addr = sP + st * P_BYTES + (c >> 1) * QCH + row * 128 + ((unit ^ (row & 7)) << 4);
+          const int unit = c * 4 + u;
+          const uint32_t addr = sP + st * P_BYTES + half * QCH + row * 128 + ((unit ^ (row & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * u]), "r"(pk[4 * u + 1]),
                        "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3]) : "memory");
         }
@@ -331,19 +351,25 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + 8 * st);
     }
-    // epilogue: O / l -> out
+    // epilogue: the two halves add their row sums, then O / l -> out (each thread its half of the row)
+    if (ok) {
+      xchg[((n_tiles & 1) * 2 + half) * 128 + row] = l_run;  // the parity slot the last tile did not use
+      ok = pair_sync();
+    }
     if (ok && !p100_wait(pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1)) ok = false;
     if (!ok) {
       if (lane == 0) give_up();
     } else {
       tc_fence_after();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      const bool store = hi < a.gsz && qpos < a.S;
-      uint4* og = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (((size_t)b * a.Hq + qh) * (size_t)a.S + (store ? qpos : 0)) * D);
+      const float l_tot = l_run + xchg[((n_tiles & 1) * 2 + (half ^ 1)) * 128 + row];
+      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+      const bool store = qpos < a.S;
+      uint4* og = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) +
+                                           (((size_t)b * a.Hq + qh) * (size_t)a.S + (store ? qpos : 0)) * D + half * OC);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem + lane_base + 256 + c * 32, r);
+        tmem_ld32(tmem + lane_base + 256 + half * OC + c * 32, r);
         tc_wait_ld();
         if (store) {
 #pragma unroll
@@ -363,7 +389,7 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
   // common exit: every thread arrives here, also after a wait that ran out
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, 512);
+  if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 // ---- host side -------------------------------------------------------------------------------------
@@ -407,7 +433,7 @@ cudaError_t run_gqa_prefill_sm100(const void* q, const void* k, const void* v, v
       !encode_bhsd(enc, &maps.v, v, (long long)B * Hkv, S, D, kP100Bc))
     return cudaErrorInvalidValue;
   const int nch = D / 64;
-  size_t smem = (size_t)nch * 16384 * 5 + 4 * 16384 + 256;  // Q, 2 x K, 2 x V, 2 x P, barriers
+  size_t smem = (size_t)nch * 16384 * 5 + 4 * 16384 + 256 + 512 * 4;  // Q, 2 x K, 2 x V, 2 x P, barriers, exchange
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: a CTA allocates all 512 TMEM columns
   auto kern = D == 64 ? gqa_prefill_sm100_kernel<64> : gqa_prefill_sm100_kernel<128>;
   static int configured[2][64] = {{0}};

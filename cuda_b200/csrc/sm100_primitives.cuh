@@ -90,7 +90,7 @@ __device__ __forceinline__ void bulk_g2s_hint(uint32_t dst_smem, const void* src
 }
 
 // 3-D tiled TMA copy global -> shared through a tensor map (cuTensorMapEncodeTiled), completion counted
-// on an mbarrier, with an L2 eviction policy.  No cluster multicast: the box lands in this CTA's own
+// on an mbarrier, with an L2 eviction policy.  The box lands in this CTA's own
 // shared memory.  The innermost coordinate times the element size must be a multiple of 16 bytes
 // (callers pass 0), the destination aligned to the swizzle pattern of the map.
 __device__ __forceinline__ void tma_load_3d_hint(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
