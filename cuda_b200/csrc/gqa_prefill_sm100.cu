@@ -60,6 +60,20 @@ __device__ __forceinline__ bool p100_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
+// 2^x for x <= 0 on the FMA / ALU pipes instead of the special-function unit, which is the busiest
+// unit of the softmax warps (one MUFU.EX2 per score is as many cycles per tile as the MMAs): round x
+// to the nearest integer n with the 1.5 * 2^23 trick, evaluate a cubic fit of 2^f on f = x - n in
+// [-0.5, 0.5] (relative error 8e-5, below what a 16-bit P keeps), add n to the exponent field.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);  // masked scores (-inf) and anything below 2^-126 end up at ~1e-38
+  const float r = x + 12582912.f;
+  const float f = x - (r - 12582912.f);
+  float p = fmaf(f, 0.05508868396282196f, 0.24260404706001282f);
+  p = fmaf(f, p, 0.6932762265205383f);
+  p = fmaf(f, p, 0.9999289512634277f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
+}
+
 // ---- PTX wrappers ------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
                                             uint32_t bar) {
@@ -330,8 +344,11 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), a.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), a.scale_log2, neg_m));
+          // every fourth exponential on the FMA pipe, the others on the special-function unit
+          const float x0 = fmaf(__uint_as_float(sr[c][i]), a.scale_log2, neg_m);
+          const float x1 = fmaf(__uint_as_float(sr[c][i + 1]), a.scale_log2, neg_m);
+          const float p0 = fast_exp2(x0);
+          const float p1 = ((i & 2) != 0) ? exp2_poly(x1) : fast_exp2(x1);
           ps4[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = a.bf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }

@@ -214,7 +214,9 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a, const __grid_constant_
   constexpr bool KV16 = (MODE >= MODE_KV_F16);  // 2-byte elements, no scales
   constexpr bool TM = (MODE >= MODE_KV_F16_TM);  // token-major rows [token][head_dim] instead of pages [head_dim][token]
   constexpr bool BF = (MODE == MODE_KV_BF16 || MODE == MODE_KV_BF16_TM);
-  // 16-bit pages of 32 / 64 tokens: rows of 64 / 128 bytes, loaded as SWIZZLE_64B / SWIZZLE_128B boxes
+  // 16-bit pages of 32 / 64 tokens: rows of 64 / 128 bytes, loaded as SWIZZLE_64B / SWIZZLE_128B boxes.
+  // (Pages of 16 tokens stay on 1-D bulk copies: as SWIZZLE_32B boxes of 32-byte rows they were measured
+  // at 5.0 TB/s against 6.2, the tiled copy engine being slow on 32-byte lines.)
   constexpr bool TMA3D = KV16 && !TM && PAGE >= 32;
   constexpr uint32_t SWZ_MASK = (PAGE >= 64) ? 7u : 3u;  // 16-byte chunk index ^= (address >> 7) & mask
   constexpr int SUB = (KV16 || NT == 1) ? 16 : 32;  // tokens per warp sub-tile
