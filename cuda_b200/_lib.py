@@ -18,6 +18,7 @@ SCALE_PER_HEAD, SCALE_PER_BLOCK, SCALE_PER_TOKEN, SCALE_MX_E8M0 = 0, 1, 2, 3
 FLAG_SKIP_MERGE = 1
 FLAG_STABLE_METADATA = 64   # lengths / offsets / block tables are not written by the kernel in front of the call
 FLAG_TEST_STALL = 128       # failure-path test: one stage is announced but never sent; waits give up quickly
+FLAG_TCGEN05 = 4096         # run on the tcgen05 / tensor-memory decode kernel where it applies (opt-in, measured slower)
 
 
 class PagedDecodeParams(C.Structure):
@@ -68,6 +69,7 @@ SYMBOLS = {
     "cuda_llm_gqa_prefill": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 5 + [C.c_float, C.c_int32, C.c_int32,
                                                                     C.POINTER(KvCacheTarget), C.c_void_p]),
     "cuda_llm_prefill_wait_timeouts": (C.c_int, [C.POINTER(C.c_uint32)]),
+    "cuda_llm_decode_tcgen05_counters": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]),
     "cuda_llm_mx_attention": (C.c_int, [C.c_void_p] * 7 + [C.c_int32] * 5 + [C.c_float, C.c_int32, C.c_int32, C.c_void_p]),
     "cuda_llm_dequant_pages": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,

@@ -7,6 +7,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <cmath>
+#include <atomic>
 #include <mutex>
 
 #include "decode_launch.cuh"
@@ -217,6 +218,57 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   return CUDA_LLM_OK;
 }
 
+// Work layout of the tcgen05 decode kernel (paged_decode_sm100.cu): one KV head per unit, tiles of 128
+// tokens, two results (one per softmax group) of `rows_max` rows per (CTA, sequence, KV head).
+static int make_layout_sm100(int S, int Hq, int Hkv, int D, int page, int max_q_len, int v_format, int scale_mode,
+                             int num_ctas, Layout& L) {
+  if (S < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D != 128 || page != 16) return CUDA_LLM_EINVAL;
+  const int group = Hq / Hkv;
+  if (max_q_len < 1) max_q_len = 1;
+  if (group * max_q_len > 16) return CUDA_LLM_EINVAL;
+  memset(&L, 0, sizeof(L));
+  L.NT = (group * max_q_len <= 8) ? 1 : 2;
+  L.rows_max = 8 * L.NT;
+  L.HG = 1;
+  L.SUBS = 2;
+  L.tok_stage = 128;
+  L.n_hg = Hkv;
+  L.PPS = 128 / page;
+  const int DV = (v_format == CUDA_LLM_KV_FP4_E2M1) ? D / 2 : D;
+  L.k_chunk = (uint32_t)D * page;
+  L.v_chunk = (uint32_t)DV * page;
+  L.ks_chunk = L.vs_chunk = (scale_mode == CUDA_LLM_SCALE_PER_TOKEN) ? (uint32_t)page * 4 : (uint32_t)(D / 32) * page;
+  if (num_ctas <= 0) num_ctas = sm_count_cached();
+  if (num_ctas <= 0) return fail(CUDA_LLM_ECUDA, "cannot query the SM count");
+  L.grid = num_ctas;
+  const size_t n_slots = (size_t)S * L.n_hg + L.grid;
+  const size_t rows = n_slots * L.SUBS * L.HG * L.rows_max;
+  L.ws_table = 256;
+  L.ws_lse = align_up(L.ws_table + (size_t)S * L.n_hg * 16, 256);
+  L.ws_o = align_up(L.ws_lse + rows * 4, 256);
+  L.ws_total = align_up(L.ws_o + rows * D * 4, 256);
+  return CUDA_LLM_OK;
+}
+
+cudaError_t launch_paged_decode_sm100(const DecodeArgs& a, int mode, int rp, int grid, cudaStream_t st);
+unsigned int decode100_wait_timeouts();
+static std::atomic<uint64_t> g_sm100_launches{0};
+
+// The tcgen05 kernel serves head_dim 128, pages of 16 tokens, E4M3 K and V with per-token fp32 or E8M0
+// block scales and 16-bit queries, when the call (CUDA_LLM_FLAG_TCGEN05) or the process
+// (CUDA_LLM_DECODE_KERNEL=tcgen05) asks for it.
+static bool decode_sm100_wanted(const CudaLlmPagedDecodeParams* p) {
+  const bool kv16 = (p->k_format == CUDA_LLM_KV_F16 || p->k_format == CUDA_LLM_KV_BF16);
+  if (kv16 || p->head_dim != 128 || p->page_size != 16) return false;
+  if (p->k_format != CUDA_LLM_KV_FP8_E4M3 || p->v_format != CUDA_LLM_KV_FP8_E4M3) return false;
+  if (p->scale_mode != CUDA_LLM_SCALE_PER_TOKEN && p->scale_mode != CUDA_LLM_SCALE_MX_E8M0) return false;
+  if (p->q_dtype == CUDA_LLM_F32 || p->rope_cos || p->rope_sin) return false;
+  if (((uintptr_t)p->query & 7) != 0) return false;
+  if (p->flags & CUDA_LLM_FLAG_TCGEN05) return true;
+  const char* v = getenv("CUDA_LLM_DECODE_KERNEL");
+  return v != nullptr && strcmp(v, "tcgen05") == 0;
+}
+
 using LaunchFn = cudaError_t (*)(const DecodeArgs&, const KvTensorMaps&, int, size_t, cudaStream_t);
 
 template <int D, int MODE>
@@ -277,6 +329,10 @@ size_t cuda_llm_paged_decode_workspace_bytes(int32_t num_seqs, int32_t num_q_hea
   if (make_layout(num_seqs, num_q_heads, num_kv_heads, head_dim, page_size, max_q_len, CUDA_LLM_KV_BF16,
                   CUDA_LLM_KV_BF16, CUDA_LLM_SCALE_PER_HEAD, num_ctas, L) == CUDA_LLM_OK && L.ws_total > need)
     need = L.ws_total;
+  // and the tcgen05 kernel's one-head units
+  if (make_layout_sm100(num_seqs, num_q_heads, num_kv_heads, head_dim, page_size, max_q_len, CUDA_LLM_KV_FP8_E4M3,
+                        CUDA_LLM_SCALE_PER_TOKEN, num_ctas, L) == CUDA_LLM_OK && L.ws_total > need)
+    need = L.ws_total;
   return need;
 }
 
@@ -311,6 +367,12 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
                        p->max_q_len, p->k_format, p->v_format, p->scale_mode, p->num_ctas, L, false,
                        p->q_dtype == CUDA_LLM_F32 ? 4 : 2);
   if (rc != CUDA_LLM_OK) return rc;
+  const bool sm100 = decode_sm100_wanted(p);
+  if (sm100) {
+    rc = make_layout_sm100(p->num_seqs, p->num_q_heads, p->num_kv_heads, p->head_dim, p->page_size, p->max_q_len,
+                           p->v_format, p->scale_mode, p->num_ctas, L);
+    if (rc != CUDA_LLM_OK) return rc;
+  }
   if (!p->workspace || p->workspace_bytes < L.ws_total)
     return fail(CUDA_LLM_EWORKSPACE, "workspace missing or smaller than cuda_llm_paged_decode_workspace_bytes()");
 
@@ -347,10 +409,10 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   a.q_dtype = p->q_dtype;
   a.out_dtype = p->out_dtype;
   a.per_block = !kv16 && (p->scale_mode == CUDA_LLM_SCALE_PER_BLOCK);
-  a.helper_pairs = kv16 ? 0 : 1;
+  a.helper_pairs = (kv16 || sm100) ? 0 : 1;
   a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
   a.n_stages = L.n_stages;
-  if (!((uintptr_t)p->query & 15)) {  // bulk copies need a 16-byte aligned source
+  if (!sm100 && !((uintptr_t)p->query & 15)) {  // bulk copies need a 16-byte aligned source
     a.q_smem_off = L.q_smem_off;
     a.q_smem_bytes = L.q_smem_bytes;
     a.q_smem_tokens = L.q_smem_tokens;
@@ -403,6 +465,22 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   else if (p->scale_mode == CUDA_LLM_SCALE_MX_E8M0) a.ks_blk_stride = a.vs_blk_stride = (uint64_t)Hkv * (D / 32) * page;
 
   const bool precise = (p->q_dtype == CUDA_LLM_F32) && L.NT == 1;
+  if (sm100) {
+    rc = check_device();
+    if (rc != CUDA_LLM_OK) return rc;
+    a.n_stages = 0;  // the kernel's own ring depth
+#ifdef CUDA_LLM_DIAGNOSTICS
+    a.n_stages = (p->flags >> 8) & 0xF;
+#endif
+    cudaError_t e = launch_paged_decode_sm100(a, p->scale_mode == CUDA_LLM_SCALE_PER_TOKEN ? MODE_TOKEN_SCALE : MODE_MX8,
+                                              L.rows_max, L.grid, st);
+    if (e != cudaSuccess) return fail_cuda(e, "paged_decode_sm100_kernel launch");
+    g_sm100_launches.fetch_add(1, std::memory_order_relaxed);
+    if (p->flags & CUDA_LLM_FLAG_SKIP_MERGE) return CUDA_LLM_OK;
+    e = launch_merge_splits<128>(a, page, L.grid, st);
+    if (e != cudaSuccess) return fail_cuda(e, "merge_splits_kernel launch");
+    return CUDA_LLM_OK;
+  }
   LaunchFn fn = nullptr;
   if (kv16)
     fn = pick_kv16(p->k_format == CUDA_LLM_KV_BF16, D, page, L.NT);
@@ -688,6 +766,16 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
   if (cache) {
     e = run_kv_append_prefill(k, v, *cache, batch_size, num_kv_heads, seq_len, head_dim, dtype, st);
     if (e != cudaSuccess) return fail_cuda(e, "kv_append_kernel launch");
+  }
+  return CUDA_LLM_OK;
+}
+
+int cuda_llm_decode_tcgen05_counters(uint64_t* launches, uint32_t* wait_timeouts) {
+  if (launches) *launches = g_sm100_launches.load(std::memory_order_relaxed);
+  if (wait_timeouts) {
+    const int rc = check_device();
+    if (rc != CUDA_LLM_OK) return rc;
+    *wait_timeouts = decode100_wait_timeouts();
   }
   return CUDA_LLM_OK;
 }

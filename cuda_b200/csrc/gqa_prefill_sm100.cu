@@ -21,7 +21,7 @@
 // elements per 128-byte line) for V, which is exactly how a [tokens, D] tile lands through TMA.
 // Every wait is bounded; a wait that runs out raises a device-side counter, lets the CTA fall
 // through to the common exit (TMEM is released there) and leaves garbage in that CTA's rows.
-#include "sm100_primitives.cuh"
+#include "tcgen05_primitives.cuh"
 #include "cuda_llm_b200.h"
 
 namespace b200 {
@@ -44,22 +44,6 @@ __device__ unsigned int g_prefill_wait_timeouts = 0;
 constexpr int kP100Threads = 320;  // 8 softmax warps, 1 TMA warp, 1 MMA warp
 constexpr int kP100Bc = 128;  // KV tokens per tile
 
-// Bounded wait of this kernel.  The events it waits for are a microsecond away and sit on the critical
-// path of every tile, so it polls with the non-suspending test_wait (a suspending try_wait was measured
-// to add microseconds per wait); 2^22 polls, a good fraction of a second, mean something is wrong.
-__device__ __forceinline__ bool p100_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-
 // 2^x for x <= 0 on the FMA / ALU pipes instead of the special-function unit, which is the busiest
 // unit of the softmax warps (one MUFU.EX2 per score is as many cycles per tile as the MMAs): round x
 // to the nearest integer n with the 1.5 * 2^23 trick, evaluate a cubic fit of 2^f on f = x - n in
@@ -74,77 +58,12 @@ __device__ __forceinline__ float exp2_poly(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
 }
 
-// ---- PTX wrappers ------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
                                             uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(dst_smem), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
       : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// D[tmem] (+)= A[smem desc] * B[smem desc], 16-bit operands, fp32 accumulate; issued by ONE thread
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-// the mbarrier receives one arrival when every tcgen05 operation issued so far by this thread is done
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane (base lane + i)
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte offsets
-// (all without their 4 low bits), descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor of kind::f16: fp32 accumulate, A / B format (0 fp16, 1 bf16), B major-ness
-// (0 K-major, 1 MN-major), N >> 3 at bit 17, M >> 4 at bit 24.
-__device__ __forceinline__ uint32_t instr_desc_f16(int fmt, int b_mn_major, int M, int N) {
-  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)b_mn_major << 16) |
-         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 template <int D>
@@ -215,10 +134,10 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
         // the K slot is free as soon as S of two tiles ago is done, the V slot only after its P V
-        if (j >= 2 && !p100_wait(k_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
+        if (j >= 2 && !tc_wait(k_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
         mbar_arrive_expect_tx(k_full + 8 * st, KV_BYTES);
         for (int c = 0; c < NCH; ++c) tma_load_3d(sK + st * KV_BYTES + c * QCH, &maps.k, c * 64, j * kP100Bc, b * a.Hkv + kvh, k_full + 8 * st);
-        if (j >= 2 && !p100_wait(v_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
+        if (j >= 2 && !tc_wait(v_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
         mbar_arrive_expect_tx(v_full + 8 * st, KV_BYTES);
         for (int c = 0; c < NCH; ++c) tma_load_3d(sV + st * KV_BYTES + c * QCH, &maps.v, c * 64, j * kP100Bc, b * a.Hkv + kvh, v_full + 8 * st);
       }
@@ -228,10 +147,10 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc_f16(a.bf16, 0, 128, kP100Bc);
       const uint32_t idesc_o = instr_desc_f16(a.bf16, 1, 128, D);
-      bool ok = p100_wait(q_full, 0);
+      bool ok = tc_wait(q_full, 0);
       auto issue_pv = [&](int j) -> bool {  // O (+)= P_j V_j
         const int st = j & 1;
-        if (!p100_wait(p_full + 8 * st, (j >> 1) & 1) || !p100_wait(v_full + 8 * st, (j >> 1) & 1)) return false;
+        if (!tc_wait(p_full + 8 * st, (j >> 1) & 1) || !tc_wait(v_full + 8 * st, (j >> 1) & 1)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < kP100Bc / 16; ++kk) {
@@ -245,7 +164,7 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       };
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int st = j & 1;
-        ok = p100_wait(k_full + 8 * st, (j >> 1) & 1) && (j < 2 || p100_wait(s_empty + 8 * st, ((j >> 1) - 1) & 1));
+        ok = tc_wait(k_full + 8 * st, (j >> 1) & 1) && (j < 2 || tc_wait(s_empty + 8 * st, ((j >> 1) - 1) & 1));
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -276,13 +195,13 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
     auto pair_sync = [&]() -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(pair_bar + 8 * quarter);
-      const bool done = p100_wait(pair_bar + 8 * quarter, pair_phase);
+      const bool done = tc_wait(pair_bar + 8 * quarter, pair_phase);
       pair_phase ^= 1;
       return done;
     };
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1, kv0 = j * kP100Bc;
-      if (!p100_wait(s_full + 8 * st, (j >> 1) & 1)) { ok = false; break; }
+      if (!tc_wait(s_full + 8 * st, (j >> 1) & 1)) { ok = false; break; }
       tc_fence_after();
       const bool need_mask = (kv0 + kP100Bc > a.S) || (a.causal && kv0 + kP100Bc - 1 > q0);
       // this thread's half of the S row in one TMEM round trip
@@ -321,7 +240,7 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       m_run = m_new;
       // O is rescaled only when a row maximum of this warp moved, and only after the previous P V is done
       if (j >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        if (!p100_wait(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1)) { ok = false; break; }
+        if (!tc_wait(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < OC / 32; ++c) {
@@ -335,7 +254,7 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
         tc_wait_st();
       }
       // this P buffer was read by the P V of two tiles ago
-      if (j >= 2 && !p100_wait(pv_done + 8 * st, ((j >> 1) - 1) & 1)) { ok = false; break; }
+      if (j >= 2 && !tc_wait(pv_done + 8 * st, ((j >> 1) - 1) & 1)) { ok = false; break; }
       // P = 2^(s - m), row sum, P (16-bit) into the swizzled K-major operand buffer (64-token chunk `half`)
       float ps4[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_m = -m_new;
@@ -373,7 +292,7 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       xchg[((n_tiles & 1) * 2 + half) * 128 + row] = l_run;  // the parity slot the last tile did not use
       ok = pair_sync();
     }
-    if (ok && !p100_wait(pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1)) ok = false;
+    if (ok && !tc_wait(pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1)) ok = false;
     if (!ok) {
       if (lane == 0) give_up();
     } else {

@@ -60,6 +60,13 @@ extern "C" {
                                         thousand polls instead of seconds.  The waits run out, all warps
                                         return, CUDA_LLM_ST_TIMEOUT (and CUDA_LLM_ST_INCOMPLETE for the rows
                                         left without a result) is set; nothing faults or hangs.          */
+#define CUDA_LLM_FLAG_TCGEN05 4096 /* run the call on the tcgen05 / tensor-memory decode kernel where it
+                                    * applies (head_dim 128, pages of 16 tokens, E4M3 K and V with per-token
+                                    * fp32 or E8M0 block scales, 16-bit queries, no rotary embedding);
+                                    * other calls ignore the flag.  The environment variable
+                                    * CUDA_LLM_DECODE_KERNEL=tcgen05 sets it for every call of the process.
+                                    * Same results contract; measured slower than the default warp-MMA
+                                    * kernel on a B200, which is why it is opt-in. */
 
 #ifdef CUDA_LLM_DIAGNOSTICS /* honoured only by a library built with -DCUDA_LLM_DIAGNOSTICS */
 #define CUDA_LLM_FLAG_DIAG_NO_MATH 2 /* diagnostics: stream the pages but skip the attention math
@@ -273,6 +280,11 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
  * since the library was loaded on the current device (0 in a healthy process; a non-zero count means
  * some prefill outputs are invalid).  Synchronises the device. */
 int cuda_llm_prefill_wait_timeouts(uint32_t* count);
+
+/* No counterpart in the reference.  Calls of this process that ran on the tcgen05 decode kernel
+ * (CUDA_LLM_FLAG_TCGEN05), and bounded waits of that kernel that ran out on the current device (the
+ * second synchronises the device).  Either pointer may be NULL. */
+int cuda_llm_decode_tcgen05_counters(uint64_t* launches, uint32_t* wait_timeouts);
 
 /* Replaces dispatch_fused_microscaled_attention<T_OUT> (kernels_api.h:103-108; the reference declares
  * it and ships no definition, test or Python binding, so the semantics are fixed here): dense
