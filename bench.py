@@ -719,6 +719,8 @@ def main():
     value = tot_bytes / (ms_step * 1e-3) / 1e12
     achieved = kv_bytes / (ms_kernel * 1e-3) / 1e9
     name = meta["name"]
+    # CUDA_LLM_DECODE_KERNEL=tcgen05 (read by the library) moves the calls it serves onto the tensor-memory kernel
+    decode_kernel = "tcgen05" if os.environ.get("CUDA_LLM_DECODE_KERNEL") == "tcgen05" else "warp_mma"
     line = {
         "metric": "paged_fp8_decode_kv_hbm_throughput", "value": value, "unit": "TB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -740,9 +742,12 @@ def main():
                    "head_dim": meta["head_dim"], "page_size": meta["page_size"],
                    "kv_tokens_per_gpu": meta["kv_tokens"], "kv_bytes_per_gpu": kv_bytes,
                    "pool_pages": meta["pool_pages"], "parallelism": parallelism,
+                   "decode_kernel": decode_kernel,
                    "l2": "inputs larger than L2 (KV working set per step >> 126 MB), no flush needed"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_source": peak_src, "kernel": "paged_decode_kernel", "kernel_ms": ms_kernel,
+                     "peak_source": peak_src,
+                     "kernel": "paged_decode_sm100_kernel" if decode_kernel == "tcgen05" and name.startswith("cfg2") else "paged_decode_kernel",
+                     "kernel_ms": ms_kernel,
                      "traffic": None},
         "e2e": {"value": tot_bytes / (ms_e2e * 1e-3) / 1e12, "unit": "TB/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,

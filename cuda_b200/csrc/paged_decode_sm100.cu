@@ -18,13 +18,15 @@
 // multiplied block by block (four S accumulators, one per 32 head_dim values, combined in fp32 by the
 // thread); V needs P * 2^e_b(token), which differs per block, so there are four P variants and four O
 // accumulators, each with its own running maximum (w_b = s + e_b), and a thread reads the lane quarter
-// of "its" block at the end.  The running maxima are only raised when a tile exceeds them by 2^7
-// (P then stays below 2^7, inside E4M3), so the cross-lane maximum and the rescale of O in TMEM run
-// on the first tile of a segment and rarely afterwards.
+// of "its" block at the end.  The running maxima are only raised when a tile exceeds them by 2^2
+// (P = 2^(w - m + 6) then stays below 2^8, inside E4M3), so the cross-lane maximum and the rescale of
+// O in TMEM run on the first tile of a segment and rarely afterwards.  Both E4M3 B operands carry a
+// second term, 16 x the rounding residual, in accumulator columns of their own.
 //
-// Roles (320 threads): warps 0-3 and 4-7 are two softmax groups taking alternate tiles, each with its
+// Roles (352 threads): warps 0-3 and 4-7 are two softmax groups taking alternate tiles, each with its
 // own S / P / O buffers and its own partial result (the split merge combines them); warp 8 walks the
-// CTA's range and issues the bulk copies; warp 9 quantises the query rows and issues the MMAs.
+// CTA's range and issues the copies; warp 9 issues the MMAs; warp 10 quantises the query rows of the
+// coming (sequence, KV head) segments.
 #include "paged_decode_kernel.cuh"
 #include "tcgen05_primitives.cuh"
 
