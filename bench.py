@@ -38,7 +38,7 @@ if ROOT not in sys.path:
 
 WORKLOADS = {"cfg1": 1, "cfg2": 2, "cfg3": 3, "cfg4": 4, "cfg5": 5}
 # secondary lines for the unquantised entry points (same Llama-3-8B head shape, bf16 K/V)
-AUX_WORKLOADS = ("pa16", "fd16", "prefill", "mxattn")
+AUX_WORKLOADS = ("pa16", "pa32", "fd16", "prefill", "mxattn")
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode-kernel launch,
@@ -210,13 +210,15 @@ def aux_workload(args, rank, world, local):
                                            "traffic": None},
                               "gpu_launches": steps}), flush=True)
         return
-    if args.workload == "pa16":
+    if args.workload in ("pa16", "pa32"):  # paged_attention over a bf16 / an fp32 cache
+        cdt = torch.bfloat16 if args.workload == "pa16" else torch.float32
         ctx = torch.randint(int(1024 * args.ctx_scale), int(4096 * args.ctx_scale) + 1, (batch,), generator=g).tolist()
-        wl = workloads.build_workload("pa16_llama8b_bf16", context_lens=ctx, q_lens=None, num_q_heads=32,
-                                      num_kv_heads=8, head_dim=128, page_size=args.page_size, q_dtype=torch.bfloat16,
+        wl = workloads.build_workload("pa16_llama8b_bf16" if cdt == torch.bfloat16 else "pa32_llama8b_fp32",
+                                      context_lens=ctx, q_lens=None, num_q_heads=32,
+                                      num_kv_heads=8, head_dim=128, page_size=args.page_size, q_dtype=cdt,
                                       scale_mode="none", pool_factor=1.25, seed=2000 + rank,
-                                      cache_dtype=torch.bfloat16).to(dev)
-        kv_bytes = sum(ctx) * 8 * 128 * 2 * 2
+                                      cache_dtype=cdt).to(dev)
+        kv_bytes = sum(ctx) * 8 * 128 * 2 * (2 if cdt == torch.bfloat16 else 4)
         fn = lambda: ops.paged_attention_forward(wl.query, wl.key_cache, wl.value_cache, wl.block_tables,
                                                  wl.context_lens)
         cfg = {"workload": wl.name, "batch_per_gpu": batch, "kv_tokens_per_gpu": sum(ctx), "page_size": args.page_size}
@@ -243,12 +245,14 @@ def aux_workload(args, rank, world, local):
                 "l2": "inputs larger than L2, no flush needed"})
     if rank != 0:
         return
-    print(json.dumps({"metric": "bf16_decode_kv_hbm_throughput", "value": kv_bytes / (ms * 1e-3) / 1e12, "unit": "TB/s",
+    f32 = args.workload == "pa32"
+    print(json.dumps({"metric": ("fp32" if f32 else "bf16") + "_decode_kv_hbm_throughput", "value": kv_bytes / (ms * 1e-3) / 1e12, "unit": "TB/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-                      "higher_is_better": True, "dtype": "bf16 mma, f32 acc", "data": "synthetic", "config": cfg,
+                      "higher_is_better": True, "dtype": "f32 SIMT" if f32 else "bf16 mma, f32 acc", "data": "synthetic", "config": cfg,
                       "roofline": {"bound": "hbm", "achieved": kv_bytes / (ms * 1e-3) / 1e9, "peak": peak,
                                    "unit": "GB/s", "frac": kv_bytes / (ms * 1e-3) / 1e9 / peak,
-                                   "peak_source": peak_src, "kernel": "paged_decode_kernel + merge_splits_kernel"},
+                                   "peak_source": peak_src,
+                                   "kernel": "dense_decode_kernel + merge_partials_kernel" if f32 else "paged_decode_kernel + merge_splits_kernel"},
                       "gpu_launches": 2 * args.steps}), flush=True)
 
 

@@ -7,7 +7,11 @@
 // paged_decode_kernel); they are plain split-KV SIMT kernels: one warp per (sequence, KV head,
 // KV split) walks its token range 32 tokens at a time, lane = token for Q.K (no shuffles in the
 // dot product, the GQA group shares every K element), one warp-wide online-softmax update per
-// query row, lane = head_dim slice for P.V.  Partials are merged by merge_partials_kernel.
+// query row, lane = head_dim slice for P.V.  In the paged layout a V row of 16 tokens is 64 contiguous
+// bytes and consecutive head_dim rows are a page apart, so the warp first copies the [head_dim][16 tokens]
+// tile of a page into shared memory as [token][head_dim + 1] with coalesced loads and reads it back
+// conflict-free (reading V straight from global memory touched 32 sectors per load for 128 useful bytes).
+// Partials are merged by merge_partials_kernel.
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 
@@ -41,6 +45,7 @@ __global__ void __launch_bounds__(128) dense_decode_kernel(const DenseArgs a) {
   constexpr float NEG_INF = -__builtin_huge_valf();
   __shared__ float q_s[4][G][D];
   __shared__ float p_s[4][G][32];
+  extern __shared__ float v_tile[];  // paged: [4 warps][16 tokens][D + 1]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * 4 + warp;
   const long long n_items = (long long)a.S * a.Hkv * a.n_splits;
@@ -124,23 +129,45 @@ __global__ void __launch_bounds__(128) dense_decode_kernel(const DenseArgs a) {
     }
     __syncwarp();
     const int nvalid = min(32, t1 - tb);
-    for (int j = 0; j < nvalid; ++j) {
-      float vv[C];
-      if (PAGED) {
-        const long long bj = __shfl_sync(0xffffffffu, blk, j);
-        const size_t vbase = ((size_t)bj * a.Hkv + kvh) * D * a.page + (tb + j) % a.page;
+    if (PAGED) {
+      // 16 tokens at a time (they lie in one page: tb is a multiple of 32, pages hold 16, 32 or 64 tokens)
+      float* vt = v_tile + warp * 16 * (D + 1);
+      for (int half = 0; half < 2 && half * 16 < nvalid; ++half) {
+        const long long bj = __shfl_sync(0xffffffffu, blk, half * 16);
+        const size_t vbase = ((size_t)bj * a.Hkv + kvh) * D * a.page + (tb + half * 16) % a.page;
+        const int t = lane & 15, dd = lane >> 4;
+#pragma unroll 8
+        for (int i = 0; i < D / 2; ++i) {
+          const int d = 2 * i + dd;
+          vt[t * (D + 1) + d] = elem_to_float(V[vbase + (size_t)d * a.page + t]);
+        }
+        __syncwarp();
+        const int nt = min(16, nvalid - half * 16);
+        for (int j = 0; j < nt; ++j) {
+          float vv[C];
 #pragma unroll
-        for (int c = 0; c < C; ++c) vv[c] = elem_to_float(V[vbase + (size_t)(lane + 32 * c) * a.page]);
-      } else {
+          for (int c = 0; c < C; ++c) vv[c] = vt[j * (D + 1) + lane + 32 * c];
+#pragma unroll
+          for (int r = 0; r < G; ++r) {
+            const float p = p_s[warp][r][half * 16 + j];
+#pragma unroll
+            for (int c = 0; c < C; ++c) acc[r][c] = fmaf(p, vv[c], acc[r][c]);
+          }
+        }
+        __syncwarp();
+      }
+    } else {
+      for (int j = 0; j < nvalid; ++j) {
+        float vv[C];
         const size_t vbase = (((size_t)s * a.Hkv + kvh) * a.seq_len + tb + j) * D;
 #pragma unroll
         for (int c = 0; c < C; ++c) vv[c] = elem_to_float(V[vbase + lane + 32 * c]);
-      }
 #pragma unroll
-      for (int r = 0; r < G; ++r) {
-        const float p = p_s[warp][r][j];
+        for (int r = 0; r < G; ++r) {
+          const float p = p_s[warp][r][j];
 #pragma unroll
-        for (int c = 0; c < C; ++c) acc[r][c] = fmaf(p, vv[c], acc[r][c]);
+          for (int c = 0; c < C; ++c) acc[r][c] = fmaf(p, vv[c], acc[r][c]);
+        }
       }
     }
     __syncwarp();
@@ -163,11 +190,19 @@ static cudaError_t launch_dense_g(const DenseArgs& a, cudaStream_t st) {
   const long long n_items = (long long)a.S * a.Hkv * a.n_splits;
   if (n_items == 0) return cudaSuccess;
   const int grid = (int)((n_items + 3) / 4);
-  if (a.group <= 1) dense_decode_kernel<T, D, 1, PAGED><<<grid, 128, 0, st>>>(a);
-  else if (a.group <= 2) dense_decode_kernel<T, D, 2, PAGED><<<grid, 128, 0, st>>>(a);
-  else if (a.group <= 4) dense_decode_kernel<T, D, 4, PAGED><<<grid, 128, 0, st>>>(a);
-  else dense_decode_kernel<T, D, 8, PAGED><<<grid, 128, 0, st>>>(a);
-  return cudaGetLastError();
+  const size_t dyn = PAGED ? (size_t)4 * 16 * (D + 1) * sizeof(float) : 0;  // the V tile of every warp
+  auto go = [&](auto kern) -> cudaError_t {
+    if (dyn + 4 * 8 * D * sizeof(float) + 4096 > 48 * 1024) {  // static + dynamic beyond the default limit
+      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+      if (e != cudaSuccess) return e;
+    }
+    kern<<<grid, 128, dyn, st>>>(a);
+    return cudaGetLastError();
+  };
+  if (a.group <= 1) return go(dense_decode_kernel<T, D, 1, PAGED>);
+  if (a.group <= 2) return go(dense_decode_kernel<T, D, 2, PAGED>);
+  if (a.group <= 4) return go(dense_decode_kernel<T, D, 4, PAGED>);
+  return go(dense_decode_kernel<T, D, 8, PAGED>);
 }
 template <int D, bool PAGED>
 static cudaError_t launch_dense_t(const DenseArgs& a, int dtype, cudaStream_t st) {
