@@ -58,6 +58,39 @@ __device__ __forceinline__ float exp2_poly(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
 }
 
+// Packed fp32 arithmetic of sm_100 (two lanes per instruction) and the three-input maximum: the softmax
+// warps are bound by the number of instructions they issue per tile, and these halve the scale / subtract,
+// the row sum, the polynomial and the row maximum.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.ftz.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.ftz.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.ftz.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// exp2_poly on two values at once
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  float r0, r1, t0, t1, f0, f1;
+  fadd2(r0, r1, x0, x1, 12582912.f, 12582912.f);
+  fadd2(t0, t1, r0, r1, -12582912.f, -12582912.f);
+  ffma2(f0, f1, t0, t1, -1.f, -1.f, x0, x1);
+  ffma2(p0, p1, f0, f1, 0.05508868396282196f, 0.05508868396282196f, 0.24260404706001282f, 0.24260404706001282f);
+  ffma2(p0, p1, f0, f1, p0, p1, 0.6932762265205383f, 0.6932762265205383f);
+  ffma2(p0, p1, f0, f1, p0, p1, 0.9999289512634277f, 0.9999289512634277f);
+  p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23));
+  p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
+}
+
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
                                             uint32_t bar) {
   asm volatile(
@@ -230,12 +263,17 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sr[c][i]));
-      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        for (int i = 0; i < 32; i += 2)
+          mx8[(i >> 1) & 7] = fmax3(mx8[(i >> 1) & 7], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+      float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       xchg[(st * 2 + half) * 128 + row] = mx;
       if (!pair_sync()) { ok = false; break; }
       mx = fmaxf(mx, xchg[(st * 2 + (half ^ 1)) * 128 + row]);
-      const float m_new = fmaxf(m_run, mx * a.scale_log2);
+      // The reference maximum of a row only moves when the tile exceeds it by more than 2^8: P = 2^(s - m)
+      // then stays below 256 (exact in 16 bits as far as its rounding goes, harmless in the fp32 sums), and O
+      // in tensor memory is rescaled in the first tile or two of a row instead of whenever a maximum creeps up.
+      const float m_tile = mx * a.scale_log2;
+      const float m_new = (m_tile > m_run + 8.f) ? m_tile : m_run;
       const float alpha = fast_exp2(m_run - m_new);
       m_run = m_new;
       // O is rescaled only when a row maximum of this warp moved, and only after the previous P V is done
@@ -256,19 +294,24 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       // this P buffer was read by the P V of two tiles ago
       if (j >= 2 && !tc_wait(pv_done + 8 * st, ((j >> 1) - 1) & 1)) { ok = false; break; }
       // P = 2^(s - m), row sum, P (16-bit) into the swizzled K-major operand buffer (64-token chunk `half`)
-      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      float ps8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // four packed accumulators
       const float neg_m = -m_new;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          // every fourth exponential on the FMA pipe, the others on the special-function unit
-          const float x0 = fmaf(__uint_as_float(sr[c][i]), a.scale_log2, neg_m);
-          const float x1 = fmaf(__uint_as_float(sr[c][i + 1]), a.scale_log2, neg_m);
-          const float p0 = fast_exp2(x0);
-          const float p1 = ((i & 2) != 0) ? exp2_poly(x1) : fast_exp2(x1);
-          ps4[(i >> 1) & 3] += p0 + p1;
+          // every fourth pair of exponentials on the FMA pipe (packed), the others on the special-function unit
+          float x0, x1, p0, p1;
+          ffma2(x0, x1, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]), a.scale_log2, a.scale_log2, neg_m, neg_m);
+          if ((i & 6) == 6) {
+            exp2_poly2(x0, x1, p0, p1);
+          } else {
+            p0 = fast_exp2(x0);
+            p1 = fast_exp2(x1);
+          }
+          const int k = (i >> 1) & 3;
+          fadd2(ps8[2 * k], ps8[2 * k + 1], ps8[2 * k], ps8[2 * k + 1], p0, p1);
           pk[i >> 1] = a.bf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
         // columns 32c .. 32c+31 of this half row: four 16-byte units of the 128-byte line
@@ -280,7 +323,7 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
                        "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3]) : "memory");
         }
       }
-      l_run = l_run * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
+      l_run = l_run * alpha + (((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7])));
       // P written (made visible to the async proxy) and O rescaled: the P V of this tile may go
       tc_fence_before();
       fence_async_smem();
