@@ -181,15 +181,23 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       const uint32_t idesc_s = instr_desc_f16(a.bf16, 0, 128, kP100Bc);
       const uint32_t idesc_o = instr_desc_f16(a.bf16, 1, 128, D);
       bool ok = tc_wait(q_full, 0);
+      // descriptor halves: the high word is a constant of the layout, the low word steps by (bytes >> 4)
+      const uint32_t hi_k = smem_desc_hi_sw128(1024);                       // K-major operands and V alike
+      const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo = smem_desc_lo(sK, 16), p_lo = smem_desc_lo(sP, 16);
+      const uint32_t v_lo = smem_desc_lo(sV, QCH);
       auto issue_pv = [&](int j) -> bool {  // O (+)= P_j V_j
         const int st = j & 1;
         if (!tc_wait(p_full + 8 * st, (j >> 1) & 1) || !tc_wait(v_full + 8 * st, (j >> 1) & 1)) return false;
         tc_fence_after();
+        const uint32_t pl = p_lo + st * (P_BYTES >> 4), vl = v_lo + st * (KV_BYTES >> 4);
+        if (j > 0) {
 #pragma unroll
-        for (int kk = 0; kk < kP100Bc / 16; ++kk) {
-          const uint64_t ad = smem_desc_sw128(sP + st * P_BYTES + (kk >> 2) * QCH + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = smem_desc_sw128(sV + st * KV_BYTES + kk * 2048, QCH, 1024);
-          umma_f16(tmem + 256, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kP100Bc / 16; ++kk)
+            umma_f16_parts(tmem + 256, pl + (((kk >> 2) * QCH + (kk & 3) * 32) >> 4), hi_k, vl + ((kk * 2048) >> 4), hi_k, idesc_o, 1u);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < kP100Bc / 16; ++kk)
+            umma_f16_parts(tmem + 256, pl + (((kk >> 2) * QCH + (kk & 3) * 32) >> 4), hi_k, vl + ((kk * 2048) >> 4), hi_k, idesc_o, kk > 0 ? 1u : 0u);
         }
         umma_commit(pv_done + 8 * st);   // this P buffer free, O updated
         umma_commit(v_empty + 8 * st);   // V stage free
@@ -200,11 +208,11 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
         ok = tc_wait(k_full + 8 * st, (j >> 1) & 1) && (j < 2 || tc_wait(s_empty + 8 * st, ((j >> 1) - 1) & 1));
         if (!ok) break;
         tc_fence_after();
+        const uint32_t kl = k_lo + st * (KV_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t ad = smem_desc_sw128(sQ + (kk >> 2) * QCH + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = smem_desc_sw128(sK + st * KV_BYTES + (kk >> 2) * QCH + (kk & 3) * 32, 16, 1024);
-          umma_f16(tmem + st * 128, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t off = ((kk >> 2) * QCH + (kk & 3) * 32) >> 4;
+          umma_f16_parts(tmem + st * 128, q_lo + off, hi_k, kl + off, hi_k, idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(s_full + 8 * st);
         umma_commit(k_empty + 8 * st);   // K stage free once S is done
