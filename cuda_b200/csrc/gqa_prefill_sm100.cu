@@ -183,21 +183,22 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       bool ok = tc_wait(q_full, 0);
       // descriptor halves: the high word is a constant of the layout, the low word steps by (bytes >> 4)
       const uint32_t hi_k = smem_desc_hi_sw128(1024);                       // K-major operands and V alike
-      const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo = smem_desc_lo(sK, 16), p_lo = smem_desc_lo(sP, 16);
+      const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo = smem_desc_lo(sK, 16);
       const uint32_t v_lo = smem_desc_lo(sV, QCH);
       auto issue_pv = [&](int j) -> bool {  // O (+)= P_j V_j
         const int st = j & 1;
         if (!tc_wait(p_full + 8 * st, (j >> 1) & 1) || !tc_wait(v_full + 8 * st, (j >> 1) & 1)) return false;
         tc_fence_after();
-        const uint32_t pl = p_lo + st * (P_BYTES >> 4), vl = v_lo + st * (KV_BYTES >> 4);
+        // P comes from tensor memory: 16 tokens of a row are 8 columns
+        const uint32_t pa = tmem + 384 + st * 64, vl = v_lo + st * (KV_BYTES >> 4);
         if (j > 0) {
 #pragma unroll
           for (int kk = 0; kk < kP100Bc / 16; ++kk)
-            umma_f16_parts(tmem + 256, pl + (((kk >> 2) * QCH + (kk & 3) * 32) >> 4), hi_k, vl + ((kk * 2048) >> 4), hi_k, idesc_o, 1u);
+            umma_f16_ts_parts(tmem + 256, pa + kk * 8, vl + ((kk * 2048) >> 4), hi_k, idesc_o, 1u);
         } else {
 #pragma unroll
           for (int kk = 0; kk < kP100Bc / 16; ++kk)
-            umma_f16_parts(tmem + 256, pl + (((kk >> 2) * QCH + (kk & 3) * 32) >> 4), hi_k, vl + ((kk * 2048) >> 4), hi_k, idesc_o, kk > 0 ? 1u : 0u);
+            umma_f16_ts_parts(tmem + 256, pa + kk * 8, vl + ((kk * 2048) >> 4), hi_k, idesc_o, kk > 0 ? 1u : 0u);
         }
         umma_commit(pv_done + 8 * st);   // this P buffer free, O updated
         umma_commit(v_empty + 8 * st);   // V stage free
@@ -322,19 +323,13 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
           fadd2(ps8[2 * k], ps8[2 * k + 1], ps8[2 * k], ps8[2 * k + 1], p0, p1);
           pk[i >> 1] = a.bf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
-        // columns 32c .. 32c+31 of this half row: four 16-byte units of the 128-byte line
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int unit = c * 4 + u;
-          const uint32_t addr = sP + st * P_BYTES + half * QCH + row * 128 + ((unit ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * u]), "r"(pk[4 * u + 1]),
-                       "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3]) : "memory");
-        }
+        // 32 tokens of this half row = 16 columns of the P buffer in tensor memory
+        tmem_st16(tmem + lane_base + 384 + st * 64 + half * 32 + c * 16, pk);
       }
+      tc_wait_st();
       l_run = l_run * alpha + (((ps8[0] + ps8[1]) + (ps8[2] + ps8[3])) + ((ps8[4] + ps8[5]) + (ps8[6] + ps8[7])));
-      // P written (made visible to the async proxy) and O rescaled: the P V of this tile may go
+      // P written and O rescaled: the P V of this tile may go
       tc_fence_before();
-      fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + 8 * st);
     }
