@@ -104,15 +104,16 @@ __global__ void __launch_bounds__(kP100Threads, 1)
 gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_constant__ PrefillMaps maps) {
   constexpr int NCH = D / 64;                 // 64-element (128-byte) chunks of head_dim
   constexpr uint32_t QCH = 128 * 128;         // bytes of one [128 rows x 64 elements] swizzled block
-  constexpr uint32_t Q_BYTES = NCH * QCH, KV_BYTES = NCH * QCH, P_BYTES = 2 * QCH;
+  constexpr uint32_t Q_BYTES = NCH * QCH, KV_BYTES = NCH * QCH;
+  constexpr int NKV = 3;                      // K and V tiles in flight each (P lives in tensor memory)
   constexpr float NEG_INF = -__builtin_huge_valf();
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);
-  const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + 2 * KV_BYTES, sP = sV + 2 * KV_BYTES;
-  const uint32_t bars = sP + 2 * P_BYTES;  // 8-byte mbarriers (P is double-buffered)
-  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, k_empty = bars + 40, s_full = bars + 56,
-                 s_empty = bars + 72, p_full = bars + 88, pv_done = bars + 104, v_empty = bars + 120,
-                 pair_bar = bars + 136, tmem_slot = bars + 168;
+  const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + NKV * KV_BYTES;
+  const uint32_t bars = sV + NKV * KV_BYTES;  // 8-byte mbarriers
+  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 32, k_empty = bars + 56, v_empty = bars + 80,
+                 s_full = bars + 104, s_empty = bars + 120, p_full = bars + 136, pv_done = bars + 152,
+                 pair_bar = bars + 168, tmem_slot = bars + 200;
   // row maxima (per tile parity, per column half) and final row sums exchanged between the two threads of a row
   float* xchg = reinterpret_cast<float*>(smem + (bars - base) + 256);  // [2 parities][2 halves][128 rows]
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base));
@@ -130,11 +131,13 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
 
   if (tid == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NKV; ++i) {
       mbar_init(k_full + 8 * i, 1);
       mbar_init(v_full + 8 * i, 1);
       mbar_init(k_empty + 8 * i, 1);
       mbar_init(v_empty + 8 * i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(s_full + 8 * i, 1);
       mbar_init(s_empty + 8 * i, 8);   // one arrival per softmax warp
       mbar_init(p_full + 8 * i, 8);
@@ -164,15 +167,20 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       for (int i = 0; i < a.gsz; ++i)
         for (int c = 0; c < NCH; ++c)
           tma_load_3d(sQ + c * QCH + i * BQ * 128, &maps.q, c * 64, q0, b * a.Hq + kvh * a.group + chunk * a.gsz + i, q_full);
+      int st = 0;           // ring slot of tile j and the parity of its use: j % NKV, (j / NKV) & 1
+      uint32_t par = 0;
       for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1;
-        // the K slot is free as soon as S of two tiles ago is done, the V slot only after its P V
-        if (j >= 2 && !tc_wait(k_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
+        // the K slot is free as soon as the S that read it is done, the V slot only after its P V
+        if (j >= NKV && !tc_wait(k_empty + 8 * st, par ^ 1)) { give_up(); break; }
         mbar_arrive_expect_tx(k_full + 8 * st, KV_BYTES);
         for (int c = 0; c < NCH; ++c) tma_load_3d(sK + st * KV_BYTES + c * QCH, &maps.k, c * 64, j * kP100Bc, b * a.Hkv + kvh, k_full + 8 * st);
-        if (j >= 2 && !tc_wait(v_empty + 8 * st, ((j >> 1) - 1) & 1)) { give_up(); break; }
+        if (j >= NKV && !tc_wait(v_empty + 8 * st, par ^ 1)) { give_up(); break; }
         mbar_arrive_expect_tx(v_full + 8 * st, KV_BYTES);
         for (int c = 0; c < NCH; ++c) tma_load_3d(sV + st * KV_BYTES + c * QCH, &maps.v, c * 64, j * kP100Bc, b * a.Hkv + kvh, v_full + 8 * st);
+        if (++st == NKV) {
+          st = 0;
+          par ^= 1;
+        }
       }
     }
   } else if (warp == 9) {
@@ -185,12 +193,14 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       const uint32_t hi_k = smem_desc_hi_sw128(1024);                       // K-major operands and V alike
       const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo = smem_desc_lo(sK, 16);
       const uint32_t v_lo = smem_desc_lo(sV, QCH);
+      int vst = 0;          // V ring slot of the next P V and the parity of its use
+      uint32_t vpar = 0;
       auto issue_pv = [&](int j) -> bool {  // O (+)= P_j V_j
         const int st = j & 1;
-        if (!tc_wait(p_full + 8 * st, (j >> 1) & 1) || !tc_wait(v_full + 8 * st, (j >> 1) & 1)) return false;
+        if (!tc_wait(p_full + 8 * st, (j >> 1) & 1) || !tc_wait(v_full + 8 * vst, vpar)) return false;
         tc_fence_after();
         // P comes from tensor memory: 16 tokens of a row are 8 columns
-        const uint32_t pa = tmem + 384 + st * 64, vl = v_lo + st * (KV_BYTES >> 4);
+        const uint32_t pa = tmem + 384 + st * 64, vl = v_lo + vst * (KV_BYTES >> 4);
         if (j > 0) {
 #pragma unroll
           for (int kk = 0; kk < kP100Bc / 16; ++kk)
@@ -201,22 +211,32 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
             umma_f16_ts_parts(tmem + 256, pa + kk * 8, vl + ((kk * 2048) >> 4), hi_k, idesc_o, kk > 0 ? 1u : 0u);
         }
         umma_commit(pv_done + 8 * st);   // this P buffer free, O updated
-        umma_commit(v_empty + 8 * st);   // V stage free
+        umma_commit(v_empty + 8 * vst);  // V stage free
+        if (++vst == NKV) {
+          vst = 0;
+          vpar ^= 1;
+        }
         return true;
       };
+      int kst = 0;          // K ring slot of the next S
+      uint32_t kpar = 0;
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int st = j & 1;
-        ok = tc_wait(k_full + 8 * st, (j >> 1) & 1) && (j < 2 || tc_wait(s_empty + 8 * st, ((j >> 1) - 1) & 1));
+        ok = tc_wait(k_full + 8 * kst, kpar) && (j < 2 || tc_wait(s_empty + 8 * st, ((j >> 1) - 1) & 1));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t kl = k_lo + st * (KV_BYTES >> 4);
+        const uint32_t kl = k_lo + kst * (KV_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk >> 2) * QCH + (kk & 3) * 32) >> 4;
           umma_f16_parts(tmem + st * 128, q_lo + off, hi_k, kl + off, hi_k, idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(s_full + 8 * st);
-        umma_commit(k_empty + 8 * st);   // K stage free once S is done
+        umma_commit(k_empty + 8 * kst);  // K stage free once S is done
+        if (++kst == NKV) {
+          kst = 0;
+          kpar ^= 1;
+        }
         if (j >= 1) ok = issue_pv(j - 1);
       }
       if (ok) ok = issue_pv(n_tiles - 1);
@@ -415,7 +435,7 @@ cudaError_t run_gqa_prefill_sm100(const void* q, const void* k, const void* v, v
       !encode_bhsd(enc, &maps.v, v, (long long)B * Hkv, S, D, kP100Bc))
     return cudaErrorInvalidValue;
   const int nch = D / 64;
-  size_t smem = (size_t)nch * 16384 * 5 + 4 * 16384 + 256 + 512 * 4;  // Q, 2 x K, 2 x V, 2 x P, barriers, exchange
+  size_t smem = (size_t)nch * 16384 * 7 + 256 + 512 * 4;  // Q, 3 x K, 3 x V, barriers, exchange
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: a CTA allocates all 512 TMEM columns
   auto kern = D == 64 ? gqa_prefill_sm100_kernel<64> : gqa_prefill_sm100_kernel<128>;
   static int configured[2][64] = {{0}};
