@@ -218,26 +218,26 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
   return CUDA_LLM_OK;
 }
 
-// Work layout of the tcgen05 decode kernel (paged_decode_sm100.cu): one KV head per unit, tiles of 128
-// tokens, two results (one per softmax group) of `rows_max` rows per (CTA, sequence, KV head).
+// Work layout of the tcgen05 decode kernel (paged_decode_sm100.cu): two adjacent KV heads per unit, tiles of
+// 128 tokens, one result of `rows_max` rows per (CTA, sequence, KV head).
 static int make_layout_sm100(int S, int Hq, int Hkv, int D, int page, int max_q_len, int v_format, int scale_mode,
                              int num_ctas, Layout& L) {
-  if (S < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D != 128 || page != 16) return CUDA_LLM_EINVAL;
+  if (S < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || Hkv % 2 || D != 128 || page != 16) return CUDA_LLM_EINVAL;
   const int group = Hq / Hkv;
   if (max_q_len < 1) max_q_len = 1;
   if (group * max_q_len > 16) return CUDA_LLM_EINVAL;
   memset(&L, 0, sizeof(L));
   L.NT = (group * max_q_len <= 8) ? 1 : 2;
   L.rows_max = 8 * L.NT;
-  L.HG = 1;
-  L.SUBS = 2;
+  L.HG = 2;
+  L.SUBS = 1;
   L.tok_stage = 128;
-  L.n_hg = Hkv;
+  L.n_hg = Hkv / 2;
   L.PPS = 128 / page;
   const int DV = (v_format == CUDA_LLM_KV_FP4_E2M1) ? D / 2 : D;
-  L.k_chunk = (uint32_t)D * page;
-  L.v_chunk = (uint32_t)DV * page;
-  L.ks_chunk = L.vs_chunk = (scale_mode == CUDA_LLM_SCALE_PER_TOKEN) ? (uint32_t)page * 4 : (uint32_t)(D / 32) * page;
+  L.k_chunk = 2u * D * page;   // both heads of a pair are contiguous in a page
+  L.v_chunk = 2u * DV * page;
+  L.ks_chunk = L.vs_chunk = 2u * ((scale_mode == CUDA_LLM_SCALE_PER_TOKEN) ? (uint32_t)page * 4 : (uint32_t)(D / 32) * page);
   if (num_ctas <= 0) num_ctas = sm_count_cached();
   if (num_ctas <= 0) return fail(CUDA_LLM_ECUDA, "cannot query the SM count");
   L.grid = num_ctas;
@@ -254,12 +254,12 @@ cudaError_t launch_paged_decode_sm100(const DecodeArgs& a, int mode, int rp, int
 unsigned int decode100_wait_timeouts();
 static std::atomic<uint64_t> g_sm100_launches{0};
 
-// The tcgen05 kernel serves head_dim 128, pages of 16 tokens, E4M3 K and V with per-token fp32 or E8M0
-// block scales and 16-bit queries, when the call (CUDA_LLM_FLAG_TCGEN05) or the process
+// The tcgen05 kernel serves head_dim 128, an even number of KV heads, pages of 16 tokens, E4M3 K and V with
+// per-token fp32 or E8M0 block scales and 16-bit queries, when the call (CUDA_LLM_FLAG_TCGEN05) or the process
 // (CUDA_LLM_DECODE_KERNEL=tcgen05) asks for it.
 static bool decode_sm100_wanted(const CudaLlmPagedDecodeParams* p) {
   const bool kv16 = (p->k_format == CUDA_LLM_KV_F16 || p->k_format == CUDA_LLM_KV_BF16);
-  if (kv16 || p->head_dim != 128 || p->page_size != 16) return false;
+  if (kv16 || p->head_dim != 128 || p->page_size != 16 || (p->num_kv_heads & 1)) return false;
   if (p->k_format != CUDA_LLM_KV_FP8_E4M3 || p->v_format != CUDA_LLM_KV_FP8_E4M3) return false;
   if (p->scale_mode != CUDA_LLM_SCALE_PER_TOKEN && p->scale_mode != CUDA_LLM_SCALE_MX_E8M0) return false;
   if (p->q_dtype == CUDA_LLM_F32 || p->rope_cos || p->rope_sin) return false;

@@ -23,10 +23,12 @@
 // O in TMEM run on the first tile of a segment and rarely afterwards.  Both E4M3 B operands carry a
 // second term, 16 x the rounding residual, in accumulator columns of their own.
 //
-// Roles (352 threads): warps 0-3 and 4-7 are two softmax groups taking alternate tiles, each with its
-// own S / P / O buffers and its own partial result (the split merge combines them); warp 8 walks the
-// CTA's range and issues the copies; warp 9 issues the MMAs; warp 10 quantises the query rows of the
-// coming (sequence, KV head) segments.
+// A work unit is a 128-token tile of TWO adjacent KV heads (their slabs are contiguous in a page, so one
+// 4 KB bulk copy per page and tensor brings both: the copy engine takes a request every ~80 cycles
+// whatever its size, and 2 KB requests could not keep up with HBM).  Roles (352 threads): warps 0-3 and
+// 4-7 are two softmax groups, one per head of the pair, each with its own S / P / O buffers; warp 8
+// walks the CTA's range and issues the copies; warp 9 issues the MMAs; warp 10 quantises the query
+// rows of the coming (sequence, head pair) segments.
 #include "paged_decode_kernel.cuh"
 #include "tcgen05_primitives.cuh"
 
@@ -52,7 +54,7 @@ struct D100Cfg {
   static constexpr int NVW = MX ? 5 : 1;       // running-maximum sets (the last one, MX only, is the denominator's)
   static constexpr int NH = (RP == 16) ? 2 : 1;  // B operands per product: [high | residual] in one (8 rows) or two (16 rows)
   static constexpr int CS = 2 * RP;              // accumulator columns per S block / O variant: [high rows | residual rows]
-  // tensor memory, per group 256 columns: S blocks from 0, O variants from 128
+  // tensor memory, per group (= head of the pair) 256 columns: S blocks from 0, O variants from 128
   // shared memory (bytes from the 1024-aligned base)
   static constexpr uint32_t kBarFull = 0, kBarEmpty = 64, kBarSFull = 128, kBarSFree = 144, kBarPFull = 160,
                             kBarPvDone = 176, kBarQReady = 192, kBarQFree = 208, kTmemSlot = 224, kDone = 228, kPlan = 232;
@@ -60,15 +62,16 @@ struct D100Cfg {
   static constexpr uint32_t kGrpBytes = 2304;
   // group scratch: maxima [5][16] f32 @0, factors [5][16] @320, reduction [4][5][16] @640, sums [4][16] @1920,
   // flags [4] @2176, "a wait of this group ran out" @2192
-  static constexpr uint32_t kQs = kGrp + 2 * kGrpBytes;      // per query buffer: 16 row factors
-  static constexpr uint32_t kQbuf = (kQs + 2 * 64 + 127) / 128 * 128;
-  static constexpr uint32_t kQbufBytes = NH * 2048;
+  static constexpr uint32_t kQs = kGrp + 2 * kGrpBytes;      // per query buffer and head: 16 row factors
+  static constexpr uint32_t kQbuf = (kQs + 2 * 2 * 64 + 127) / 128 * 128;
+  static constexpr uint32_t kQHead = NH * 2048;              // one head's operand
+  static constexpr uint32_t kQbufBytes = 2 * kQHead;         // one buffer: both heads
   static constexpr uint32_t kP = kQbuf + 2 * kQbufBytes;
   static constexpr uint32_t kPBytes = NV * NH * 2048;        // per group
   static constexpr uint32_t kStages = (kP + 2 * kPBytes + 1023) / 1024 * 1024;
-  // stage: 8 page slabs of K, 8 of V, 8 x 64 bytes of K scales, 8 x 64 bytes of V scales
-  static constexpr uint32_t kOffV = 8 * 2048, kOffKs = kOffV + 8 * 2048, kOffVs = kOffKs + 8 * 64;
-  static constexpr uint32_t kStageBytes = kOffVs + 8 * 64;
+  // stage: 8 pages x 2 heads of K slabs, the same of V, 8 x 128 bytes of K scales, 8 x 128 bytes of V scales
+  static constexpr uint32_t kPageK = 4096, kOffV = 8 * kPageK, kOffKs = 2 * kOffV, kOffVs = kOffKs + 8 * 128;
+  static constexpr uint32_t kStageBytes = kOffVs + 8 * 128;
   static constexpr int kStagesMax = (int)((kSmemBudget - kStages) / kStageBytes) < kMaxStages
                                         ? (int)((kSmemBudget - kStages) / kStageBytes) : kMaxStages;
 };
@@ -165,7 +168,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
   asm volatile("griddepcontrol.launch_dependents;");
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
-      mbar_init(full_bar + 8 * i, 33);  // the byte count's arrival + one per producer lane (scale copies)
+      mbar_init(full_bar + 8 * i, 9);   // the byte count's arrival + one per page lane of the producer (scale copies)
       mbar_init(empty_bar + 8 * i, 1);
     }
     for (int g = 0; g < 2; ++g) {
@@ -186,7 +189,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
   }
 
   // ---------------------------------------------------------------- plan: equal unit ranges
-  // (the arithmetic of paged_decode_kernel with one KV head per unit and tiles of 128 tokens)
+  // (the arithmetic of paged_decode_kernel with two KV heads per unit and tiles of 128 tokens)
   const int per = (a.S + kD100Threads - 1) / kD100Threads;
   const int s_lo = min(a.S, tid * per), s_hi = min(a.S, s_lo + per);
   auto seq_cost = [&](int s) -> long long {
@@ -236,7 +239,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
   __syncthreads();
   const bool has_work = u_begin < u_end;
 
-  // the (sequence, KV head, tile) units of this CTA's range, walked by the producer, by the table
+  // the (sequence, head pair, tile) units of this CTA's range, walked by the producer, by the table
   // prefetch and by the query warp (each with its own cursor)
   auto load_seq = [&](UnitCursor& c) {
     c.ctx = eff_ctx(a, c.s, PAGE);
@@ -303,7 +306,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
     if (a.early_plan) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     int seg_cta_first = 0, seg_n_cta = 1, seg_idx = 0, seg_n = 1, seg_count = -1;
-    bool seg_fresh = true, ok = true;
+    bool seg_fresh = true, seg_direct = false, ok = true;
     int issued = 0, slot = 0;
     uint32_t phase = 0;
     for (int it = 0;; ++it, slot = (slot + 1 == NS) ? 0 : slot + 1, phase ^= (slot == 0) ? 1u : 0u) {
@@ -318,7 +321,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
           sts128(sb0 + kMetaOff + slot * (uint32_t)sizeof(StageMeta) + 16, FLAG_END, 0, 0, 0);
           mbar_arrive_expect_tx(fb, 0u);
         }
-        mbar_arrive(fb);
+        if (lane < 8) mbar_arrive(fb);
         break;
       }
       cp_async_wait<kBtAhead - 1>();
@@ -328,6 +331,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
         const long long seg_last = ic.seg_first + (long long)(ic.tiles - 1);
         seg_cta_first = (int)(ic.seg_first / per_cta);
         seg_n_cta = (int)(seg_last / per_cta) - seg_cta_first + 1;
+        seg_direct = seg_n_cta == 1;   // the whole (sequence, head pair) lies in this CTA's range: no merge needed
         seg_idx = 0;
         ++seg_count;
         seg_n = (int)min((long long)(ic.tiles - ic.tile), u_end - ic.pos);  // tiles of this segment in this CTA's range
@@ -345,7 +349,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
       const bool is_last = (seg_idx == seg_n - 1);
       const uint32_t meta = sb0 + kMetaOff + slot * (uint32_t)sizeof(StageMeta);
       if (lane == 0) {
-        const int flags = (is_new ? FLAG_NEW : 0) | (is_last ? FLAG_LAST : 0);
+        const int flags = (is_new ? FLAG_NEW : 0) | (is_last ? FLAG_LAST : 0) | (seg_direct ? FLAG_DIRECT : 0);
         sts128(meta, ic.s, ic.hg, tok0, ic.ctx);
         sts128(meta + 16, flags, ic.s * a.n_hg + ic.hg + vb, ic.qbase, ic.qlen);
         sts128(meta + 32, seg_idx, seg_n, seg_count, 0);
@@ -353,7 +357,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
           int32_t* t = a.table + 4 * (size_t)(ic.s * a.n_hg + ic.hg);
           t[0] = seg_cta_first;
           t[1] = seg_n_cta;
-          t[2] = 0;
+          t[2] = seg_direct ? 1 : 0;
         }
         mbar_arrive_expect_tx(fb, (uint32_t)np * (a.k_chunk + a.v_chunk));
       }
@@ -363,20 +367,23 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
       const bool stalled = a.stall_test && ic.pos == kSegGap;
       const uint32_t sb = sb0 + C::kStages + slot * C::kStageBytes;
       if (lane < np && !stalled) {
+        // both heads of the pair are contiguous in the page: one 4 KB copy per tensor
         const uint64_t b = (uint64_t)c_blk;
-        bulk_g2s_hint(sb + lane * 2048, a.kc + b * a.k_blk_stride + (uint64_t)ic.hg * a.k_chunk, a.k_chunk, fb, stream_policy);
-        bulk_g2s_hint(sb + C::kOffV + lane * 2048, a.vc + b * a.v_blk_stride + (uint64_t)ic.hg * a.v_chunk, a.v_chunk, fb,
+        bulk_g2s_hint(sb + lane * C::kPageK, a.kc + b * a.k_blk_stride + (uint64_t)ic.hg * a.k_chunk, a.k_chunk, fb, stream_policy);
+        bulk_g2s_hint(sb + C::kOffV + lane * C::kPageK, a.vc + b * a.v_blk_stride + (uint64_t)ic.hg * a.v_chunk, a.v_chunk, fb,
                       stream_policy);
       }
-      {
-        // the 64 scale bytes of a (page, head) go as four 16-byte cp.async (lane = page * 4 + chunk): the
-        // bulk-copy engine takes as long for 64 bytes as for 2 KB
-        const int pg = lane >> 2, ch = lane & 3;
-        const uint64_t b = (uint64_t)__shfl_sync(0xffffffffu, c_blk, pg);
-        if (pg < np) {
-          const uint64_t off = b * a.ks_blk_stride + (uint64_t)ic.hg * a.ks_chunk + ch * 16;
-          cp_async_16(sb + C::kOffKs + pg * 64 + ch * 16, a.ks + off);
-          cp_async_16(sb + C::kOffVs + pg * 64 + ch * 16, a.vs + off);
+      if (lane < 8) {
+        // the 128 scale bytes of a (page, head pair) go as 16-byte cp.async from the lane of the page (the
+        // bulk-copy engine takes as long for them as for 4 KB), then one arrival per lane that fires when
+        // they have landed
+        if (lane < np) {
+          const uint64_t off = (uint64_t)c_blk * a.ks_blk_stride + (uint64_t)ic.hg * a.ks_chunk;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            cp_async_16(sb + C::kOffKs + lane * 128 + ch * 16, a.ks + off + ch * 16);
+            cp_async_16(sb + C::kOffVs + lane * 128 + ch * 16, a.vs + off + ch * 16);
+          }
         }
         cp_async_arrive_noinc(fb);
       }
@@ -396,10 +403,10 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
     }
   } else if (has_work && warp == 10) {
     // =============================================================== query warp
-    // The query rows of every (sequence, KV head) of the range, up to two segments ahead of the MMAs:
-    // E4M3 high part and residual as a K-major operand, byte (row n, d) at (d / 16) * 256 + n * 16 + d % 16.
-    // Every row is scaled by a power of two that brings its largest magnitude into [128, 256); the factor
-    // goes back in with the softmax scale.
+    // The query rows of every (sequence, head pair) of the range, up to two segments ahead of the MMAs:
+    // per head, E4M3 high part and 16 x residual as a K-major operand, byte (row n, d) at
+    // (d / 16) * 256 + n * 16 + d % 16.  Every row is scaled by a power of two that brings its largest
+    // magnitude into [128, 256); the factor goes back in with the softmax scale.
     if (a.early_plan) asm volatile("griddepcontrol.wait;" ::: "memory");
     UnitCursor c;
     seat(c);
@@ -413,50 +420,54 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
           ok = false;
           break;
         }
-        const int kvh = c.hg, R = a.group * c.qlen;
-        const uint32_t qbuf = sb0 + C::kQbuf + qb * C::kQbufBytes;
-        float* qs = reinterpret_cast<float*>(smem + C::kQs + qb * 64);
-        uint2 raw[RP];
+        const int R = a.group * c.qlen;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          const int kvh = c.hg * 2 + h;
+          const uint32_t qbuf = sb0 + C::kQbuf + qb * C::kQbufBytes + h * C::kQHead;
+          float* qs = reinterpret_cast<float*>(smem + C::kQs + (qb * 2 + h) * 64);
+          uint2 raw[RP];
 #pragma unroll
-        for (int r = 0; r < RP; ++r) {
-          raw[r] = make_uint2(0u, 0u);
-          if (r < R) {
-            const int jq = r / a.group, iq = r - jq * a.group;
-            const size_t base = ((size_t)(c.qbase + jq) * a.Hq + (size_t)kvh * a.group + iq) * D + 4 * lane;
-            raw[r] = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(a.q) + base);
+          for (int r = 0; r < RP; ++r) {
+            raw[r] = make_uint2(0u, 0u);
+            if (r < R) {
+              const int jq = r / a.group, iq = r - jq * a.group;
+              const size_t base = ((size_t)(c.qbase + jq) * a.Hq + (size_t)kvh * a.group + iq) * D + 4 * lane;
+              raw[r] = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(a.q) + base);
+            }
           }
-        }
 #pragma unroll
-        for (int r = 0; r < RP; ++r) {
-          float x[4];
-          if (a.q_dtype == CUDA_LLM_F16) {
-            x[0] = f16x2_lo(raw[r].x); x[1] = f16x2_hi(raw[r].x); x[2] = f16x2_lo(raw[r].y); x[3] = f16x2_hi(raw[r].y);
-          } else {
-            x[0] = __uint_as_float(raw[r].x << 16); x[1] = __uint_as_float(raw[r].x & 0xffff0000u);
-            x[2] = __uint_as_float(raw[r].y << 16); x[3] = __uint_as_float(raw[r].y & 0xffff0000u);
+          for (int r = 0; r < RP; ++r) {
+            float x[4];
+            if (a.q_dtype == CUDA_LLM_F16) {
+              x[0] = f16x2_lo(raw[r].x); x[1] = f16x2_hi(raw[r].x); x[2] = f16x2_lo(raw[r].y); x[3] = f16x2_hi(raw[r].y);
+            } else {
+              x[0] = __uint_as_float(raw[r].x << 16); x[1] = __uint_as_float(raw[r].x & 0xffff0000u);
+              x[2] = __uint_as_float(raw[r].y << 16); x[3] = __uint_as_float(raw[r].y & 0xffff0000u);
+            }
+            float am = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            // 2^k with amax * 2^k in [128, 256): exponent field 127 + 7 - (field(amax) - 127)
+            int ef = (int)((__float_as_uint(am) >> 23) & 0xffu);
+            ef = min(max(ef, 16), 250);  // zero / tiny rows: a finite factor, the bytes come out as zeros anyway
+            const float up = __uint_as_float((uint32_t)(261 - ef) << 23);
+            const float dn = __uint_as_float((uint32_t)(ef - 7) << 23);
+            uint32_t top = 0, rest = 0;
+#pragma unroll
+            for (int pp = 0; pp < 2; ++pp) {
+              const float y0 = x[2 * pp] * up, y1 = x[2 * pp + 1] * up;
+              const uint32_t t = f32x2_to_e4m3x2(y0, y1);
+              const uint32_t t16 = e4m3x2_to_f16x2_lo(t);
+              const uint32_t rr = f32x2_to_e4m3x2((y0 - f16x2_lo(t16)) * kResScale, (y1 - f16x2_hi(t16)) * kResScale);
+              top |= t << (16 * pp);
+              rest |= rr << (16 * pp);
+            }
+            const uint32_t off = (uint32_t)(lane >> 2) * 256 + (lane & 3) * 4;
+            sts32(qbuf + off + r * 16, (int)top);
+            sts32(qbuf + (NH == 1 ? (8 + r) * 16 : 2048 + r * 16) + off, (int)rest);
+            if (lane == 0) qs[r] = a.scale_log2 * dn;
           }
-          float am = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-          // 2^k with amax * 2^k in [128, 256): exponent field 127 + 7 - (field(amax) - 127)
-          int ef = (int)((__float_as_uint(am) >> 23) & 0xffu);
-          ef = min(max(ef, 16), 250);  // zero / tiny rows: a finite factor, the bytes come out as zeros anyway
-          const float up = __uint_as_float((uint32_t)(261 - ef) << 23);
-          const float dn = __uint_as_float((uint32_t)(ef - 7) << 23);
-          uint32_t top = 0, rest = 0;
-#pragma unroll
-          for (int pp = 0; pp < 2; ++pp) {
-            const float y0 = x[2 * pp] * up, y1 = x[2 * pp + 1] * up;
-            const uint32_t t = f32x2_to_e4m3x2(y0, y1);
-            const uint32_t t16 = e4m3x2_to_f16x2_lo(t);
-            const uint32_t rr = f32x2_to_e4m3x2((y0 - f16x2_lo(t16)) * kResScale, (y1 - f16x2_hi(t16)) * kResScale);
-            top |= t << (16 * pp);
-            rest |= rr << (16 * pp);
-          }
-          const uint32_t off = (uint32_t)(lane >> 2) * 256 + (lane & 3) * 4;
-          sts32(qbuf + off + r * 16, (int)top);
-          sts32(qbuf + (NH == 1 ? (8 + r) * 16 : 2048 + r * 16) + off, (int)rest);
-          if (lane == 0) qs[r] = a.scale_log2 * dn;
         }
         fence_async_smem();
         __syncwarp();
@@ -471,49 +482,50 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
     }
   } else if (has_work && warp == 9) {
     // =============================================================== MMA issue
+    // Descriptors as 32-bit halves: the high word is a constant of the layout, the low word is
+    // (address >> 4) | (leading offset >> 4) << 16 and steps by an addition.
     const uint32_t idesc_s = instr_desc_e4m3(1, 0, 128, 16);   // A = K (MN-major), B = Q (K-major)
     const uint32_t idesc_pv = instr_desc_e4m3(0, 1, 128, 16);  // A = V (K-major), B = P^T (MN-major)
-    uint32_t n_s[2] = {0, 0}, n_pv[2] = {0, 0};
+    const uint32_t hi_k = ((C::kPageK >> 4) & 0x3FFFu) | (1u << 14);  // K: next 16 tokens = next page
+    const uint32_t hi_q = ((128u >> 4) & 0x3FFFu) | (1u << 14);       // Q: next 8 rows
+    const uint32_t hi_v = ((128u >> 4) & 0x3FFFu) | (1u << 14);       // V: next 8 head_dim rows
+    const uint32_t hi_p = ((2048u >> 4) & 0x3FFFu) | (1u << 14);      // P: next 16 columns (unused at N = 16)
+    uint32_t n_it = 0;
     int qb = 0;  // query buffer of the current segment (segments alternate)
     bool ok = true;
-    // P V of a tile whose P has been written: k-steps of 32 tokens, every variant into its accumulator
     int pv_slot = 0, pv_nv = 0, pv_fresh = 0;
-    auto issue_pv = [&](int g) -> bool {
-      if (!warp_wait_relaxed(sb0 + C::kBarPFull + 8 * g, n_pv[g] & 1)) return false;
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t vt = sb0 + C::kStages + pv_slot * C::kStageBytes + C::kOffV;
-        const uint32_t pb = sb0 + C::kP + g * C::kPBytes;
-        const int nk = (pv_nv + 31) >> 5;
-        for (int ks = 0; ks < nk; ++ks) {
-          const uint64_t ad = smem_desc_interleaved(vt + ks * 4096, 2048, 128);
+    // P V of the previous stage, both heads: k-steps of 32 tokens, every variant into its accumulator
+    auto issue_pv = [&](uint32_t n) -> bool {
+      for (int g = 0; g < 2; ++g) {
+        if (!warp_wait_relaxed(sb0 + C::kBarPFull + 8 * g, n & 1)) return false;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t vt_lo = smem_desc_lo(sb0 + C::kStages + pv_slot * C::kStageBytes + C::kOffV + g * 2048, C::kPageK);
+          const uint32_t pb_lo = smem_desc_lo(sb0 + C::kP + g * C::kPBytes, 128);
+          const int nk = (pv_nv + 31) >> 5;
+          for (int ks = 0; ks < nk; ++ks) {
 #pragma unroll
-          for (int v = 0; v < NV; ++v)
+            for (int v = 0; v < NV; ++v)
 #pragma unroll
-            for (int hh = 0; hh < NH; ++hh) {
-              const uint64_t bd = smem_desc_interleaved(pb + (v * NH + hh) * 2048 + ks * 512, 128, 2048);
-              umma_f8(tmem + g * 256 + 128 + v * C::CS + hh * 16, ad, bd, idesc_pv, (pv_fresh && ks == 0) ? 0u : 1u);
-            }
+              for (int hh = 0; hh < NH; ++hh)
+                umma_f8_parts(tmem + g * 256 + 128 + v * C::CS + hh * 16, vt_lo + ks * ((2 * C::kPageK) >> 4), hi_v,
+                              pb_lo + (((v * NH + hh) * 2048 + ks * 512) >> 4), hi_p, idesc_pv, (pv_fresh && ks == 0) ? 0u : 1u);
+          }
+          umma_commit(sb0 + C::kBarPvDone + 8 * g);
+          if (g == 1) umma_commit(empty_bar + 8 * pv_slot);
         }
-        umma_commit(sb0 + C::kBarPvDone + 8 * g);
-        umma_commit(empty_bar + 8 * pv_slot);
+        __syncwarp();
       }
-      __syncwarp();
-      ++n_pv[g];
       return true;
     };
     int slot = 0;
     uint32_t phase = 0;
-    int it = 0;
-    for (;; ++it, slot = (slot + 1 == NS) ? 0 : slot + 1, phase ^= (slot == 0) ? 1u : 0u) {
+    for (;; ++n_it, slot = (slot + 1 == NS) ? 0 : slot + 1, phase ^= (slot == 0) ? 1u : 0u) {
       if (!warp_wait(full_bar + 8 * slot, phase)) { ok = false; break; }
       const uint32_t meta = sb0 + kMetaOff + slot * (uint32_t)sizeof(StageMeta);
       const uint4 m0 = lds128(meta), m1 = lds128(meta + 16), m2 = lds128(meta + 32);
       const int flags = (int)m1.x;
       if (flags & FLAG_END) break;
-      const int g = it & 1;
-      // the S buffer of this group has been read
-      if (n_s[g] > 0 && !warp_wait(sb0 + C::kBarSFree + 8 * g, (n_s[g] - 1) & 1)) { ok = false; break; }
       if (flags & FLAG_NEW) {
         const int segc = (int)m2.z;
         // every product issued so far, among them all with the previous segment's query operand, frees that buffer
@@ -521,29 +533,30 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
         qb = segc & 1;
         if (!warp_wait(sb0 + C::kBarQReady + 8 * qb, (uint32_t)(segc >> 1) & 1)) { ok = false; break; }
       }
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t kt = sb0 + C::kStages + slot * C::kStageBytes;
-        const uint32_t qbuf = sb0 + C::kQbuf + qb * C::kQbufBytes;
+      for (int g = 0; g < 2 && ok; ++g) {
+        // the S buffer of this group has been read
+        if (n_it > 0 && !warp_wait(sb0 + C::kBarSFree + 8 * g, (n_it - 1) & 1)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t kt_lo = smem_desc_lo(sb0 + C::kStages + slot * C::kStageBytes + g * 2048, 128);
+          const uint32_t q_lo = smem_desc_lo(sb0 + C::kQbuf + qb * C::kQbufBytes + g * C::kQHead, 256);
 #pragma unroll
-        for (int b = 0; b < NB; ++b) {
-          const uint64_t ad = smem_desc_interleaved(kt + b * 512, 128, 2048);
+          for (int b = 0; b < NB; ++b)
 #pragma unroll
-          for (int hh = 0; hh < NH; ++hh) {
-            const uint64_t bd = smem_desc_interleaved(qbuf + hh * 2048 + b * 512, 256, 128);
-            umma_f8(tmem + g * 256 + (MX ? b * C::CS : 0) + hh * 16, ad, bd, idesc_s, (MX || b == 0) ? 0u : 1u);
-          }
+            for (int hh = 0; hh < NH; ++hh)
+              umma_f8_parts(tmem + g * 256 + (MX ? b * C::CS : 0) + hh * 16, kt_lo + ((b * 512) >> 4), hi_k,
+                            q_lo + ((hh * 2048 + b * 512) >> 4), hi_q, idesc_s, (MX || b == 0) ? 0u : 1u);
+          umma_commit(sb0 + C::kBarSFull + 8 * g);
         }
-        umma_commit(sb0 + C::kBarSFull + 8 * g);
+        __syncwarp();
       }
-      __syncwarp();
-      ++n_s[g];
-      if (it > 0 && !issue_pv(g ^ 1)) { ok = false; break; }
+      if (!ok) break;
+      if (n_it > 0 && !issue_pv(n_it - 1)) { ok = false; break; }
       pv_slot = slot;
       pv_nv = min(kD100Tile, (int)m0.w - (int)m0.z);
-      pv_fresh = ((int)m2.x < 2) ? 1 : 0;
+      pv_fresh = (flags & FLAG_NEW) ? 1 : 0;
     }
-    if (ok && it > 0 && !issue_pv((it - 1) & 1)) ok = false;
+    if (ok && n_it > 0 && !issue_pv(n_it - 1)) ok = false;
     if (!ok && lane == 0) {
       atomicOr(a.status, CUDA_LLM_ST_TIMEOUT);
       atomicAdd(&g_decode100_wait_timeouts, 1u);
@@ -556,7 +569,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
       mbar_arrive(sb0 + C::kBarSFull + 8);
     }
   } else if (has_work && warp < 8) {
-    // =============================================================== softmax groups
+    // =============================================================== softmax groups (one per head of the pair)
     if (a.early_plan) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int g = warp >> 2, gw = warp & 3;
     const int tk = gw * 32 + lane;  // token of the tile / head_dim index of the output this thread owns
@@ -584,26 +597,26 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
     // query token of row r (r / group), four bits per row
     unsigned long long jq_of = 0;
     for (int r = 0; r < RP; ++r) jq_of |= (unsigned long long)((r / a.group) & 15) << (4 * r);
-    int slot = g % NS;
-    uint32_t sphase = (uint32_t)(g / NS) & 1;
-    for (int it = g;; it += 2) {
-      if (!warp_wait_relaxed(s_full, n_g & 1) && lane == 0) flg[4] = 1;
+    int slot = 0;
+    uint32_t sphase = 0;
+    for (;;) {
+      if (!tc_wait_relaxed(s_full, n_g & 1)) flg[4] = 1;
       const bool finished = *done_flag != 0;  // set before the arrival that ended the wait above
-      if (!finished) (void)warp_wait(full_bar + 8 * slot, sphase);  // complete already: orders the reads of the stage
+      if (!finished) (void)tc_wait(full_bar + 8 * slot, sphase);  // complete already: orders the reads of the stage
       tc_fence_after();
       const uint32_t meta = sb0 + kMetaOff + slot * (uint32_t)sizeof(StageMeta);
       const uint4 m0 = lds128(meta), m1 = lds128(meta + 16), m2 = lds128(meta + 32);
-      const int tok0 = (int)m0.z, ctx = (int)m0.w, mslot = (int)m1.y, qlen = (int)m1.w;
-      const int seg_idx = (int)m2.x, seg_n = (int)m2.y;
+      const int tok0 = (int)m0.z, ctx = (int)m0.w, flags = (int)m1.x, mslot = (int)m1.y, qbase = (int)m1.z, qlen = (int)m1.w;
+      const int kvh = (int)m0.y * 2 + g;
       const int R = a.group * qlen;
       const int nv = max(0, min(kD100Tile, ctx - tok0));
       const uint32_t sb = sb0 + C::kStages + slot * C::kStageBytes;
-      const bool grp_new = seg_idx < 2, grp_last = seg_idx >= seg_n - 2;
+      const bool grp_new = (flags & FLAG_NEW) != 0, grp_last = (flags & FLAG_LAST) != 0;
       if (grp_new) {
         // row factors of the segment's query operand (written by the query warp before it arrived on q_ready)
         const int qbi = (int)m2.z & 1;
-        if (!finished && !warp_wait(sb0 + C::kBarQReady + 8 * qbi, ((uint32_t)m2.z >> 1) & 1) && lane == 0) flg[4] = 1;
-        const float* qs = reinterpret_cast<const float*>(smem + C::kQs + qbi * 64);
+        if (!finished && !tc_wait(sb0 + C::kBarQReady + 8 * qbi, ((uint32_t)m2.z >> 1) & 1)) flg[4] = 1;
+        const float* qs = reinterpret_cast<const float*>(smem + C::kQs + (qbi * 2 + g) * 64);
 #pragma unroll
         for (int r = 0; r < RP; ++r) {
           qsr[r] = qs[r];
@@ -612,13 +625,14 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
       }
       // ---- raw logits of this token: S accumulators -> x[r] (log2 domain, softmax scale applied)
       float x[RP];
+      const uint32_t sc_off = (uint32_t)(tk >> 4) * 128 + g * 64;  // this token's page and head in the scale areas
       {
         float kscl[MX ? 4 : 1];
         if (MX) {
 #pragma unroll
-          for (int b = 0; b < 4; ++b) kscl[MX ? b : 0] = __uint_as_float(lds8(sb + C::kOffKs + (tk >> 4) * 64 + b * 16 + (tk & 15)) << 23);
+          for (int b = 0; b < 4; ++b) kscl[MX ? b : 0] = __uint_as_float(lds8(sb + C::kOffKs + sc_off + b * 16 + (tk & 15)) << 23);
         } else {
-          kscl[0] = __uint_as_float(lds32(sb + C::kOffKs + (tk >> 4) * 64 + (tk & 15) * 4));
+          kscl[0] = __uint_as_float(lds32(sb + C::kOffKs + sc_off + (tk & 15) * 4));
         }
 #pragma unroll
         for (int r = 0; r < RP; ++r) x[r] = 0.f;
@@ -654,7 +668,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
       float woff[NV];
       float vrc = 1.f;
       if (MX) {
-        const uint32_t base = sb + C::kOffVs + (tk >> 4) * 64 + (tk & 15);
+        const uint32_t base = sb + C::kOffVs + sc_off + (tk & 15);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           uint32_t e = lds8(base + b * 16);
@@ -663,14 +677,14 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
           woff[MX ? b : 0] = (float)((int)e - 127);
         }
       } else {
-        float v = __uint_as_float(lds32(sb + C::kOffVs + (tk >> 4) * 64 + (tk & 15) * 4));
+        float v = __uint_as_float(lds32(sb + C::kOffVs + sc_off + (tk & 15) * 4));
         if (tk >= nv) v = 1.f;
         v = fmaxf(v, 1e-30f);
         woff[0] = fast_log2(v);
         vrc = fast_rcp(v);
       }
       // ---- does any weight exceed its running maximum by more than 2^kLazyMax?  (The first tile of a
-      // group in a segment always takes the update path, which also initialises the maxima.)
+      // segment always takes the update path, which also initialises the maxima.)
       bool exceed = false;
       if (!grp_new) {
 #pragma unroll
@@ -715,7 +729,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
         for (int r = 0; r < RP; ++r) l_t[r] *= ftab[(NVW - 1) * 16 + r];
         // O of this group in TMEM: wait for its last P V, scale this thread's lane
         if (n_g > 0) {
-          if (!warp_wait(pv_done, (n_g - 1) & 1) && lane == 0) flg[4] = 1;
+          if (!tc_wait(pv_done, (n_g - 1) & 1)) flg[4] = 1;
           pv_waited = true;
           tc_fence_after();
           if (!grp_new) {
@@ -735,7 +749,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
       }
       // ---- P = 2^(w - m) per variant, denominator, E4M3 high + residual, one 16-byte store per token
       if (!pv_waited && n_g > 0) {
-        if (!warp_wait(pv_done, (n_g - 1) & 1) && lane == 0) flg[4] = 1;  // the previous P V has read the P buffer
+        if (!tc_wait(pv_done, (n_g - 1) & 1)) flg[4] = 1;  // the previous P V has read the P buffer
       }
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
@@ -769,11 +783,11 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
         for (int r = 0; r < RP; ++r) l_t[r] += fast_exp2(x[r] - mtab[(NVW - 1) * 16 + r]);
       }
       // a tile that ends inside its last 32-token step: the V bytes of the dead tokens of that step may be
-      // anything (a NaN code times P = 0 is a NaN): zero them.  This thread takes head_dim row tk.
+      // anything (a NaN code times P = 0 is a NaN): zero them.  This thread takes head_dim row tk of its head.
       if (nv < kD100Tile) {
         const int p_lo = nv >> 4, p_hi = ((nv + 31) >> 5) << 1;  // first page with dead tokens, end of the live steps
         for (int pg = p_lo; pg < p_hi; ++pg) {
-          const uint32_t addr = sb + C::kOffV + pg * 2048 + tk * 16;
+          const uint32_t addr = sb + C::kOffV + pg * C::kPageK + g * 2048 + tk * 16;
           const int keep = max(0, nv - pg * 16);  // live tokens of this page (0..15)
           uint4 w = lds128(addr);
           uint32_t ww[4] = {w.x, w.y, w.z, w.w};
@@ -791,8 +805,9 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
       if (lane == 0) mbar_arrive(p_full);
 
       if (grp_last) {
-        // ---- result of this group for the segment: O / l, base-2 log-sum-exp, into the partial slot
-        if (!warp_wait(pv_done, n_g & 1) && lane == 0) flg[4] = 1;
+        // ---- result of this head for the segment: O / l and the base-2 log-sum-exp into the partial slot, or
+        // straight into the output when the whole segment lay in this CTA's range
+        if (!tc_wait(pv_done, n_g & 1)) flg[4] = 1;
         tc_fence_after();
         const int v = MX ? gw : 0;
         uint32_t o[C::CS];
@@ -818,7 +833,8 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
           atomicOr(a.status, CUDA_LLM_ST_SCALE_RANGE);
           scale_range_bad = 0;
         }
-        const size_t prow0 = ((size_t)mslot * 2 + g) * RP;
+        const bool direct = (flags & FLAG_DIRECT) != 0;
+        const size_t prow0 = ((size_t)mslot * 2 + g) * RP;  // [slot][head of the pair][row]
 #pragma unroll
         for (int r = 0; r < RP; ++r) {
           if (r >= R) continue;
@@ -829,24 +845,22 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
           // to the last set's (fp32 scales: the same set, and the same 2^kPShift)
           const float rel = MX ? fast_exp2(mtab[v * 16 + r] - m_l - kPShift) : 1.f;
           const float inv = (l > 0.f) ? rel * fast_rcp(l) : 0.f;
-          a.part_o[(prow0 + r) * D + tk] = val * inv;
-          if (tk == r) a.part_lse[prow0 + r] = (l > 0.f) ? m_l + fast_log2(l) - (MX ? 0.f : kPShift) : NEG_INF;
-        }
-        if (seg_n == 1) {  // the other group had no tile of this segment: an empty partial in its place
-          const size_t prow1 = ((size_t)mslot * 2 + (g ^ 1)) * RP;
-#pragma unroll
-          for (int r = 0; r < RP; ++r) {
-            if (r >= R) continue;
-            a.part_o[(prow1 + r) * D + tk] = 0.f;
-            if (tk == r) a.part_lse[prow1 + r] = NEG_INF;
+          const float lse2 = (l > 0.f) ? m_l + fast_log2(l) - (MX ? 0.f : kPShift) : NEG_INF;
+          if (direct) {
+            const int jq = (int)((jq_of >> (4 * r)) & 15), iq = r - jq * a.group;
+            const size_t row = (size_t)(qbase + jq) * a.Hq + (size_t)kvh * a.group + iq;
+            store_out_elem(a.out, a.out_dtype, row * D + tk, val * inv);
+            if (a.lse && tk == r) a.lse[row] = lse2 * 0.69314718055994531f;
+          } else {
+            a.part_o[(prow0 + r) * D + tk] = val * inv;
+            if (tk == r) a.part_lse[prow0 + r] = lse2;
           }
         }
         named_bar(1 + g, 128);  // sums[] and the tables are rewritten by the next segment
       }
       ++n_g;
-      slot += 2;
-      if (slot >= NS) {
-        slot -= NS;
+      if (++slot == NS) {
+        slot = 0;
         sphase ^= 1u;
       }
     }
