@@ -61,7 +61,7 @@ extern "C" {
                                         return, CUDA_LLM_ST_TIMEOUT (and CUDA_LLM_ST_INCOMPLETE for the rows
                                         left without a result) is set; nothing faults or hangs.          */
 #define CUDA_LLM_FLAG_TCGEN05 4096 /* run the call on the tcgen05 / tensor-memory decode kernel where it
-                                    * applies (head_dim 128, pages of 16 tokens, E4M3 K and V with per-token
+                                    * applies (head_dim 128, an even number of KV heads, pages of 16 tokens, E4M3 K and V with per-token
                                     * fp32 or E8M0 block scales, 16-bit queries, no rotary embedding);
                                     * other calls ignore the flag.  The environment variable
                                     * CUDA_LLM_DECODE_KERNEL=tcgen05 sets it for every call of the process.
