@@ -228,7 +228,7 @@ static int make_layout_sm100(int S, int Hq, int Hkv, int D, int page, int max_q_
   if (group * max_q_len > 16) return CUDA_LLM_EINVAL;
   memset(&L, 0, sizeof(L));
   L.NT = (group * max_q_len <= 8) ? 1 : 2;
-  L.rows_max = 8 * L.NT;
+  L.rows_max = (group * max_q_len <= 4) ? 4 : 8 * L.NT;  // the kernel's padded row counts: 4, 8, 16
   L.HG = 2;
   L.SUBS = 1;
   L.tok_stage = 128;

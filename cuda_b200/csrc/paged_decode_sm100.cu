@@ -53,15 +53,20 @@ struct D100Cfg {
   static constexpr int NV = MX ? 4 : 1;        // P variants = O accumulators
   static constexpr int NVW = MX ? 5 : 1;       // running-maximum sets (the last one, MX only, is the denominator's)
   static constexpr int NH = (RP == 16) ? 2 : 1;  // B operands per product: [high | residual] in one (8 rows) or two (16 rows)
-  static constexpr int CS = 2 * RP;              // accumulator columns per S block / O variant: [high rows | residual rows]
-  // tensor memory, per group (= head of the pair) 256 columns: S blocks from 0, O variants from 128
-  // shared memory (bytes from the 1024-aligned base)
-  static constexpr uint32_t kBarFull = 0, kBarEmpty = 64, kBarSFull = 128, kBarSFree = 144, kBarPFull = 160,
-                            kBarPvDone = 176, kBarQReady = 192, kBarQFree = 208, kTmemSlot = 224, kDone = 228, kPlan = 232;
+  // accumulator columns per S block / O variant: [high rows | residual rows], padded to the 16 columns an MMA has at least
+  static constexpr int CS = (RP <= 8) ? 16 : 32;
+  // tensor memory, per group (= head of the pair) 256 columns: S blocks from 0 (a second S buffer from 64
+  // where the blocks of one fit in 64 columns), O variants from 128
+  static constexpr int SCOLS = (MX ? 4 : 1) * CS;    // columns of one S buffer
+  static constexpr int NSB = (SCOLS <= 64) ? 2 : 1;  // S buffers per group
+  // shared memory (bytes from the 1024-aligned base): mbarriers in the first 256 bytes
+  static constexpr uint32_t kBarFull = 0, kBarEmpty = 64, kBarSFull = 128, kBarSFree = 160, kBarPFull = 192,
+                            kBarPvDone = 208, kBarQReady = 224, kBarQFree = 240;
   static constexpr uint32_t kGrp = kBtRingOff + kBtRing * kMaxPagesPerStage * 4;  // per-group scratch
   static constexpr uint32_t kGrpBytes = 2304;
   // group scratch: maxima [5][16] f32 @0, factors [5][16] @320, reduction [4][5][16] @640, sums [4][16] @1920,
-  // flags [4] @2176, "a wait of this group ran out" @2192
+  // flags [4] @2176, "a wait of this group ran out" @2192; behind that in group 0's: TMEM address, end flag, plan
+  static constexpr uint32_t kTmemSlot = kGrp + 2208, kDone = kGrp + 2212, kPlan = kGrp + 2216;
   static constexpr uint32_t kQs = kGrp + 2 * kGrpBytes;      // per query buffer and head: 16 row factors
   static constexpr uint32_t kQbuf = (kQs + 2 * 2 * 64 + 127) / 128 * 128;
   static constexpr uint32_t kQHead = NH * 2048;              // one head's operand
@@ -172,8 +177,10 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
       mbar_init(empty_bar + 8 * i, 1);
     }
     for (int g = 0; g < 2; ++g) {
-      mbar_init(sb0 + C::kBarSFull + 8 * g, 1);
-      mbar_init(sb0 + C::kBarSFree + 8 * g, 4);
+      for (int b = 0; b < 2; ++b) {  // per S buffer
+        mbar_init(sb0 + C::kBarSFull + 8 * (2 * g + b), 1);
+        mbar_init(sb0 + C::kBarSFree + 8 * (2 * g + b), 4);
+      }
       mbar_init(sb0 + C::kBarPFull + 8 * g, 4);
       mbar_init(sb0 + C::kBarPvDone + 8 * g, 1);
       mbar_init(sb0 + C::kBarQReady + 8 * g, 1);
@@ -465,7 +472,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
             }
             const uint32_t off = (uint32_t)(lane >> 2) * 256 + (lane & 3) * 4;
             sts32(qbuf + off + r * 16, (int)top);
-            sts32(qbuf + (NH == 1 ? (8 + r) * 16 : 2048 + r * 16) + off, (int)rest);
+            sts32(qbuf + (NH == 1 ? (RP + r) * 16 : 2048 + r * 16) + off, (int)rest);
             if (lane == 0) qs[r] = a.scale_log2 * dn;
           }
         }
@@ -533,9 +540,12 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
         qb = segc & 1;
         if (!warp_wait(sb0 + C::kBarQReady + 8 * qb, (uint32_t)(segc >> 1) & 1)) { ok = false; break; }
       }
+      // S buffer of this stage (two per group where they fit: the S of stage n is then issued as soon as its
+      // data is there, not only once the group has started on stage n - 1) and the use count of that buffer
+      const uint32_t sbuf = n_it % C::NSB, suse = n_it / C::NSB;
       for (int g = 0; g < 2 && ok; ++g) {
-        // the S buffer of this group has been read
-        if (n_it > 0 && !warp_wait(sb0 + C::kBarSFree + 8 * g, (n_it - 1) & 1)) { ok = false; break; }
+        // the previous S in this buffer has been read
+        if (suse > 0 && !warp_wait(sb0 + C::kBarSFree + 8 * (2 * g + sbuf), (suse - 1) & 1)) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) {
           const uint32_t kt_lo = smem_desc_lo(sb0 + C::kStages + slot * C::kStageBytes + g * 2048, 128);
@@ -544,9 +554,9 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
           for (int b = 0; b < NB; ++b)
 #pragma unroll
             for (int hh = 0; hh < NH; ++hh)
-              umma_f8_parts(tmem + g * 256 + (MX ? b * C::CS : 0) + hh * 16, kt_lo + ((b * 512) >> 4), hi_k,
+              umma_f8_parts(tmem + g * 256 + sbuf * 64 + (MX ? b * C::CS : 0) + hh * 16, kt_lo + ((b * 512) >> 4), hi_k,
                             q_lo + ((hh * 2048 + b * 512) >> 4), hi_q, idesc_s, (MX || b == 0) ? 0u : 1u);
-          umma_commit(sb0 + C::kBarSFull + 8 * g);
+          umma_commit(sb0 + C::kBarSFull + 8 * (2 * g + sbuf));
         }
         __syncwarp();
       }
@@ -565,8 +575,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
     if (lane == 0) {
       *done_flag = 1;
       __threadfence_block();
-      mbar_arrive(sb0 + C::kBarSFull);
-      mbar_arrive(sb0 + C::kBarSFull + 8);
+      for (int i = 0; i < 4; ++i) mbar_arrive(sb0 + C::kBarSFull + 8 * i);
     }
   } else if (has_work && warp < 8) {
     // =============================================================== softmax groups (one per head of the pair)
@@ -579,10 +588,9 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
     float* red = reinterpret_cast<float*>(smem + grp + 640);       // [4][NVW][16]
     float* sums = reinterpret_cast<float*>(smem + grp + 1920);     // [4][16]
     volatile uint32_t* flg = reinterpret_cast<volatile uint32_t*>(smem + grp + 2176);  // [4], then [4] = a wait ran out
-    const uint32_t s_full = sb0 + C::kBarSFull + 8 * g, s_free = sb0 + C::kBarSFree + 8 * g,
-                   p_full = sb0 + C::kBarPFull + 8 * g, pv_done = sb0 + C::kBarPvDone + 8 * g;
-    const uint32_t t_s = tmem + ((uint32_t)(gw * 32) << 16) + g * 256;
-    const uint32_t t_o = t_s + 128;
+    const uint32_t p_full = sb0 + C::kBarPFull + 8 * g, pv_done = sb0 + C::kBarPvDone + 8 * g;
+    const uint32_t t_g = tmem + ((uint32_t)(gw * 32) << 16) + g * 256;
+    const uint32_t t_o = t_g + 128;
     const uint32_t pbuf = sb0 + C::kP + g * C::kPBytes;
     uint32_t n_g = 0;
     float l_t[RP];
@@ -600,7 +608,10 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
     int slot = 0;
     uint32_t sphase = 0;
     for (;;) {
-      if (!tc_wait_relaxed(s_full, n_g & 1)) flg[4] = 1;
+      const uint32_t sbuf = n_g % C::NSB, suse = n_g / C::NSB;
+      const uint32_t s_full = sb0 + C::kBarSFull + 8 * (2 * g + sbuf), s_free = sb0 + C::kBarSFree + 8 * (2 * g + sbuf);
+      const uint32_t t_s = t_g + sbuf * 64;
+      if (!tc_wait_relaxed(s_full, suse & 1)) flg[4] = 1;
       const bool finished = *done_flag != 0;  // set before the arrival that ended the wait above
       if (!finished) (void)tc_wait(full_bar + 8 * slot, sphase);  // complete already: orders the reads of the stage
       tc_fence_after();
@@ -639,7 +650,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
 #pragma unroll
         for (int b = 0; b < (MX ? 4 : 1); ++b) {
           uint32_t sr[C::CS];
-          if constexpr (RP == 8) tmem_ld16(t_s + b * C::CS, sr);
+          if constexpr (C::CS == 16) tmem_ld16(t_s + b * C::CS, sr);
           else tmem_ld32(t_s + b * C::CS, sr);
           tc_wait_ld();
 #pragma unroll
@@ -735,12 +746,12 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
           if (!grp_new) {
             const int v = MX ? gw : 0;
             uint32_t o[C::CS];
-            if constexpr (RP == 8) tmem_ld16(t_o + v * C::CS, o);
+            if constexpr (C::CS == 16) tmem_ld16(t_o + v * C::CS, o);
             else tmem_ld32(t_o + v * C::CS, o);
             tc_wait_ld();
 #pragma unroll
-            for (int c = 0; c < C::CS; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * ftab[v * 16 + (c & (RP - 1))]);
-            if constexpr (RP == 8) tmem_st16(t_o + v * C::CS, o);
+            for (int c = 0; c < C::CS; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * ftab[v * 16 + (c & (RP - 1))]);  // (unused columns: any factor)
+            if constexpr (C::CS == 16) tmem_st16(t_o + v * C::CS, o);
             else tmem_st32(t_o + v * C::CS, o);
             tc_wait_st();
             tc_fence_before();
@@ -763,16 +774,19 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
         uint32_t top[RP / 2], rest[RP / 2];
 #pragma unroll
         for (int j = 0; j < RP / 2; ++j) split_e4m3x2(p[2 * j], p[2 * j + 1], top[j], rest[j]);
-        if (RP == 8) {
+        if (RP == 4) {
+          // columns: high rows 0..3, residual rows 0..3, eight columns of zeros
+          sts128u(pbuf + v * 2048 + tk * 16, make_uint4(top[0] | (top[1] << 16), rest[0] | (rest[1] << 16), 0u, 0u));
+        } else if (RP == 8) {
           uint4 w;
-          w.x = top[0] | (top[1] << 16); w.y = top[2] | (top[3] << 16);
-          w.z = rest[0] | (rest[1] << 16); w.w = rest[2] | (rest[3] << 16);
+          w.x = top[0] | (top[1] << 16); w.y = top[2] | (top[RP == 8 ? 3 : 0] << 16);
+          w.z = rest[0] | (rest[1] << 16); w.w = rest[RP == 8 ? 2 : 0] | (rest[RP == 8 ? 3 : 0] << 16);
           sts128u(pbuf + v * 2048 + tk * 16, w);
         } else {
           uint4 w, u;
-          w.x = top[0] | (top[1] << 16); w.y = top[2] | (top[3] << 16);
+          w.x = top[0] | (top[1] << 16); w.y = top[RP == 16 ? 2 : 0] | (top[RP == 16 ? 3 : 0] << 16);
           w.z = top[RP == 16 ? 4 : 0] | (top[RP == 16 ? 5 : 0] << 16); w.w = top[RP == 16 ? 6 : 0] | (top[RP == 16 ? 7 : 0] << 16);
-          u.x = rest[0] | (rest[1] << 16); u.y = rest[2] | (rest[3] << 16);
+          u.x = rest[0] | (rest[1] << 16); u.y = rest[RP == 16 ? 2 : 0] | (rest[RP == 16 ? 3 : 0] << 16);
           u.z = rest[RP == 16 ? 4 : 0] | (rest[RP == 16 ? 5 : 0] << 16); u.w = rest[RP == 16 ? 6 : 0] | (rest[RP == 16 ? 7 : 0] << 16);
           sts128u(pbuf + (v * 2) * 2048 + tk * 16, w);
           sts128u(pbuf + (v * 2 + 1) * 2048 + tk * 16, u);
@@ -811,7 +825,7 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
         tc_fence_after();
         const int v = MX ? gw : 0;
         uint32_t o[C::CS];
-        if constexpr (RP == 8) tmem_ld16(t_o + v * C::CS, o);
+        if constexpr (C::CS == 16) tmem_ld16(t_o + v * C::CS, o);
         else tmem_ld32(t_o + v * C::CS, o);
         tc_wait_ld();
         tc_fence_before();
@@ -916,10 +930,14 @@ static cudaError_t launch_d100(const DecodeArgs& a, int grid, cudaStream_t st) {
   return cudaLaunchKernelEx(&cfg, kern, b);
 }
 
-// mode: MODE_TOKEN_SCALE / MODE_MX8; rp: 8 or 16 padded query rows per KV head.  `a.n_stages` > 0 caps the ring.
+// mode: MODE_TOKEN_SCALE / MODE_MX8; rp: 4, 8 or 16 padded query rows per KV head.  `a.n_stages` > 0 caps the ring.
 cudaError_t launch_paged_decode_sm100(const DecodeArgs& a, int mode, int rp, int grid, cudaStream_t st) {
-  if (mode == MODE_TOKEN_SCALE) return rp == 8 ? launch_d100<MODE_TOKEN_SCALE, 8>(a, grid, st) : launch_d100<MODE_TOKEN_SCALE, 16>(a, grid, st);
-  if (mode == MODE_MX8) return rp == 8 ? launch_d100<MODE_MX8, 8>(a, grid, st) : launch_d100<MODE_MX8, 16>(a, grid, st);
+  if (mode == MODE_TOKEN_SCALE)
+    return rp == 4 ? launch_d100<MODE_TOKEN_SCALE, 4>(a, grid, st)
+                   : rp == 8 ? launch_d100<MODE_TOKEN_SCALE, 8>(a, grid, st) : launch_d100<MODE_TOKEN_SCALE, 16>(a, grid, st);
+  if (mode == MODE_MX8)
+    return rp == 4 ? launch_d100<MODE_MX8, 4>(a, grid, st)
+                   : rp == 8 ? launch_d100<MODE_MX8, 8>(a, grid, st) : launch_d100<MODE_MX8, 16>(a, grid, st);
   return cudaErrorInvalidValue;
 }
 

@@ -52,10 +52,10 @@ def test_config2_shapes(ops, batch, ctx_scale):
     assert_parity(out, oracle_out(wl), torch.bfloat16, "cfg2")
 
 
-@pytest.mark.parametrize("hq,hkv", [(8, 8), (16, 8), (64, 8), (32, 2), (12, 4)])
+@pytest.mark.parametrize("hq,hkv", [(8, 8), (16, 8), (64, 8), (32, 2), (12, 4), (24, 4)])
 @pytest.mark.parametrize("q_dtype", [torch.bfloat16, torch.float16])
 def test_group_sizes(ops, hq, hkv, q_dtype):
-    """GQA groups of 1, 2, 8, 16 and 3 query heads per KV head (8 or 16 padded accumulator rows)."""
+    """GQA groups of 1, 2, 8, 16, 3 and 6 query heads per KV head (4, 8 or 16 padded accumulator rows)."""
     wl = _workload([1, 15, 16, 17, 127, 128, 129, 300, 1025], hq=hq, hkv=hkv, seed=hq + hkv, q_dtype=q_dtype)
     out = _run(ops, wl.to("cuda"))
     assert_parity(out, oracle_out(wl), q_dtype, f"group {hq // hkv}")
