@@ -110,17 +110,20 @@ static EncodeTiledFn encode_tiled_fn() {
 
 EncodeTiledFn tensor_map_encoder() { return encode_tiled_fn(); }
 
-// Tensor map of a 16-bit paged cache [num_blocks][Hkv * D][page]: boxes of `box_rows` head_dim lines of
-// one page, swizzled over the 64 or 128 bytes of a line.
-static int encode_cache_map(CUtensorMap* map, const void* cache, int num_blocks, int Hkv, int D, int page, int box_rows) {
+// Tensor map of a paged cache [num_blocks][Hkv * D][page] of 1- or 2-byte elements: boxes of `box_rows`
+// head_dim lines of one page, swizzled over the 64 or 128 bytes of a line.
+static int encode_cache_map(CUtensorMap* map, const void* cache, int num_blocks, int Hkv, int D, int page, int box_rows,
+                            int elem_bytes = 2) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return fail(CUDA_LLM_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t eb = (cuuint64_t)elem_bytes;
   const cuuint64_t dims[3] = {(cuuint64_t)page, (cuuint64_t)Hkv * D, (cuuint64_t)num_blocks};
-  const cuuint64_t strides[2] = {(cuuint64_t)page * 2, (cuuint64_t)Hkv * D * page * 2};
+  const cuuint64_t strides[2] = {(cuuint64_t)page * eb, (cuuint64_t)Hkv * D * page * eb};
   const cuuint32_t box[3] = {(cuuint32_t)page, (cuuint32_t)box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(cache), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, page >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+  const CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                         const_cast<void*>(cache), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, page * elem_bytes >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char msg[96];
@@ -498,12 +501,15 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   if (rc != CUDA_LLM_OK) return rc;
   KvTensorMaps tm;
   memset(&tm, 0, sizeof(tm));
-  if (kv16 && page >= 32) {
-    // pages of 32 / 64 tokens travel as swizzled TMA boxes (at most 256 head_dim lines each)
+  const bool e4m3_page64 = !kv16 && p->v_format == CUDA_LLM_KV_FP8_E4M3 && page == 64;
+  if ((kv16 && page >= 32) || e4m3_page64) {
+    // 16-bit pages of 32 / 64 tokens and 8-bit pages of 64 tokens (rows of 64 / 128 bytes) travel as swizzled
+    // TMA boxes (at most 256 head_dim lines each)
+    const int eb = kv16 ? 2 : 1;
     a.tma_box_rows = L.HG * D < 256 ? L.HG * D : 256;
     a.tma_boxes = (L.HG * D) / a.tma_box_rows;
-    rc = encode_cache_map(&tm.k, p->key_cache, p->num_blocks, Hkv, D, page, a.tma_box_rows);
-    if (rc == CUDA_LLM_OK) rc = encode_cache_map(&tm.v, p->value_cache, p->num_blocks, Hkv, D, page, a.tma_box_rows);
+    rc = encode_cache_map(&tm.k, p->key_cache, p->num_blocks, Hkv, D, page, a.tma_box_rows, eb);
+    if (rc == CUDA_LLM_OK) rc = encode_cache_map(&tm.v, p->value_cache, p->num_blocks, Hkv, D, page, a.tma_box_rows, eb);
     if (rc != CUDA_LLM_OK) return rc;
   }
   cudaError_t e = fn(a, tm, L.grid, L.smem_bytes, st);

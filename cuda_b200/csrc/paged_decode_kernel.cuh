@@ -217,8 +217,12 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a, const __grid_constant_
   // 16-bit pages of 32 / 64 tokens: rows of 64 / 128 bytes, loaded as SWIZZLE_64B / SWIZZLE_128B boxes.
   // (Pages of 16 tokens stay on 1-D bulk copies: as SWIZZLE_32B boxes of 32-byte rows they were measured
   // at 5.0 TB/s against 6.2, the tiled copy engine being slow on 32-byte lines.)
-  constexpr bool TMA3D = KV16 && !TM && PAGE >= 32;
-  constexpr uint32_t SWZ_MASK = (PAGE >= 64) ? 7u : 3u;  // 16-byte chunk index ^= (address >> 7) & mask
+  // 8-bit pages of 64 tokens have rows of 64 bytes too (four of the eight rows of an ldmatrix phase in the same
+  // banks): the same swizzled boxes.  (Rows of 32 bytes stay on bulk copies, see above; packed E2M1 V as well.)
+  constexpr bool TMA3D8 = !KV16 && !V4 && PAGE == 64;
+  constexpr bool TMA3D = (KV16 && !TM && PAGE >= 32) || TMA3D8;
+  constexpr int EB = KV16 ? 2 : 1;               // bytes per cache element
+  constexpr uint32_t SWZ_MASK = (PAGE * EB >= 128) ? 7u : 3u;  // 16-byte chunk index ^= (address >> 7) & mask
   constexpr int SUB = (KV16 || NT == 1) ? 16 : 32;  // tokens per warp sub-tile
   constexpr int MT = SUB / 16;                   // m-tiles of S^T == k-tiles of PV per sub-tile
   constexpr float NEG_INF = -__builtin_huge_valf();
@@ -544,11 +548,18 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a, const __grid_constant_
         const int pg = lane / a.tma_boxes, bx = lane - pg * a.tma_boxes;
         const int blk_pg = __shfl_sync(0xffffffffu, c_blk, pg < np ? pg : 0);
         if (pg < np) {
-          const uint32_t box_bytes = (uint32_t)a.tma_box_rows * (PAGE * 2);
+          const uint32_t box_bytes = (uint32_t)a.tma_box_rows * (PAGE * EB);
           const int row = ic.hg * a.HG * D + bx * a.tma_box_rows;
           tma_load_3d_hint(sb + pg * a.k_page_stride + bx * box_bytes, &tmaps.k, 0, row, blk_pg, fb, stream_policy);
           tma_load_3d_hint(sb + a.off_v + pg * a.v_page_stride + bx * box_bytes, &tmaps.v, 0, row, blk_pg, fb,
                            stream_policy);
+        }
+        if (TMA3D8 && NTYPES == 4 && lane < np && !B200_DIAG(a.debug & 16)) {  // the scales stay on bulk copies
+          const uint64_t b = (uint64_t)c_blk;
+          bulk_g2s_hint(sb + a.off_ks + lane * a.ks_page_stride, a.ks + b * a.ks_blk_stride + (uint64_t)ic.hg * a.ks_chunk,
+                        a.ks_chunk, fb, stream_policy);
+          bulk_g2s_hint(sb + a.off_vs + lane * a.vs_page_stride, a.vs + b * a.vs_blk_stride + (uint64_t)ic.hg * a.vs_chunk,
+                        a.vs_chunk, fb, stream_policy);
         }
       } else if (!TM && !no_copy && !stalled) {
         const uint32_t sb = stage0 + slot * a.stage_bytes;
@@ -632,6 +643,10 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a, const __grid_constant_
         k_lm[mt] ^= ((k_lm[mt] >> 7) & SWZ_MASK) << 4;
         v_lm[mt] ^= ((v_lm[mt] >> 7) & SWZ_MASK) << 4;
       }
+    } else if (TMA3D8) {
+      // 8-bit rows of 64 bytes, swizzled the same way; steps of 32 rows are multiples of 1024 bytes
+      k_lm[mt] ^= ((k_lm[mt] >> 7) & SWZ_MASK) << 4;
+      v_lm[mt] ^= ((v_lm[mt] >> 7) & SWZ_MASK) << 4;
     }
   }
 
