@@ -30,6 +30,11 @@ cudaError_t run_mx_attention(const void* q, const float* qs, const void* k, cons
 cudaError_t run_kv_append_prefill(const void* k, const void* v, const CudaLlmKvCacheTarget& c, int B, int Hkv, int S,
                                   int D, int in_dtype, cudaStream_t st);
 size_t dense_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens);
+size_t paged_f32_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens);
+bool paged_f32_decode_supported(int D, int page, const void* k, const void* v);
+cudaError_t run_paged_f32_decode(const void* q, const void* k, const void* v, const int32_t* bt, const int32_t* ctx,
+                                 void* out, int S, int Hq, int Hkv, int D, int max_blocks, int num_blocks,
+                                 float softmax_scale, void* workspace, int num_sms, cudaStream_t st);
 cudaError_t run_dense_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
                              const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int page,
                              int max_blocks, int num_blocks, int seq_len, float softmax_scale, int dtype,
@@ -256,6 +261,7 @@ static int make_layout_sm100(int S, int Hq, int Hkv, int D, int page, int max_q_
 cudaError_t launch_paged_decode_sm100(const DecodeArgs& a, int mode, int rp, int grid, cudaStream_t st);
 unsigned int decode100_wait_timeouts();
 static std::atomic<uint64_t> g_sm100_launches{0};
+static std::atomic<uint64_t> g_f32_launches{0};
 
 // The tcgen05 kernel serves head_dim 128, an even number of KV heads, pages of 16 tokens, E4M3 K and V with
 // per-token fp32 or E8M0 block scales and 16-bit queries, when the call (CUDA_LLM_FLAG_TCGEN05) or the process
@@ -615,6 +621,10 @@ size_t cuda_llm_dense_decode_workspace_bytes(int32_t num_seqs, int32_t num_heads
                                              int32_t head_dim, int32_t max_tokens) {
   if (check_dense(num_seqs, num_heads, num_kv_heads, head_dim, CUDA_LLM_F32) != CUDA_LLM_OK || max_tokens < 0) return 0;
   size_t need = dense_decode_workspace_bytes(num_seqs, num_heads, num_kv_heads, head_dim, max_tokens);
+  {  // an fp32 cache with pages of 16 tokens runs on the bulk-copy kernel, which cuts sequences into more chunks
+    const size_t f32 = paged_f32_decode_workspace_bytes(num_seqs, num_heads, num_kv_heads, head_dim, max_tokens);
+    if (f32 > need) need = f32;
+  }
   // a 16-bit paged cache runs on the persistent kernel: cover its split partials for every page size
   for (int page = 16; page <= 64; page *= 2) {
     Layout L;
@@ -660,6 +670,14 @@ int cuda_llm_paged_attention(const void* query, const void* key_cache, const voi
     p.k_format = p.v_format = (dtype == CUDA_LLM_F16) ? CUDA_LLM_KV_F16 : CUDA_LLM_KV_BF16;
     p.softmax_scale = softmax_scale;
     return cuda_llm_paged_decode(&p, stream);
+  }
+  if (dtype == CUDA_LLM_F32 && paged_f32_decode_supported(head_dim, page_size, key_cache, value_cache) &&
+      !((uintptr_t)workspace & 15)) {
+    cudaError_t e = run_paged_f32_decode(query, key_cache, value_cache, block_tables, context_lens, out, num_seqs,
+                                         num_heads, num_kv_heads, head_dim, max_blocks_per_seq, num_blocks, softmax_scale,
+                                         workspace, sm_count_cached(), reinterpret_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) g_f32_launches.fetch_add(1, std::memory_order_relaxed);
+    return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "paged_attention (fp32) launch");
   }
   cudaError_t e = run_dense_decode(true, query, key_cache, value_cache, block_tables, context_lens, out, num_seqs,
                                    num_heads, num_kv_heads, head_dim, page_size, max_blocks_per_seq, num_blocks, 0,
@@ -773,6 +791,12 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
     e = run_kv_append_prefill(k, v, *cache, batch_size, num_kv_heads, seq_len, head_dim, dtype, st);
     if (e != cudaSuccess) return fail_cuda(e, "kv_append_kernel launch");
   }
+  return CUDA_LLM_OK;
+}
+
+int cuda_llm_paged_attention_f32_launches(uint64_t* launches) {
+  if (!launches) return fail(CUDA_LLM_EINVAL, "null argument");
+  *launches = g_f32_launches.load(std::memory_order_relaxed);
   return CUDA_LLM_OK;
 }
 
