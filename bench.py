@@ -38,7 +38,7 @@ if ROOT not in sys.path:
 
 WORKLOADS = {"cfg1": 1, "cfg2": 2, "cfg3": 3, "cfg4": 4, "cfg5": 5}
 # secondary lines for the unquantised entry points (same Llama-3-8B head shape, bf16 K/V)
-AUX_WORKLOADS = ("pa16", "pa32", "fd16", "prefill", "mxattn")
+AUX_WORKLOADS = ("pa16", "pa32", "fd16", "fd32", "prefill", "mxattn")
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode-kernel launch,
@@ -224,12 +224,13 @@ def aux_workload(args, rank, world, local):
         cfg = {"workload": wl.name, "batch_per_gpu": batch, "kv_tokens_per_gpu": sum(ctx), "page_size": args.page_size}
     else:
         seq = int(2560 * args.ctx_scale)
-        q = torch.randn(batch, 32, 1, 128, generator=g).to(torch.bfloat16).to(dev)
-        k = torch.randn(batch, 8, seq, 128, generator=g).to(torch.bfloat16).to(dev)
-        v = torch.randn(batch, 8, seq, 128, generator=g).to(torch.bfloat16).to(dev)
-        kv_bytes = 2 * k.numel() * 2
+        cdt = torch.float32 if args.workload == "fd32" else torch.bfloat16
+        q = torch.randn(batch, 32, 1, 128, generator=g).to(cdt).to(dev)
+        k = torch.randn(batch, 8, seq, 128, generator=g).to(cdt).to(dev)
+        v = torch.randn(batch, 8, seq, 128, generator=g).to(cdt).to(dev)
+        kv_bytes = 2 * k.numel() * k.element_size()
         fn = lambda: ops.async_flash_decode(q, k, v)
-        cfg = {"workload": "fd16_llama8b_bf16", "batch_per_gpu": batch, "seq_len": seq}
+        cfg = {"workload": "fd32_llama8b_fp32" if cdt == torch.float32 else "fd16_llama8b_bf16", "batch_per_gpu": batch, "seq_len": seq}
     for _ in range(args.warmup):
         fn()
     torch.cuda.synchronize()
@@ -245,14 +246,14 @@ def aux_workload(args, rank, world, local):
                 "l2": "inputs larger than L2, no flush needed"})
     if rank != 0:
         return
-    f32 = args.workload == "pa32"
+    f32 = args.workload in ("pa32", "fd32")
     print(json.dumps({"metric": ("fp32" if f32 else "bf16") + "_decode_kv_hbm_throughput", "value": kv_bytes / (ms * 1e-3) / 1e12, "unit": "TB/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
                       "higher_is_better": True, "dtype": "f32 SIMT" if f32 else "bf16 mma, f32 acc", "data": "synthetic", "config": cfg,
                       "roofline": {"bound": "hbm", "achieved": kv_bytes / (ms * 1e-3) / 1e9, "peak": peak,
                                    "unit": "GB/s", "frac": kv_bytes / (ms * 1e-3) / 1e9 / peak,
                                    "peak_source": peak_src,
-                                   "kernel": "dense_decode_kernel + merge_partials_kernel" if f32 else "paged_decode_kernel + merge_splits_kernel"},
+                                   "kernel": "paged_f32_decode_kernel + merge_partials_kernel" if f32 else "paged_decode_kernel + merge_splits_kernel"},
                       "gpu_launches": 2 * args.steps}), flush=True)
 
 

@@ -32,9 +32,10 @@ cudaError_t run_kv_append_prefill(const void* k, const void* v, const CudaLlmKvC
 size_t dense_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens);
 size_t paged_f32_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens);
 bool paged_f32_decode_supported(int D, int page, const void* k, const void* v);
-cudaError_t run_paged_f32_decode(const void* q, const void* k, const void* v, const int32_t* bt, const int32_t* ctx,
-                                 void* out, int S, int Hq, int Hkv, int D, int max_blocks, int num_blocks,
-                                 float softmax_scale, void* workspace, int num_sms, cudaStream_t st);
+cudaError_t run_paged_f32_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
+                                 const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int max_blocks,
+                                 int num_blocks, int seq_len, float softmax_scale, void* workspace, int num_sms,
+                                 cudaStream_t st);
 cudaError_t run_dense_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
                              const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int page,
                              int max_blocks, int num_blocks, int seq_len, float softmax_scale, int dtype,
@@ -673,9 +674,10 @@ int cuda_llm_paged_attention(const void* query, const void* key_cache, const voi
   }
   if (dtype == CUDA_LLM_F32 && paged_f32_decode_supported(head_dim, page_size, key_cache, value_cache) &&
       !((uintptr_t)workspace & 15)) {
-    cudaError_t e = run_paged_f32_decode(query, key_cache, value_cache, block_tables, context_lens, out, num_seqs,
-                                         num_heads, num_kv_heads, head_dim, max_blocks_per_seq, num_blocks, softmax_scale,
-                                         workspace, sm_count_cached(), reinterpret_cast<cudaStream_t>(stream));
+    cudaError_t e = run_paged_f32_decode(true, query, key_cache, value_cache, block_tables, context_lens, out, num_seqs,
+                                         num_heads, num_kv_heads, head_dim, max_blocks_per_seq, num_blocks, 0,
+                                         softmax_scale, workspace, sm_count_cached(),
+                                         reinterpret_cast<cudaStream_t>(stream));
     if (e == cudaSuccess) g_f32_launches.fetch_add(1, std::memory_order_relaxed);
     return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "paged_attention (fp32) launch");
   }
@@ -739,6 +741,15 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
     if (e != cudaSuccess) return fail_cuda(e, "paged_decode_kernel launch");
     e = (head_dim == 64) ? launch_merge_splits<64>(a, 16, L.grid, st) : launch_merge_splits<128>(a, 16, L.grid, st);
     return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "merge_splits_kernel launch");
+  }
+  if (dtype == CUDA_LLM_F32 && seq_len > 0 && paged_f32_decode_supported(head_dim, 16, k, v) &&
+      !((uintptr_t)workspace & 15)) {
+    // fp32 K/V: the bulk-copy kernel in its token-major mode
+    cudaError_t e = run_paged_f32_decode(false, q, k, v, nullptr, nullptr, o, batch_size, num_heads, num_kv_heads,
+                                         head_dim, (seq_len + 15) / 16, 1, seq_len, softmax_scale, workspace,
+                                         sm_count_cached(), reinterpret_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) g_f32_launches.fetch_add(1, std::memory_order_relaxed);
+    return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "flash_decode (fp32) launch");
   }
   cudaError_t e = run_dense_decode(false, q, k, v, nullptr, nullptr, o, batch_size, num_heads, num_kv_heads, head_dim,
                                    1, 1, 1, seq_len, softmax_scale, dtype, workspace, reinterpret_cast<cudaStream_t>(stream));

@@ -21,8 +21,16 @@
 //   three butterfly steps) and in P.V (the lane multiplies by the probabilities of exactly the tokens it
 //   scored, so P never moves; partial outputs are summed over tq once per item).
 //
+// The same kernel serves the reference's contiguous fp32 K/V (async_flash_decode_kernel.cuh:29-220, tensors
+// [B, H, S, D], one token = one row of head_dim floats) as its token-major mode: a slot then holds 16
+// consecutive token rows, lane (dq, tl) = (lane & 7, lane >> 3) reads the 16 bytes of head_dim values
+// 32kb + 4dq .. +3 of token rows tl, tl + 4, ... (again 128 contiguous bytes per phase), dot products are
+// summed over dq and outputs over tl.
+//
 // Waits are bounded (mbar_wait); a warp whose wait runs out records CUDA_LLM_ST_TIMEOUT in the status
 // word, waits (bounded) for its own copies still in flight and returns.
+#include <type_traits>
+
 #include "paged_decode_kernel.cuh"
 
 namespace b200 {
@@ -47,6 +55,7 @@ struct PagedF32Args {
   uint32_t* status;
   uint32_t* counter;  // next item
   int S, Hq, Hkv, group, max_blocks, num_blocks, n_splits, chunk_pages, n_rg;
+  int seq_len;        // token-major mode: tokens of every sequence (bt and ctx are null)
   long long n_items;
   float scale_log2;
 };
@@ -66,9 +75,10 @@ static void f32_split_plan(int S, int Hkv, int group, int max_pages, int& chunk_
   n_splits = max_pages > 0 ? (int)((max_pages + c - 1) / c) : 1;
 }
 
-template <int D, int GP>
+template <int D, int GP, bool TM>
 __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(const PagedF32Args a) {
-  constexpr int KK = D / 8;                  // head_dim rows per lane
+  constexpr int KK = D / 8;                  // head_dim values per lane
+  constexpr int KB = D / 32;                 // token-major: 32-wide head_dim blocks
   constexpr uint32_t SLOT = D * 16 * 4;      // bytes of a slab
   constexpr float NEG_INF = -__builtin_huge_valf();
   extern __shared__ __align__(128) uint8_t smem_f32[];
@@ -76,7 +86,8 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
   __shared__ int2 queue[kF32Warps][4];       // items issued and not yet consumed: (item, live tokens)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tq = lane & 3, dl = lane >> 2;
+  const int tq = lane & 3, dl = lane >> 2;   // paged: token quad, head_dim row
+  const int dq = lane & 7, tl = lane >> 3;   // token-major: head_dim quad, token row
   uint8_t* ring = smem_f32 + (size_t)warp * kF32Slots * SLOT;
   const uint32_t ring_u32 = smem_u32(ring);
   const uint32_t bar0 = smem_u32(&bars[warp][0]);
@@ -91,22 +102,26 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
 
   // ---- issue side: a cursor over the pages of the item being fetched
   uint32_t iseq = 0, cseq = 0;  // slots issued / consumed
-  int it_kvh = 0, it_page = 0, it_npages = 0, it_kv = 0, it_first_blk = 0, it_s = 0;
+  int it_kvh = 0, it_page = 0, it_npages = 0, it_kv = 0, it_first_blk = 0, it_s = 0, it_ntok = 0;
   int it_bt = 0;                // lane j: block of page (it_page & ~31) + j of the item
   bool it_have = false, it_done = false;
   int qw = 0, qr = 0;           // queue write / read positions
   int next_raw = 0;             // lane 0: the item the next acquire takes (fetched one item ahead)
   if (lane == 0) next_raw = (int)atomicAdd(a.counter, 1u);
 
+  // Items are numbered chunk-major: every sequence's first chunk comes before any second chunk.  The
+  // chunks handed out last are then the high ones, which short sequences do not have and longer ones
+  // fill only partly, so the work left for the end is fine-grained and the warps finish together.
   auto item_coords = [&](long long item, int& s, int& kvh, int& split, int& rg) {
     rg = (int)(item % a.n_rg);
     item /= a.n_rg;
-    split = (int)(item % a.n_splits);
-    item /= a.n_splits;
     kvh = (int)(item % a.Hkv);
-    s = (int)(item / a.Hkv);
+    item /= a.Hkv;
+    s = (int)(item % a.S);
+    split = (int)(item / a.S);
   };
   auto load_bt = [&]() {
+    if (TM) return;
     const int pg = it_first_blk + (it_page & ~31) + lane;
     int b = (pg < a.max_blocks && (it_page & ~31) + lane < it_npages) ? a.bt[(size_t)it_s * a.max_blocks + pg] : 0;
     if (b < 0 || b >= a.num_blocks) {
@@ -125,8 +140,8 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
       if (lane == 0) next_raw = (int)atomicAdd(a.counter, 1u);
       int s, kvh, split, rg;
       item_coords(item, s, kvh, split, rg);
-      int ctx = a.ctx[s];
-      ctx = max(0, min(ctx, a.max_blocks * 16));
+      int ctx = TM ? a.seq_len : a.ctx[s];
+      if (!TM) ctx = max(0, min(ctx, a.max_blocks * 16));
       const int t0 = split * a.chunk_pages * 16;
       const int n_tok = max(0, min(ctx - t0, a.chunk_pages * 16));
       if (n_tok == 0) {
@@ -146,6 +161,7 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
       it_page = 0;
       it_kv = 0;
       it_first_blk = t0 >> 4;
+      it_ntok = n_tok;
       it_have = true;
       load_bt();
       if (lane == 0) queue[warp][qw & 3] = make_int2((int)item, n_tok);
@@ -156,12 +172,21 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
   auto issue_one = [&]() {
     if (!it_have) acquire();
     if (!it_have) return;
-    const int blk = __shfl_sync(0xffffffffu, it_bt, it_page & 31);
-    const float* src = (it_kv ? a.v : a.k) + ((size_t)blk * a.Hkv + it_kvh) * (size_t)(D * 16);
+    const float* src;
+    uint32_t bytes = SLOT;
+    if (TM) {
+      // 16 consecutive token rows of this (sequence, KV head); the last tile of a sequence may be shorter
+      const size_t tok = (size_t)(it_first_blk + it_page) * 16;
+      src = (it_kv ? a.v : a.k) + (((size_t)it_s * a.Hkv + it_kvh) * a.seq_len + tok) * D;
+      bytes = (uint32_t)min(16, it_ntok - it_page * 16) * (D * 4);
+    } else {
+      const int blk = __shfl_sync(0xffffffffu, it_bt, it_page & 31);
+      src = (it_kv ? a.v : a.k) + ((size_t)blk * a.Hkv + it_kvh) * (size_t)(D * 16);
+    }
     const uint32_t slot = iseq % kF32Slots;
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar0 + 8 * slot, SLOT);
-      bulk_g2s_hint(ring_u32 + slot * SLOT, src, SLOT, bar0 + 8 * slot, policy);
+      mbar_arrive_expect_tx(bar0 + 8 * slot, bytes);
+      bulk_g2s_hint(ring_u32 + slot * SLOT, src, bytes, bar0 + 8 * slot, policy);
     }
     ++iseq;
     it_kv ^= 1;
@@ -216,7 +241,9 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
         for (int r = 0; r < GP; ++r) {
 #pragma unroll
           for (int kk = 0; kk < KK; ++kk) {
-            qv[r][kk] = (r < c_rows) ? qp[(size_t)r * D + dl + 8 * kk] : 0.f;
+            // paged: head_dim dl + 8kk; token-major: head_dim 32 (kk / 4) + 4dq + kk % 4
+            const int d = TM ? 32 * (kk >> 2) + 4 * dq + (kk & 3) : dl + 8 * kk;
+            qv[r][kk] = (r < c_rows) ? qp[(size_t)r * D + d] : 0.f;
             acc[r][kk] = 0.f;
           }
           m_run[r] = -1.0e30f;  // a finite floor: max - max never becomes inf - inf
@@ -227,38 +254,53 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
       float sc[GP][4];
 #pragma unroll
       for (int r = 0; r < GP; ++r) sc[r][0] = sc[r][1] = sc[r][2] = sc[r][3] = 0.f;
+      if (TM) {
 #pragma unroll
-      for (int kk = 0; kk < KK; ++kk) {
-        const float4 kv = ks[(dl + 8 * kk) * 4 + tq];
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int r = 0; r < GP; ++r) {
-          sc[r][0] = fmaf(qv[r][kk], kv.x, sc[r][0]);
-          sc[r][1] = fmaf(qv[r][kk], kv.y, sc[r][1]);
-          sc[r][2] = fmaf(qv[r][kk], kv.z, sc[r][2]);
-          sc[r][3] = fmaf(qv[r][kk], kv.w, sc[r][3]);
+          for (int kb = 0; kb < KB; ++kb) {
+            const float4 kv = ks[(tl + 4 * j) * (D / 4) + 8 * kb + dq];
+#pragma unroll
+            for (int r = 0; r < GP; ++r)
+              sc[r][j] = fmaf(qv[r][4 * kb + 3], kv.w, fmaf(qv[r][4 * kb + 2], kv.z,
+                         fmaf(qv[r][4 * kb + 1], kv.y, fmaf(qv[r][4 * kb], kv.x, sc[r][j]))));
+          }
+      } else {
+#pragma unroll
+        for (int kk = 0; kk < KK; ++kk) {
+          const float4 kv = ks[(dl + 8 * kk) * 4 + tq];
+#pragma unroll
+          for (int r = 0; r < GP; ++r) {
+            sc[r][0] = fmaf(qv[r][kk], kv.x, sc[r][0]);
+            sc[r][1] = fmaf(qv[r][kk], kv.y, sc[r][1]);
+            sc[r][2] = fmaf(qv[r][kk], kv.z, sc[r][2]);
+            sc[r][3] = fmaf(qv[r][kk], kv.w, sc[r][3]);
+          }
         }
       }
       __syncwarp();  // every lane has read the slab: the slot may be refilled
       ++cseq;
       fill();
-      // sum over the eight dl lanes
+      // sum over the eight lanes that share the tokens (paged: dl, token-major: dq)
 #pragma unroll
-      for (int o = 4; o < 32; o <<= 1)
+      for (int o = TM ? 1 : 4; o < (TM ? 8 : 32); o <<= 1)
 #pragma unroll
         for (int r = 0; r < GP; ++r)
 #pragma unroll
           for (int j = 0; j < 4; ++j) sc[r][j] += __shfl_xor_sync(0xffffffffu, sc[r][j], o);
-      const int tok = c_page * 16 + 4 * tq;  // first token of this lane within the item
+      // token of sc[.][j] within the item: paged 4tq + j, token-major tl + 4j
+      const int tok = c_page * 16 + (TM ? tl : 4 * tq);
+      constexpr int TSTEP = TM ? 4 : 1;
       bool rescale = false;
       float alpha[GP];
 #pragma unroll
       for (int r = 0; r < GP; ++r) {
         float x[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) x[j] = (tok + j < c_ntok) ? sc[r][j] * a.scale_log2 : NEG_INF;
+        for (int j = 0; j < 4; ++j) x[j] = (tok + TSTEP * j < c_ntok) ? sc[r][j] * a.scale_log2 : NEG_INF;
         float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, TM ? 8 : 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, TM ? 16 : 2));
         const float mn = fmaxf(m_run[r], mx);
         alpha[r] = fast_exp2(m_run[r] - mn);
         rescale |= (alpha[r] != 1.f);
@@ -269,7 +311,7 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
           p[r][j] = fast_exp2(x[j] - mn);
           ps += p[r][j];
         }
-        l_run[r] = l_run[r] * alpha[r] + ps;  // over this lane's tokens; summed over tq at the end
+        l_run[r] = l_run[r] * alpha[r] + ps;  // over this lane's tokens; summed over tq / tl at the end
       }
       if (rescale) {  // uniform over the warp: every lane holds the same maxima
 #pragma unroll
@@ -286,8 +328,27 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
         return;
       }
       const float4* vs = reinterpret_cast<const float4*>(ring + slot * SLOT);
-      const int left = c_ntok - (c_page * 16 + 4 * tq);  // live tokens among this lane's four
-      if (left >= 4) {
+      if (TM) {
+        // a dead token row may hold anything (the copy of a short last tile leaves old bytes behind):
+        // its probability is exactly 0, and its values are replaced by 0 so that 0 * NaN cannot occur
+        const bool tail = c_ntok - c_page * 16 < 16;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const bool live_tok = !tail || (c_page * 16 + tl + 4 * j < c_ntok);
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb) {
+            float4 vv = vs[(tl + 4 * j) * (D / 4) + 8 * kb + dq];
+            if (!live_tok) vv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < GP; ++r) {
+              acc[r][4 * kb] = fmaf(p[r][j], vv.x, acc[r][4 * kb]);
+              acc[r][4 * kb + 1] = fmaf(p[r][j], vv.y, acc[r][4 * kb + 1]);
+              acc[r][4 * kb + 2] = fmaf(p[r][j], vv.z, acc[r][4 * kb + 2]);
+              acc[r][4 * kb + 3] = fmaf(p[r][j], vv.w, acc[r][4 * kb + 3]);
+            }
+          }
+        }
+      } else if (c_ntok - (c_page * 16 + 4 * tq) >= 4) {
 #pragma unroll
         for (int kk = 0; kk < KK; ++kk) {
           const float4 vv = vs[(dl + 8 * kk) * 4 + tq];
@@ -297,6 +358,7 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
         }
       } else {
         // the tail of the sequence: a dead slot may hold anything, 0 * NaN must not reach the accumulator
+        const int left = c_ntok - (c_page * 16 + 4 * tq);  // live tokens among this lane's four
 #pragma unroll
         for (int kk = 0; kk < KK; ++kk) {
           float4 vv = vs[(dl + 8 * kk) * 4 + tq];
@@ -318,17 +380,26 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
 #pragma unroll
       for (int r = 0; r < GP; ++r) {
         float l = l_run[r];
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        l += __shfl_xor_sync(0xffffffffu, l, TM ? 8 : 1);
+        l += __shfl_xor_sync(0xffffffffu, l, TM ? 16 : 2);
         const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
         for (int kk = 0; kk < KK; ++kk) {
           float v = acc[r][kk];
-          v += __shfl_xor_sync(0xffffffffu, v, 1);
-          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, TM ? 8 : 1);
+          v += __shfl_xor_sync(0xffffffffu, v, TM ? 16 : 2);
           acc[r][kk] = v * inv;
         }
-        if (r < c_rows) {
+        if (r < c_rows && TM) {
+          // lane (dq, tl) stores the four values of head_dim block tl: 32 consecutive floats per 8 lanes
+          float* po = a.part_o + (c_row0 + r) * D;
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb)
+            if (tl == kb)
+              *reinterpret_cast<float4*>(po + 32 * kb + 4 * dq) =
+                  make_float4(acc[r][4 * kb], acc[r][4 * kb + 1], acc[r][4 * kb + 2], acc[r][4 * kb + 3]);
+          if (lane == 0) a.part_lse[c_row0 + r] = l > 0.f ? (m_run[r] + log2f(l)) * 0.69314718055994531f : NEG_INF;
+        } else if (r < c_rows) {
           float* po = a.part_o + (c_row0 + r) * D;
           // lane (tq, dl) stores head_dim rows dl + 8 * (4i + tq): 32 consecutive floats per instruction
 #pragma unroll
@@ -343,7 +414,7 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
   }
 }
 
-template <int D, int GP>
+template <int D, int GP, bool TM>
 static cudaError_t launch_f32(const PagedF32Args& a, int grid, cudaStream_t st) {
   const size_t dyn = (size_t)kF32Warps * kF32Slots * D * 16 * 4;
   static bool attr_set[64] = {false};
@@ -351,11 +422,11 @@ static cudaError_t launch_f32(const PagedF32Args& a, int grid, cudaStream_t st) 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev >= 64 || !attr_set[dev]) {
-    e = cudaFuncSetAttribute(paged_f32_decode_kernel<D, GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+    e = cudaFuncSetAttribute(paged_f32_decode_kernel<D, GP, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
     if (e != cudaSuccess) return e;
     if (dev < 64) attr_set[dev] = true;
   }
-  paged_f32_decode_kernel<D, GP><<<grid, 32 * kF32Warps, dyn, st>>>(a);
+  paged_f32_decode_kernel<D, GP, TM><<<grid, 32 * kF32Warps, dyn, st>>>(a);
   return cudaGetLastError();
 }
 
@@ -370,15 +441,19 @@ bool paged_f32_decode_supported(int D, int page, const void* k, const void* v) {
   return page == 16 && (D == 64 || D == 128) && !(((uintptr_t)k | (uintptr_t)v) & 15);
 }
 
-cudaError_t run_paged_f32_decode(const void* q, const void* k, const void* v, const int32_t* bt, const int32_t* ctx,
-                                 void* out, int S, int Hq, int Hkv, int D, int max_blocks, int num_blocks,
-                                 float softmax_scale, void* workspace, int num_sms, cudaStream_t st) {
+// `paged`: K/V are caches [num_blocks, Hkv, D, 16] read through bt / ctx; otherwise contiguous tensors
+// [S, Hkv, seq_len, D] (bt and ctx unused, max_blocks = pages that cover seq_len).
+cudaError_t run_paged_f32_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
+                                 const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int max_blocks,
+                                 int num_blocks, int seq_len, float softmax_scale, void* workspace, int num_sms,
+                                 cudaStream_t st) {
   PagedF32Args a;
   a.q = reinterpret_cast<const float*>(q);
   a.k = reinterpret_cast<const float*>(k);
   a.v = reinterpret_cast<const float*>(v);
   a.bt = bt; a.ctx = ctx;
   a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.group = Hq / Hkv; a.max_blocks = max_blocks; a.num_blocks = num_blocks;
+  a.seq_len = seq_len;
   f32_split_plan(S, Hkv, a.group, max_blocks, a.chunk_pages, a.n_splits);
   a.n_rg = (a.group + 3) / 4;
   a.n_items = (long long)S * Hkv * a.n_splits * a.n_rg;
@@ -394,8 +469,15 @@ cudaError_t run_paged_f32_decode(const void* q, const void* k, const void* v, co
   if (e != cudaSuccess) return e;
   const int grid = num_sms > 0 ? num_sms : 148;
   const int gp = a.group >= 3 ? 4 : a.group;
-  if (D == 64) e = gp == 1 ? launch_f32<64, 1>(a, grid, st) : gp == 2 ? launch_f32<64, 2>(a, grid, st) : launch_f32<64, 4>(a, grid, st);
-  else e = gp == 1 ? launch_f32<128, 1>(a, grid, st) : gp == 2 ? launch_f32<128, 2>(a, grid, st) : launch_f32<128, 4>(a, grid, st);
+  auto go = [&](auto d_tag, auto tm_tag) -> cudaError_t {
+    constexpr int DD = decltype(d_tag)::value;
+    constexpr bool T = decltype(tm_tag)::value;
+    return gp == 1 ? launch_f32<DD, 1, T>(a, grid, st) : gp == 2 ? launch_f32<DD, 2, T>(a, grid, st) : launch_f32<DD, 4, T>(a, grid, st);
+  };
+  using I64 = std::integral_constant<int, 64>;
+  using I128 = std::integral_constant<int, 128>;
+  if (paged) e = (D == 64) ? go(I64{}, std::false_type{}) : go(I128{}, std::false_type{});
+  else e = (D == 64) ? go(I64{}, std::true_type{}) : go(I128{}, std::true_type{});
   if (e != cudaSuccess) return e;
   return launch_merge_partials(a.part_o, a.part_lse, a.n_splits, (long long)rows, D, out, CUDA_LLM_F32, nullptr, st);
 }

@@ -286,9 +286,9 @@ int cuda_llm_prefill_wait_timeouts(uint32_t* count);
  * second synchronises the device).  Either pointer may be NULL. */
 int cuda_llm_decode_tcgen05_counters(uint64_t* launches, uint32_t* wait_timeouts);
 
-/* No counterpart in the reference.  Calls of cuda_llm_paged_attention by this process that ran on the
- * bulk-copy fp32 kernel (fp32 cache, pages of 16 tokens); other fp32 shapes run on the plain split-KV
- * kernel. */
+/* No counterpart in the reference.  Calls of cuda_llm_paged_attention (fp32 cache, pages of 16 tokens)
+ * and cuda_llm_flash_decode (fp32 K/V) by this process that ran on the bulk-copy fp32 kernel; other
+ * fp32 shapes run on the plain split-KV kernel. */
 int cuda_llm_paged_attention_f32_launches(uint64_t* launches);
 
 /* Replaces dispatch_fused_microscaled_attention<T_OUT> (kernels_api.h:103-108; the reference declares

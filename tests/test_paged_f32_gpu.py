@@ -137,3 +137,35 @@ def test_repeatable(ops):
     order: two runs are bit-identical."""
     wl = _workload([3000, 700, 2222, 64], 4, 4, 128, seed=6)
     assert torch.equal(_run(ops, wl), _run(ops, wl))
+
+
+# ------------------------------------------------------------------------------------------------
+# contiguous fp32 K/V (the reference's async_flash_decode, tensors [B, H, S, D]): the token-major mode
+# ------------------------------------------------------------------------------------------------
+def _flash_case(b, hkv, group, s, d, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(b, hkv * group, 1, d, generator=g)
+    k = torch.randn(b, hkv, s, d, generator=g)
+    v = torch.randn(b, hkv, s, d, generator=g)
+    ref = O.ref_flash_decode(q, k.repeat_interleave(group, dim=1), v.repeat_interleave(group, dim=1))
+    return q, k, v, ref
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("hkv,group", [(1, 1), (2, 2), (2, 3), (8, 4), (2, 8), (3, 1)])
+@pytest.mark.parametrize("s", [1, 15, 16, 17, 130, 777, 2049])
+def test_flash_decode_fp32(ops, d, hkv, group, s):
+    q, k, v, ref = _flash_case(2, hkv, group, s, d, seed=s + hkv + group)
+    before = _launches(ops)
+    out = ops.async_flash_decode(q.cuda(), k.cuda(), v.cuda())
+    torch.cuda.synchronize()
+    assert _launches(ops) == before + 1
+    _check(out, ref, f"flash d {d} hkv {hkv} group {group} s {s}")
+
+
+def test_flash_decode_fp32_long(ops):
+    """One long sequence (many chunks per head, a short last tile) and a batch of short ones."""
+    for b, s in ((1, 50003), (24, 301)):
+        q, k, v, ref = _flash_case(b, 2, 4, s, 128, seed=s)
+        out = ops.async_flash_decode(q.cuda(), k.cuda(), v.cuda())
+        _check(out, ref, f"flash long {b}x{s}")
