@@ -35,6 +35,9 @@ merge_partials_kernel(const float* __restrict__ parts_out, const float* __restri
                       int out_dtype, float* lse) {
   const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
+  // may be launched as a programmatic dependent of the kernel that writes the parts: nothing of theirs
+  // is read before this wait (a no-op after an ordinary launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (row >= rows) return;
   constexpr int VPL = D / 32;
   constexpr float LOG2E = 1.4426950408889634f;
@@ -86,15 +89,21 @@ cudaError_t launch_merge_partials(const float* parts_out, const float* parts_lse
                                   long long rows, int head_dim, void* out, int out_dtype,
                                   float* lse, cudaStream_t st) {
   if (rows == 0) return cudaSuccess;
-  const int grid = (int)((rows + 3) / 4);
   const size_t os = (size_t)rows * head_dim, ls = (size_t)rows;  // dense [P, rows, D] and [P, rows]
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((rows + 3) / 4));
+  cfg.blockDim = dim3(128);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while the kernel in front drains
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   if (head_dim == 64)
-    merge_partials_kernel<64><<<grid, 128, 0, st>>>(parts_out, parts_lse, os, ls, num_parts, rows, out,
-                                                    out_dtype, lse);
-  else
-    merge_partials_kernel<128><<<grid, 128, 0, st>>>(parts_out, parts_lse, os, ls, num_parts, rows, out,
-                                                     out_dtype, lse);
-  return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, merge_partials_kernel<64>, parts_out, parts_lse, os, ls, num_parts, rows, out,
+                              out_dtype, lse);
+  return cudaLaunchKernelEx(&cfg, merge_partials_kernel<128>, parts_out, parts_lse, os, ls, num_parts, rows, out,
+                            out_dtype, lse);
 }
 
 }  // namespace b200

@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
     mbar_fence_init();
   }
   __syncwarp();
+  asm volatile("griddepcontrol.launch_dependents;");  // the merge may be scheduled; it waits for this grid's end
   const uint64_t policy = l2_policy_evict_first();
   const size_t rows_total = (size_t)a.S * a.Hq;
 
