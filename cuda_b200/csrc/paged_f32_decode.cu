@@ -29,6 +29,7 @@
 //
 // Waits are bounded (mbar_wait); a warp whose wait runs out records CUDA_LLM_ST_TIMEOUT in the status
 // word, waits (bounded) for its own copies still in flight and returns.
+#include <cstdlib>
 #include <type_traits>
 
 #include "paged_decode_kernel.cuh"
@@ -58,6 +59,7 @@ struct PagedF32Args {
   int seq_len;        // token-major mode: tokens of every sequence (bt and ctx are null)
   long long n_items;
   float scale_log2;
+  int stall_test;     // failure-path test: the copy of the first K slab of sequence 0 is announced and never sent
 };
 
 // (chunk_pages, n_splits) for a launch: about kF32TargetItems items when every sequence is full, chunks of
@@ -187,7 +189,8 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
     const uint32_t slot = iseq % kF32Slots;
     if (lane == 0) {
       mbar_arrive_expect_tx(bar0 + 8 * slot, bytes);
-      bulk_g2s_hint(ring_u32 + slot * SLOT, src, bytes, bar0 + 8 * slot, policy);
+      if (!(a.stall_test && (it_s | it_kvh | it_first_blk | it_page | it_kv) == 0))  // first K slab of the launch
+        bulk_g2s_hint(ring_u32 + slot * SLOT, src, bytes, bar0 + 8 * slot, policy);
     }
     ++iseq;
     it_kv ^= 1;
@@ -222,7 +225,7 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
     // ------------------------------------------------------------ K slab: scores of 16 tokens
     {
       const uint32_t slot = cseq % kF32Slots;
-      if (!mbar_wait(bar0 + 8 * slot, (cseq / kF32Slots) & 1, 0)) {
+      if (!mbar_wait(bar0 + 8 * slot, (cseq / kF32Slots) & 1, a.stall_test)) {
         give_up();
         return;
       }
@@ -324,7 +327,7 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
     // ------------------------------------------------------------ V slab: O += P V
     {
       const uint32_t slot = cseq % kF32Slots;
-      if (!mbar_wait(bar0 + 8 * slot, (cseq / kF32Slots) & 1, 0)) {
+      if (!mbar_wait(bar0 + 8 * slot, (cseq / kF32Slots) & 1, a.stall_test)) {
         give_up();
         return;
       }
@@ -459,6 +462,10 @@ cudaError_t run_paged_f32_decode(bool paged, const void* q, const void* k, const
   a.n_rg = (a.group + 3) / 4;
   a.n_items = (long long)S * Hkv * a.n_splits * a.n_rg;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  {  // CUDA_LLM_TEST_STALL=1: the failure-path test of this kernel (its entry points carry no flags word)
+    const char* env = getenv("CUDA_LLM_TEST_STALL");
+    a.stall_test = (env && env[0] == '1') ? 1 : 0;
+  }
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   const size_t rows = (size_t)S * Hq;
   a.status = reinterpret_cast<uint32_t*>(ws);

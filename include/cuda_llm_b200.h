@@ -288,7 +288,10 @@ int cuda_llm_decode_tcgen05_counters(uint64_t* launches, uint32_t* wait_timeouts
 
 /* No counterpart in the reference.  Calls of cuda_llm_paged_attention (fp32 cache, pages of 16 tokens)
  * and cuda_llm_flash_decode (fp32 K/V) by this process that ran on the bulk-copy fp32 kernel; other
- * fp32 shapes run on the plain split-KV kernel. */
+ * fp32 shapes run on the plain split-KV kernel.  Failure-path test of that kernel (its entry points
+ * carry no flags word): with CUDA_LLM_TEST_STALL=1 in the environment the first copy of a launch is
+ * announced and never sent and every wait gives up after a few thousand polls; the wait runs out, the
+ * warp returns, CUDA_LLM_ST_TIMEOUT is set in the workspace's status word, nothing faults or hangs. */
 int cuda_llm_paged_attention_f32_launches(uint64_t* launches);
 
 /* Replaces dispatch_fused_microscaled_attention<T_OUT> (kernels_api.h:103-108; the reference declares

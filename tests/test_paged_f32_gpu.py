@@ -169,3 +169,35 @@ def test_flash_decode_fp32_long(ops):
         q, k, v, ref = _flash_case(b, 2, 4, s, 128, seed=s)
         out = ops.async_flash_decode(q.cuda(), k.cuda(), v.cuda())
         _check(out, ref, f"flash long {b}x{s}")
+
+
+def test_bounded_wait_runs_out_and_the_context_survives(ops, monkeypatch):
+    """CUDA_LLM_TEST_STALL=1: the first copy of the launch is announced and never sent.  The wait must run
+    out, the call must return, the status word must say CUDA_LLM_ST_TIMEOUT, and the next call on the same
+    workspace must be bit-identical to the call before."""
+    from cuda_b200 import _lib as L
+    wl = _workload([3000, 700, 2222, 64], 4, 4, 128, seed=6).to("cuda")
+    n, hq, d = wl.query.shape
+    lib = L.load()
+    need = lib.cuda_llm_dense_decode_workspace_bytes(n, hq, 4, d, wl.block_tables.shape[1] * 16)
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+
+    def call():
+        out = torch.empty_like(wl.query)
+        L.check(lib.cuda_llm_paged_attention(wl.query.data_ptr(), wl.key_cache.data_ptr(), wl.value_cache.data_ptr(),
+                                             wl.block_tables.data_ptr(), wl.context_lens.data_ptr(), out.data_ptr(),
+                                             n, hq, 4, d, 16, wl.block_tables.shape[1], wl.key_cache.shape[0],
+                                             wl.softmax_scale, L.F32, ws.data_ptr(), ws.numel(), None), "paged_attention")
+        torch.cuda.synchronize()                            # returns: nothing hangs
+        return out
+
+    ref = call()
+    assert ops.decode_status(ws) == 0
+    monkeypatch.setenv("CUDA_LLM_TEST_STALL", "1")
+    call()
+    assert ops.decode_status(ws) & L.ST_TIMEOUT
+    monkeypatch.delenv("CUDA_LLM_TEST_STALL")
+    ws[:4] = 0
+    again = call()
+    assert ops.decode_status(ws) == 0
+    assert torch.equal(again, ref)
