@@ -38,7 +38,7 @@ if ROOT not in sys.path:
 
 WORKLOADS = {"cfg1": 1, "cfg2": 2, "cfg3": 3, "cfg4": 4, "cfg5": 5}
 # secondary lines for the unquantised entry points (same Llama-3-8B head shape, bf16 K/V)
-AUX_WORKLOADS = ("pa16", "pa32", "fd16", "fd32", "prefill", "mxattn")
+AUX_WORKLOADS = ("pa16", "pa32", "fd16", "fd32", "prefill", "mxattn", "kvappend")
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode-kernel launch,
@@ -209,6 +209,50 @@ def aux_workload(args, rank, world, local):
                                            "kernel": "gqa_prefill_sm100_kernel" if (args.workload == "prefill" and os.environ.get("CUDA_LLM_PREFILL_KERNEL") != "warp_mma") else "gqa_prefill_kernel",
                                            "traffic": None},
                               "gpu_launches": steps}), flush=True)
+        return
+    if args.workload == "kvappend":
+        # quantise-and-store of new K/V tokens into the paged cache (the step in front of the decode path):
+        # a prefill's worth of tokens [n, Hkv, D] bf16 -> E4M3 codes + per-token fp32 scales, pages of 16 tokens
+        # in a shuffled pool, every sequence page-aligned
+        n_seq = args.batch or 4
+        seq = int(4096 * args.ctx_scale)
+        n, hkv, d, page = n_seq * seq, 8, 128, 16
+        k_new = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16).to(dev)
+        v_new = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16).to(dev)
+        pages = n_seq * ((seq + page - 1) // page)
+        perm = torch.randperm(pages, generator=g).to(torch.int32)
+        tok = torch.arange(n)
+        page_of = (tok // seq) * ((seq + page - 1) // page) + (tok % seq) // page
+        slot_block = perm[page_of].to(torch.int32).to(dev)
+        slot_offset = ((tok % seq) % page).to(torch.int32).to(dev)
+        kc = torch.zeros(pages, hkv, d, page, dtype=torch.uint8, device=dev)
+        vc = torch.zeros_like(kc)
+        ksc = torch.zeros(pages, hkv, page, dtype=torch.float32, device=dev)
+        vsc = torch.zeros_like(ksc)
+        fn = lambda: ops.kv_cache_append(k_new, v_new, slot_block, slot_offset, kc, vc, ksc, vsc)
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        peak, peak_src = measured_peak()
+        moved = 2 * n * hkv * (d * 2 + d + 4)   # bf16 in, one code byte per element and one fp32 scale per token out
+        if rank == 0:
+            print(json.dumps({"metric": "kv_append_hbm_throughput", "value": moved / (ms * 1e-3) / 1e12, "unit": "TB/s",
+                              "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                              "higher_is_better": True, "dtype": "bf16 -> e4m3 + f32 scale", "data": "synthetic",
+                              "config": {"workload": "kvappend_prefill_llama8b", "tokens": n, "kv_heads": hkv, "head_dim": d,
+                                         "page_size": page, "bytes_moved": moved,
+                                         "l2": "the cache written by one step is re-read by nothing; inputs of %d MB" % (4 * n * hkv * d // 2 ** 20)},
+                              "roofline": {"bound": "hbm", "achieved": moved / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                                           "frac": moved / (ms * 1e-3) / 1e9 / peak, "peak_source": peak_src,
+                                           "kernel": "kv_append_kernel"},
+                              "gpu_launches": args.steps}), flush=True)
         return
     if args.workload in ("pa16", "pa32"):  # paged_attention over a bf16 / an fp32 cache
         cdt = torch.bfloat16 if args.workload == "pa16" else torch.float32

@@ -5,7 +5,8 @@
 //   per-token fp32 scale : scale = max(amax / 448, 1e-8); code = E4M3(x / scale), round to nearest even
 //   E8M0 block scale     : e = floor(log2(amax_block)) - emax (8 for E4M3, 2 for E2M1), code = x / 2^e
 //   per-head fp32 scale  : the given scale is used, code = E4M3(x / scale)
-// One warp per (token, KV head); lanes split head_dim; codes go to cache[block][head][d][offset].
+// One warp per (token, KV head, K | V) quantises; lanes split head_dim; codes go to cache[block][head][d][offset],
+// as 16-byte rows of 16 tokens where the new tokens fill whole pages.
 #include "paged_decode_kernel.cuh"
 
 namespace b200 {
@@ -22,6 +23,8 @@ struct AppendArgs {
   uint32_t* status;  // may be null
   int n, Hkv, page, num_blocks, in_dtype, v_format, scale_mode;
   int seq_len;  // 0: source rows are [n, Hkv, D]; > 0: source is [n / seq_len, Hkv, seq_len, D] (prefill layout)
+  int aligned;  // set by the launcher: caches and scales allow 16-byte rows
+  int src_vec;  // set by the launcher: the source tensors allow 8-byte loads
 };
 
 __device__ __forceinline__ uint32_t quant_e4m3_byte(float y) { return f32x2_to_e4m3x2(y, 0.f) & 0xffu; }
@@ -40,32 +43,56 @@ __device__ __forceinline__ uint32_t quant_e2m1_nibble(float y) {
   return c | ((__float_as_uint(y) >> 31) << 3);
 }
 
-template <int D>
-__global__ void __launch_bounds__(128) kv_append_kernel(const AppendArgs a) {
-  constexpr int E = D / 32;  // elements per lane: lane owns d = lane*E .. lane*E+E-1 (E = 2 or 4)
-  const int lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (item >= 2LL * a.n * a.Hkv) return;
-  const int is_v = (int)(item & 1);
-  const int h = (int)((item >> 1) % a.Hkv);
-  const int tok = (int)((item >> 1) / a.Hkv);
-  const int blk = a.slot_block[tok], off = a.slot_offset[tok];
-  if (blk < 0 || blk >= a.num_blocks || off < 0 || off >= a.page) {
-    if (a.status && lane == 0) atomicOr(a.status, CUDA_LLM_ST_BAD_BLOCK);
-    return;
+// E consecutive elements of a source row as fp32 (one vector load for the 16-bit types)
+template <int E>
+__device__ __forceinline__ void load_elems(const void* src, int dtype, size_t idx, bool vec, float (&x)[E]) {
+  if (!vec) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) x[e] = load_q_elem(src, dtype, idx + e);
+  } else if (dtype == CUDA_LLM_F32) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) x[e] = reinterpret_cast<const float*>(src)[idx + e];
+  } else {
+    uint32_t w[E / 2];
+    if (E == 4) {
+      const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(src) + idx);
+      w[0] = v.x;
+      w[E / 2 - 1] = v.y;
+    } else {
+      w[0] = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(src) + idx);
+    }
+#pragma unroll
+    for (int e = 0; e < E; e += 2) {
+      if (dtype == CUDA_LLM_F16) {
+        x[e] = f16x2_lo(w[e / 2]);
+        x[e + 1] = f16x2_hi(w[e / 2]);
+      } else {
+        x[e] = __uint_as_float(w[e / 2] << 16);
+        x[e + 1] = __uint_as_float(w[e / 2] & 0xffff0000u);
+      }
+    }
   }
+}
+
+// One token row of one head, quantised by a warp: lane owns d = lane*E .. lane*E+E-1.  Returns the lane's
+// code bytes packed little-endian (E bytes of E4M3, E/2 bytes of nibble pairs for E2M1), the per-token fp32
+// scale (SCALE_PER_TOKEN) and the E8M0 byte of the lane's 32-element block (SCALE_MX_E8M0).
+template <int D>
+__device__ __forceinline__ uint32_t quantise_row(const AppendArgs& a, long long tok, int h, int is_v, int blk, int lane,
+                                                 float& tok_scale, uint32_t& eb_out) {
+  constexpr int E = D / 32;
   const void* src = is_v ? a.v_new : a.k_new;
   float x[E];
   const size_t src_row = a.seq_len > 0 ? ((size_t)(tok / a.seq_len) * a.Hkv + h) * a.seq_len + (tok % a.seq_len)
                                        : (size_t)tok * a.Hkv + h;
-#pragma unroll
-  for (int e = 0; e < E; ++e) x[e] = load_q_elem(src, a.in_dtype, src_row * D + lane * E + e);
+  load_elems<E>(src, a.in_dtype, src_row * D + lane * E, a.src_vec != 0, x);
   float amax = 0.f;
 #pragma unroll
   for (int e = 0; e < E; ++e) amax = fmaxf(amax, fabsf(x[e]));
   const bool fp4 = is_v && a.v_format == CUDA_LLM_KV_FP4_E2M1;
-  uint8_t* cache = is_v ? a.vc : a.kc;
-  void* scale = is_v ? a.vs : a.ks;
+  const void* scale = is_v ? a.vs : a.ks;
+  tok_scale = 0.f;
+  eb_out = 0;
   if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0) {
     // a 32-element block = 32/E consecutive lanes
 #pragma unroll
@@ -74,9 +101,7 @@ __global__ void __launch_bounds__(128) kv_append_kernel(const AppendArgs a) {
     const int ef = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;  // floor(log2(amax))
     const int eb = min(254, max(0, ef - (fp4 ? 2 : 8) + 127));
     const float inv = __uint_as_float((uint32_t)(254 - eb) << 23);      // 2^-(eb-127); eb in [0,254] -> exact except eb=254
-    const int b = (lane * E) / 32;
-    if ((lane * E) % 32 == 0)
-      reinterpret_cast<uint8_t*>(scale)[(((size_t)blk * a.Hkv + h) * (D / 32) + b) * a.page + off] = (uint8_t)eb;
+    eb_out = (uint32_t)eb;
 #pragma unroll
     for (int e = 0; e < E; ++e) x[e] = (eb == 0) ? x[e] * 1.7014118346046923e38f : x[e] * inv;
   } else {
@@ -85,7 +110,7 @@ __global__ void __launch_bounds__(128) kv_append_kernel(const AppendArgs a) {
     float sc;
     if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN) {
       sc = fmaxf(__fdiv_rn(amax, 448.f), 1e-8f);
-      if (lane == 0) reinterpret_cast<float*>(scale)[((size_t)blk * a.Hkv + h) * a.page + off] = sc;
+      tok_scale = sc;
     } else if (a.scale_mode == CUDA_LLM_SCALE_PER_BLOCK) {
       sc = reinterpret_cast<const float*>(scale)[(size_t)blk * a.Hkv + h];
     } else {
@@ -94,24 +119,193 @@ __global__ void __launch_bounds__(128) kv_append_kernel(const AppendArgs a) {
 #pragma unroll
     for (int e = 0; e < E; ++e) x[e] = __fdiv_rn(x[e], sc);
   }
+  uint32_t packed = 0;
+  if (!fp4) {
+#pragma unroll
+    for (int e = 0; e < E; e += 2) packed |= f32x2_to_e4m3x2(x[e], x[e + 1]) << (8 * e);
+  } else {
+#pragma unroll
+    for (int e = 0; e < E; e += 2) packed |= (quant_e2m1_nibble(x[e]) | (quant_e2m1_nibble(x[e + 1]) << 4)) << (4 * e);
+  }
+  return packed;
+}
+
+// Few new tokens (a decode step appends one per sequence): one warp per (token, KV head, K | V), every code
+// byte stored on its own.
+template <int D>
+__global__ void __launch_bounds__(128) kv_append_token_kernel(const AppendArgs a) {
+  constexpr int E = D / 32;
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= 2LL * a.n * a.Hkv) return;
+  const int is_v = (int)(item & 1);
+  const int h = (int)((item >> 1) % a.Hkv);
+  const long long tok = (item >> 1) / a.Hkv;
+  const int blk = a.slot_block[tok], off = a.slot_offset[tok];
+  if (blk < 0 || blk >= a.num_blocks || off < 0 || off >= a.page) {
+    if (a.status && lane == 0) atomicOr(a.status, CUDA_LLM_ST_BAD_BLOCK);
+    return;
+  }
+  float tsc;
+  uint32_t eb;
+  const uint32_t packed = quantise_row<D>(a, tok, h, is_v, blk, lane, tsc, eb);
+  const bool fp4 = is_v && a.v_format == CUDA_LLM_KV_FP4_E2M1;
+  uint8_t* cache = is_v ? a.vc : a.kc;
+  void* scale = is_v ? a.vs : a.ks;
+  if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN && lane == 0)
+    reinterpret_cast<float*>(scale)[((size_t)blk * a.Hkv + h) * a.page + off] = tsc;
+  if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0 && (lane * E) % 32 == 0)
+    reinterpret_cast<uint8_t*>(scale)[(((size_t)blk * a.Hkv + h) * (D / 32) + (lane * E) / 32) * a.page + off] = (uint8_t)eb;
   if (!fp4) {
     uint8_t* dst = cache + (((size_t)blk * a.Hkv + h) * D + lane * E) * a.page + off;
 #pragma unroll
-    for (int e = 0; e < E; ++e) dst[(size_t)e * a.page] = (uint8_t)quant_e4m3_byte(x[e]);
+    for (int e = 0; e < E; ++e) dst[(size_t)e * a.page] = (uint8_t)(packed >> (8 * e));
   } else {
     uint8_t* dst = cache + (((size_t)blk * a.Hkv + h) * (D / 2) + lane * (E / 2)) * a.page + off;
 #pragma unroll
-    for (int e = 0; e < E; e += 2)
-      dst[(size_t)(e / 2) * a.page] = (uint8_t)(quant_e2m1_nibble(x[e]) | (quant_e2m1_nibble(x[e + 1]) << 4));
+    for (int e = 0; e < E / 2; ++e) dst[(size_t)e * a.page] = (uint8_t)(packed >> (8 * e));
   }
 }
 
-cudaError_t launch_kv_append(const AppendArgs& a, int D, cudaStream_t st) {
-  const long long items = 2LL * a.n * a.Hkv;
-  if (items == 0) return cudaSuccess;
-  const int grid = (int)((items + 3) / 4);
-  if (D == 64) kv_append_kernel<64><<<grid, 128, 0, st>>>(a);
-  else kv_append_kernel<128><<<grid, 128, 0, st>>>(a);
+// A CTA takes 16 consecutive new tokens of one KV head, K and V.  When the 16 tokens fill 16 consecutive
+// slots of one page (a prefill writes whole pages), their codes are collected in shared memory as
+// [token][head_dim] and written out transposed, 16 bytes (16 tokens) per head_dim row, so that a page slab
+// is written with full-width stores; per-token and E8M0 scales likewise, as rows of 16.  Otherwise (single
+// new tokens of a decode step, ragged ends) every code byte is stored on its own, one warp per token.
+template <int D>
+__global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a) {
+  constexpr int E = D / 32;
+  constexpr int NB = D / 32;
+  __shared__ __align__(16) uint32_t tile[2][16][D / 4];   // codes: [K | V][token][head_dim byte rows]
+  __shared__ __align__(16) float tok_scales[2][16];
+  __shared__ __align__(16) uint8_t mx_scales[2][NB][16];
+  __shared__ int s_fast, s_blk, s_off0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = (int)(blockIdx.x % a.Hkv);
+  const long long t0 = (long long)(blockIdx.x / a.Hkv) * 16;
+  if (warp == 0) {
+    const long long tok = t0 + (lane & 15);
+    bool ok = tok < a.n;
+    const int blk = ok ? a.slot_block[tok] : -1, off = ok ? a.slot_offset[tok] : -1;
+    const int blk0 = __shfl_sync(0xffffffffu, blk, 0), off0 = __shfl_sync(0xffffffffu, off, 0);
+    ok = ok && blk == blk0 && off == off0 + (lane & 15) && blk0 >= 0 && blk0 < a.num_blocks && off0 >= 0 &&
+         (off0 & 15) == 0 && off0 + 16 <= a.page;
+    const bool fast = __all_sync(0xffffffffu, ok) && a.aligned;
+    if (lane == 0) {
+      s_fast = fast ? 1 : 0;
+      s_blk = blk0;
+      s_off0 = off0;
+    }
+  }
+  __syncthreads();
+  const bool fast = s_fast != 0;
+  const bool fp4v = a.v_format == CUDA_LLM_KV_FP4_E2M1;
+#pragma unroll 1
+  for (int i = 0; i < 8; ++i) {  // four tokens per warp, K and V
+    const int tl = warp * 4 + (i >> 1), is_v = i & 1;
+    const long long tok = t0 + tl;
+    if (tok >= a.n) break;
+    int blk = s_blk, off = s_off0 + tl;
+    if (!fast) {
+      blk = a.slot_block[tok];
+      off = a.slot_offset[tok];
+      if (blk < 0 || blk >= a.num_blocks || off < 0 || off >= a.page) {
+        if (a.status && lane == 0) atomicOr(a.status, CUDA_LLM_ST_BAD_BLOCK);
+        continue;
+      }
+    }
+    float tsc;
+    uint32_t eb;
+    const uint32_t packed = quantise_row<D>(a, tok, h, is_v, blk, lane, tsc, eb);
+    const bool fp4 = is_v && fp4v;
+    if (fast) {
+      // E4M3: E bytes at byte row lane*E; E2M1: E/2 bytes at byte row lane*E/2
+      if (!fp4) {
+        if (E == 4) tile[is_v][tl][lane] = packed;
+        else reinterpret_cast<uint16_t*>(&tile[is_v][tl][0])[lane] = (uint16_t)packed;
+      } else {
+        if (E == 4) reinterpret_cast<uint16_t*>(&tile[is_v][tl][0])[lane] = (uint16_t)packed;
+        else reinterpret_cast<uint8_t*>(&tile[is_v][tl][0])[lane] = (uint8_t)packed;
+      }
+      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN && lane == 0) tok_scales[is_v][tl] = tsc;
+      if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0 && (lane * E) % 32 == 0) mx_scales[is_v][(lane * E) / 32][tl] = (uint8_t)eb;
+    } else {
+      uint8_t* cache = is_v ? a.vc : a.kc;
+      void* scale = is_v ? a.vs : a.ks;
+      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN && lane == 0)
+        reinterpret_cast<float*>(scale)[((size_t)blk * a.Hkv + h) * a.page + off] = tsc;
+      if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0 && (lane * E) % 32 == 0)
+        reinterpret_cast<uint8_t*>(scale)[(((size_t)blk * a.Hkv + h) * NB + (lane * E) / 32) * a.page + off] = (uint8_t)eb;
+      if (!fp4) {
+        uint8_t* dst = cache + (((size_t)blk * a.Hkv + h) * D + lane * E) * a.page + off;
+#pragma unroll
+        for (int e = 0; e < E; ++e) dst[(size_t)e * a.page] = (uint8_t)(packed >> (8 * e));
+      } else {
+        uint8_t* dst = cache + (((size_t)blk * a.Hkv + h) * (D / 2) + lane * (E / 2)) * a.page + off;
+#pragma unroll
+        for (int e = 0; e < E / 2; ++e) dst[(size_t)e * a.page] = (uint8_t)(packed >> (8 * e));
+      }
+    }
+  }
+  if (!fast) return;
+  __syncthreads();
+  const int blk = s_blk, off0 = s_off0;
+  const int is_v = warp & 1;
+  if (warp < 2) {
+    // ---- codes: lane takes byte rows 4*lane .. 4*lane+3 of the tile, all 16 tokens
+    const int rows = (is_v && fp4v) ? D / 2 : D;
+    if (4 * lane < rows) {
+      uint32_t o[4][4];  // [row][token quad]
+#pragma unroll
+      for (int tq = 0; tq < 4; ++tq) {
+        const uint32_t w0 = tile[is_v][4 * tq][lane], w1 = tile[is_v][4 * tq + 1][lane];
+        const uint32_t w2 = tile[is_v][4 * tq + 2][lane], w3 = tile[is_v][4 * tq + 3][lane];
+        // 4 x 4 byte transpose: word j of the result = byte j of w0, w1, w2, w3
+        const uint32_t lo01 = prmt(w0, w1, 0x5140), lo23 = prmt(w2, w3, 0x5140);
+        const uint32_t hi01 = prmt(w0, w1, 0x7362), hi23 = prmt(w2, w3, 0x7362);
+        o[0][tq] = prmt(lo01, lo23, 0x5410);
+        o[1][tq] = prmt(lo01, lo23, 0x7632);
+        o[2][tq] = prmt(hi01, hi23, 0x5410);
+        o[3][tq] = prmt(hi01, hi23, 0x7632);
+      }
+      uint8_t* dst = (is_v ? a.vc : a.kc) + (((size_t)blk * a.Hkv + h) * rows + 4 * lane) * a.page + off0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(dst + (size_t)j * a.page) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+    }
+  } else {
+    // ---- scales of the 16 tokens
+    void* scale = is_v ? a.vs : a.ks;
+    if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN) {
+      if (lane < 16) reinterpret_cast<float*>(scale)[((size_t)blk * a.Hkv + h) * a.page + off0 + lane] = tok_scales[is_v][lane];
+    } else if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0) {
+      if (lane < NB * 4) {
+        const int b = lane >> 2, part = lane & 3;
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(scale) + (((size_t)blk * a.Hkv + h) * NB + b) * a.page + off0 + 4 * part) =
+            *reinterpret_cast<const uint32_t*>(&mx_scales[is_v][b][4 * part]);
+      }
+    }
+  }
+}
+
+constexpr int kAppendTileMinTokens = 1024;  // below this the per-token kernel has more warps in flight
+
+cudaError_t launch_kv_append(AppendArgs a, int D, cudaStream_t st) {
+  if (a.n == 0) return cudaSuccess;
+  // full-width rows need 16-byte aligned caches (every page slab then is) and 4-byte aligned scales
+  a.aligned = !(((uintptr_t)a.kc | (uintptr_t)a.vc) & 15) && !(((uintptr_t)a.ks | (uintptr_t)a.vs) & 3) && (a.page % 16 == 0);
+  a.src_vec = !(((uintptr_t)a.k_new | (uintptr_t)a.v_new) & 15);
+  if (a.n < kAppendTileMinTokens || !a.aligned) {
+    const long long items = 2LL * a.n * a.Hkv;
+    const unsigned grid = (unsigned)((items + 3) / 4);
+    if (D == 64) kv_append_token_kernel<64><<<grid, 128, 0, st>>>(a);
+    else kv_append_token_kernel<128><<<grid, 128, 0, st>>>(a);
+    return cudaGetLastError();
+  }
+  const long long groups = ((long long)a.n + 15) / 16;
+  const unsigned grid = (unsigned)(groups * a.Hkv);
+  if (D == 64) kv_append_tile_kernel<64><<<grid, 128, 0, st>>>(a);
+  else kv_append_tile_kernel<128><<<grid, 128, 0, st>>>(a);
   return cudaGetLastError();
 }
 

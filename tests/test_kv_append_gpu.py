@@ -52,6 +52,88 @@ def test_append_is_bit_exact(mode, vfmt, d, page, dtype):
     assert (kc.cpu().permute(0, 3, 1, 2)[untouched] == 0xAA).all()
 
 
+@pytest.mark.parametrize("mode,vfmt", [("per_token", "fp8_e4m3"), ("mx_e8m0", "fp8_e4m3"),
+                                       ("mx_e8m0", "fp4_e2m1"), ("per_head", "fp8_e4m3")])
+@pytest.mark.parametrize("d,page,dtype", [(128, 16, torch.bfloat16), (64, 32, torch.float32), (128, 64, torch.float16),
+                                          (64, 16, torch.bfloat16)])
+def test_append_of_many_tokens_is_bit_exact(mode, vfmt, d, page, dtype):
+    """A prefill's worth of tokens (the kernel that writes whole 16-token rows): a page-aligned sequence
+    (full-width rows), a sequence that starts in the middle of a page (every group of 16 straddles the row
+    grid: byte stores), scattered single tokens and a ragged last group, in one call."""
+    from cuda_b200 import ops
+    torch.manual_seed(5)
+    h = 4
+    n_a, n_b, n_c = 40 * page + 16, 517, 77        # aligned, misaligned by 5 slots, scattered
+    n = n_a + n_b + n_c
+    assert n >= 1024 and n % 16 != 0
+    pages_a, pages_b = (n_a + page - 1) // page, (n_b + 5 + page - 1) // page
+    nb = pages_a + pages_b + 12
+    perm = torch.randperm(nb)
+    blk = torch.empty(n, dtype=torch.int64)
+    off = torch.empty(n, dtype=torch.int64)
+    ta = torch.arange(n_a)
+    blk[:n_a], off[:n_a] = perm[ta // page], ta % page
+    tb = torch.arange(n_b) + 5
+    blk[n_a:n_a + n_b], off[n_a:n_a + n_b] = perm[pages_a + tb // page], tb % page
+    free = perm[pages_a + pages_b:]                                       # 12 pages for the scattered tokens
+    slots = torch.randperm(12 * page)[:n_c]
+    blk[n_a + n_b:], off[n_a + n_b:] = free[slots // page], slots % page
+    mag = torch.exp2(torch.randint(-12, 6, (n, h, d // 32, 1)).float()).expand(n, h, d // 32, 32).reshape(n, h, d)
+    k = (torch.randn(n, h, d) * mag).to(dtype)
+    v = (torch.randn(n, h, d) * mag).to(dtype)
+    k[3] = 0
+    k_head = (k.float().abs().amax(dim=(0, 2)) / 448.0).clamp_min(1e-8)
+    v_head = (v.float().abs().amax(dim=(0, 2)) / 448.0).clamp_min(1e-8)
+    kc_ref, ks_ref = O.quantize_tokens(k.float(), "fp8_e4m3", mode, k_head)
+    vc_ref, vs_ref = O.quantize_tokens(v.float(), vfmt, mode, v_head)
+    dv = d // 2 if vfmt == "fp4_e2m1" else d
+    kc = torch.full((nb, h, d, page), 0xAA, dtype=torch.uint8, device="cuda")
+    vc = torch.full((nb, h, dv, page), 0xAA, dtype=torch.uint8, device="cuda")
+    if mode == "per_token":
+        ks = torch.full((nb, h, page), -1.0, device="cuda"); vs = ks.clone()
+    elif mode == "mx_e8m0":
+        ks = torch.full((nb, h, d // 32, page), 0xAA, dtype=torch.uint8, device="cuda"); vs = ks.clone()
+    else:
+        ks = k_head.cuda(); vs = v_head.cuda()
+    ops.kv_cache_append(k.cuda(), v.cuda(), blk.to(torch.int32).cuda(), off.to(torch.int32).cuda(), kc, vc, ks, vs)
+    torch.cuda.synchronize()
+    assert torch.equal(kc.cpu()[blk, :, :, off], kc_ref)
+    assert torch.equal(vc.cpu()[blk, :, :, off], vc_ref)
+    if mode == "per_token":
+        assert torch.equal(ks.cpu()[blk, :, off], ks_ref) and torch.equal(vs.cpu()[blk, :, off], vs_ref)
+    elif mode == "mx_e8m0":
+        assert torch.equal(ks.cpu()[blk, :, :, off], ks_ref) and torch.equal(vs.cpu()[blk, :, :, off], vs_ref)
+    untouched = torch.ones(nb, page, dtype=torch.bool)
+    untouched[blk, off] = False
+    assert (kc.cpu().permute(0, 3, 1, 2)[untouched] == 0xAA).all()
+    assert (vc.cpu().permute(0, 3, 1, 2)[untouched] == 0xAA).all()
+    if mode == "mx_e8m0":
+        assert (ks.cpu().permute(0, 3, 1, 2)[untouched] == 0xAA).all()
+    elif mode == "per_token":
+        assert (ks.cpu().permute(0, 2, 1)[untouched] == -1.0).all()
+
+
+def test_append_of_many_tokens_reports_a_bad_slot():
+    from cuda_b200 import _lib as L
+    n, h, d, page, nb = 2048, 2, 128, 16, 130
+    k = torch.randn(n, h, d, device="cuda", dtype=torch.bfloat16)
+    t = torch.arange(n)
+    blk, off = (t // page).to(torch.int32), (t % page).to(torch.int32)
+    blk[16 * 7 + 3] = nb + 5                                    # one token of one group points outside the pool
+    kc = torch.zeros(nb, h, d, page, dtype=torch.uint8, device="cuda"); vc = torch.zeros_like(kc)
+    ks = torch.zeros(nb, h, page, device="cuda"); vs = torch.zeros_like(ks)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    blk_d, off_d = blk.cuda(), off.cuda()
+    L.check(L.load().cuda_llm_kv_append(k.data_ptr(), k.data_ptr(), blk_d.data_ptr(), off_d.data_ptr(), kc.data_ptr(),
+                                        vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), n, h, d, page, nb, L.BF16,
+                                        L.KV_FP8_E4M3, L.SCALE_PER_TOKEN, status.data_ptr(), None), "kv_append")
+    torch.cuda.synchronize()
+    assert status.item() & L.ST_BAD_BLOCK
+    # the other 15 tokens of that group and every other group were written
+    written = (ks.cpu() != 0).permute(0, 2, 1)[..., 0]          # [nb, page]
+    assert written[:n // page].sum().item() == n - 1
+
+
 def test_append_then_decode_round_trip():
     """Fill a cache token by token with the append kernel, then attend over it: same result as the
     oracle on the host-quantised cache."""
