@@ -43,24 +43,40 @@ __device__ __forceinline__ uint32_t quant_e2m1_nibble(float y) {
   return c | ((__float_as_uint(y) >> 31) << 3);
 }
 
-// E consecutive elements of a source row as fp32 (one vector load for the 16-bit types)
+// E consecutive elements of a source row, as loaded (one vector load where the tensors allow it) ...
 template <int E>
-__device__ __forceinline__ void load_elems(const void* src, int dtype, size_t idx, bool vec, float (&x)[E]) {
-  if (!vec) {
-#pragma unroll
-    for (int e = 0; e < E; ++e) x[e] = load_q_elem(src, dtype, idx + e);
-  } else if (dtype == CUDA_LLM_F32) {
-#pragma unroll
-    for (int e = 0; e < E; ++e) x[e] = reinterpret_cast<const float*>(src)[idx + e];
-  } else {
-    uint32_t w[E / 2];
+__device__ __forceinline__ uint4 load_raw(const void* src, int dtype, size_t idx, bool vec) {
+  uint4 r = make_uint4(0u, 0u, 0u, 0u);
+  if (!vec) {  // element by element, kept as fp32 bits
+    r.x = __float_as_uint(load_q_elem(src, dtype, idx));
+    r.y = __float_as_uint(load_q_elem(src, dtype, idx + 1));
     if (E == 4) {
-      const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(src) + idx);
-      w[0] = v.x;
-      w[E / 2 - 1] = v.y;
-    } else {
-      w[0] = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(src) + idx);
+      r.z = __float_as_uint(load_q_elem(src, dtype, idx + 2));
+      r.w = __float_as_uint(load_q_elem(src, dtype, idx + 3));
     }
+  } else if (dtype == CUDA_LLM_F32) {
+    if (E == 4) {
+      r = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(src) + idx);
+    } else {
+      const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const float*>(src) + idx);
+      r.x = v.x; r.y = v.y;
+    }
+  } else if (E == 4) {
+    const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(src) + idx);
+    r.x = v.x; r.y = v.y;
+  } else {
+    r.x = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(src) + idx);
+  }
+  return r;
+}
+// ... and widened to fp32
+template <int E>
+__device__ __forceinline__ void raw_to_float(const uint4& r, int dtype, bool vec, float (&x)[E]) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  if (!vec || dtype == CUDA_LLM_F32) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) x[e] = __uint_as_float(w[e]);
+  } else {
 #pragma unroll
     for (int e = 0; e < E; e += 2) {
       if (dtype == CUDA_LLM_F16) {
@@ -73,19 +89,19 @@ __device__ __forceinline__ void load_elems(const void* src, int dtype, size_t id
     }
   }
 }
+__device__ __forceinline__ size_t source_row(const AppendArgs& a, long long tok, int h) {
+  return a.seq_len > 0 ? ((size_t)(tok / a.seq_len) * a.Hkv + h) * a.seq_len + (tok % a.seq_len) : (size_t)tok * a.Hkv + h;
+}
 
 // One token row of one head, quantised by a warp: lane owns d = lane*E .. lane*E+E-1.  Returns the lane's
 // code bytes packed little-endian (E bytes of E4M3, E/2 bytes of nibble pairs for E2M1), the per-token fp32
 // scale (SCALE_PER_TOKEN) and the E8M0 byte of the lane's 32-element block (SCALE_MX_E8M0).
 template <int D>
-__device__ __forceinline__ uint32_t quantise_row(const AppendArgs& a, long long tok, int h, int is_v, int blk, int lane,
+__device__ __forceinline__ uint32_t quantise_row(const AppendArgs& a, const uint4& raw, int h, int is_v, int blk, int lane,
                                                  float& tok_scale, uint32_t& eb_out) {
   constexpr int E = D / 32;
-  const void* src = is_v ? a.v_new : a.k_new;
   float x[E];
-  const size_t src_row = a.seq_len > 0 ? ((size_t)(tok / a.seq_len) * a.Hkv + h) * a.seq_len + (tok % a.seq_len)
-                                       : (size_t)tok * a.Hkv + h;
-  load_elems<E>(src, a.in_dtype, src_row * D + lane * E, a.src_vec != 0, x);
+  raw_to_float<E>(raw, a.in_dtype, a.src_vec != 0, x);
   float amax = 0.f;
 #pragma unroll
   for (int e = 0; e < E; ++e) amax = fmaxf(amax, fabsf(x[e]));
@@ -148,7 +164,8 @@ __global__ void __launch_bounds__(128) kv_append_token_kernel(const AppendArgs a
   }
   float tsc;
   uint32_t eb;
-  const uint32_t packed = quantise_row<D>(a, tok, h, is_v, blk, lane, tsc, eb);
+  const uint4 raw = load_raw<E>(is_v ? a.v_new : a.k_new, a.in_dtype, source_row(a, tok, h) * D + lane * E, a.src_vec != 0);
+  const uint32_t packed = quantise_row<D>(a, raw, h, is_v, blk, lane, tsc, eb);
   const bool fp4 = is_v && a.v_format == CUDA_LLM_KV_FP4_E2M1;
   uint8_t* cache = is_v ? a.vc : a.kc;
   void* scale = is_v ? a.vs : a.ks;
@@ -167,15 +184,41 @@ __global__ void __launch_bounds__(128) kv_append_token_kernel(const AppendArgs a
   }
 }
 
-// A CTA takes 16 consecutive new tokens of one KV head, K and V.  When the 16 tokens fill 16 consecutive
-// slots of one page (a prefill writes whole pages), their codes are collected in shared memory as
-// [token][head_dim] and written out transposed, 16 bytes (16 tokens) per head_dim row, so that a page slab
-// is written with full-width stores; per-token and E8M0 scales likewise, as rows of 16.  Otherwise (single
-// new tokens of a decode step, ragged ends) every code byte is stored on its own, one warp per token.
+// x / sc, correctly rounded, for many x and one sc: y = RN(1 / sc) once, then q = RN(x y), r = x - q sc (exact,
+// one FMA), q' = RN(q + r y).  q' equals the IEEE quotient whenever y is the correctly rounded reciprocal, q
+// is within an ulp of the quotient and nothing leaves the normal range (Markstein's division theorem); the one
+// divisor the theorem excludes (a significand of all ones) and divisors whose reciprocal is not normal take
+// the IEEE division.  Callers guarantee sc > 0 and |x / sc| far below the overflow threshold.
+struct Divisor {
+  float sc, y;
+  bool fast;
+  __device__ __forceinline__ explicit Divisor(float s) : sc(s) {
+    asm("rcp.rn.f32 %0, %1;" : "=f"(y) : "f"(s));  // IEEE reciprocal, round to nearest even
+    const uint32_t b = __float_as_uint(s), e = (b >> 23) & 0xffu, ey = (__float_as_uint(y) >> 23) & 0xffu;
+    fast = (b & 0x7fffffu) != 0x7fffffu && e >= 1 && e <= 253 && ey >= 1 && ey <= 253;
+  }
+  __device__ __forceinline__ float div(float x) const {
+    if (!fast) return __fdiv_rn(x, sc);
+    const float q = __fmul_rn(x, y);
+    const float qq = __fmaf_rn(__fmaf_rn(-q, sc, x), y, q);
+    // the divisor is positive, so the quotient has the sign of x; the sums above turn -0 into +0
+    return __uint_as_float((__float_as_uint(qq) & 0x7fffffffu) | (__float_as_uint(x) & 0x80000000u));
+  }
+};
+
+// A CTA takes 16 consecutive new tokens of one KV head, K and V: 32 rows of head_dim values.  A row is
+// quantised by head_dim / 16 adjacent lanes, 16 values each (four or eight rows per warp at a time, so the
+// per-row work -- the maximum, its scale, a reciprocal -- is shared by 16 values per lane instead of 4).
+// When the 16 tokens fill 16 consecutive slots of one page (a prefill writes whole pages), their codes are
+// collected in shared memory as [token][head_dim] and written out transposed, 16 bytes (16 tokens) per
+// head_dim row, so that a page slab is written with full-width stores; per-token and E8M0 scales likewise, as
+// rows of 16.  Otherwise (ragged ends, sequences that start inside a page) every code byte is stored on its own.
 template <int D>
 __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a) {
-  constexpr int E = D / 32;
   constexpr int NB = D / 32;
+  constexpr int LPR = D / 16;        // lanes per row
+  constexpr int RPP = 32 / LPR;      // rows per warp and pass
+  constexpr int PASSES = 32 / (4 * RPP);
   __shared__ __align__(16) uint32_t tile[2][16][D / 4];   // codes: [K | V][token][head_dim byte rows]
   __shared__ __align__(16) float tok_scales[2][16];
   __shared__ __align__(16) uint8_t mx_scales[2][NB][16];
@@ -197,53 +240,139 @@ __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a)
       s_off0 = off0;
     }
   }
+  const int sub = lane % LPR, d0 = sub * 16;
+  const bool vec = a.src_vec != 0;
+  const bool wide = vec && a.in_dtype == CUDA_LLM_F32;
+  // the rows of this lane (row r: token r / 2, K for even r, V for odd r), all requested before the first is used
+  uint4 raw[PASSES][4];
+#pragma unroll
+  for (int ps = 0; ps < PASSES; ++ps) {
+    const int r = (ps * 4 + warp) * RPP + lane / LPR;
+    const long long tok = t0 + (r >> 1);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) raw[ps][j] = make_uint4(0u, 0u, 0u, 0u);
+    if (tok < a.n) {
+      const void* src = (r & 1) ? a.v_new : a.k_new;
+      const size_t idx = source_row(a, tok, h) * D + d0;
+      if (!vec) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          raw[ps][j] = make_uint4(__float_as_uint(load_q_elem(src, a.in_dtype, idx + 4 * j)),
+                                  __float_as_uint(load_q_elem(src, a.in_dtype, idx + 4 * j + 1)),
+                                  __float_as_uint(load_q_elem(src, a.in_dtype, idx + 4 * j + 2)),
+                                  __float_as_uint(load_q_elem(src, a.in_dtype, idx + 4 * j + 3)));
+      } else if (wide) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) raw[ps][j] = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(src) + idx)[j];
+      } else {
+        raw[ps][0] = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(src) + idx)[0];
+        raw[ps][1] = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(src) + idx)[1];
+      }
+    }
+  }
   __syncthreads();
   const bool fast = s_fast != 0;
   const bool fp4v = a.v_format == CUDA_LLM_KV_FP4_E2M1;
-#pragma unroll 1
-  for (int i = 0; i < 8; ++i) {  // four tokens per warp, K and V
-    const int tl = warp * 4 + (i >> 1), is_v = i & 1;
+#pragma unroll
+  for (int ps = 0; ps < PASSES; ++ps) {
+    const int r = (ps * 4 + warp) * RPP + lane / LPR;
+    const int tl = r >> 1, is_v = r & 1;
     const long long tok = t0 + tl;
-    if (tok >= a.n) break;
+    const bool row_live = tok < a.n;
     int blk = s_blk, off = s_off0 + tl;
-    if (!fast) {
+    bool slot_ok = row_live;
+    if (!fast && row_live) {
       blk = a.slot_block[tok];
       off = a.slot_offset[tok];
-      if (blk < 0 || blk >= a.num_blocks || off < 0 || off >= a.page) {
-        if (a.status && lane == 0) atomicOr(a.status, CUDA_LLM_ST_BAD_BLOCK);
-        continue;
+      slot_ok = blk >= 0 && blk < a.num_blocks && off >= 0 && off < a.page;
+      if (!slot_ok && a.status && sub == 0) atomicOr(a.status, CUDA_LLM_ST_BAD_BLOCK);
+    }
+    // ---- the 16 values of this lane as fp32
+    float x[16];
+    if (!vec || wide) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        x[4 * j] = __uint_as_float(raw[ps][j].x); x[4 * j + 1] = __uint_as_float(raw[ps][j].y);
+        x[4 * j + 2] = __uint_as_float(raw[ps][j].z); x[4 * j + 3] = __uint_as_float(raw[ps][j].w);
+      }
+    } else {
+      const uint32_t w[8] = {raw[ps][0].x, raw[ps][0].y, raw[ps][0].z, raw[ps][0].w,
+                             raw[ps][1].x, raw[ps][1].y, raw[ps][1].z, raw[ps][1].w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (a.in_dtype == CUDA_LLM_F16) {
+          x[2 * j] = f16x2_lo(w[j]);
+          x[2 * j + 1] = f16x2_hi(w[j]);
+        } else {
+          x[2 * j] = __uint_as_float(w[j] << 16);
+          x[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
       }
     }
-    float tsc;
-    uint32_t eb;
-    const uint32_t packed = quantise_row<D>(a, tok, h, is_v, blk, lane, tsc, eb);
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(x[e]));
     const bool fp4 = is_v && fp4v;
-    if (fast) {
-      // E4M3: E bytes at byte row lane*E; E2M1: E/2 bytes at byte row lane*E/2
-      if (!fp4) {
-        if (E == 4) tile[is_v][tl][lane] = packed;
-        else reinterpret_cast<uint16_t*>(&tile[is_v][tl][0])[lane] = (uint16_t)packed;
+    void* scale = is_v ? a.vs : a.ks;
+    float tsc = 0.f;
+    uint32_t eb = 0;
+    if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // a 32-element block = two adjacent lanes
+      amax = fmaxf(amax, 7.888609052210118e-31f);  // 2^-100, as the host recipe clamps
+      const int ef = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;  // floor(log2(amax))
+      eb = (uint32_t)min(254, max(0, ef - (fp4 ? 2 : 8) + 127));
+      const float inv = __uint_as_float((uint32_t)(254 - eb) << 23);      // 2^-(eb-127); eb in [0,254] -> exact except eb=254
+#pragma unroll
+      for (int e = 0; e < 16; ++e) x[e] = (eb == 0) ? x[e] * 1.7014118346046923e38f : x[e] * inv;
+    } else {
+#pragma unroll
+      for (int o = 1; o < LPR; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN) {
+        tsc = fmaxf(__fdiv_rn(amax, 448.f), 1e-8f);
+        const Divisor dv(tsc);  // |x / tsc| <= 448 (1 + 2^-23)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) x[e] = dv.div(x[e]);
       } else {
-        if (E == 4) reinterpret_cast<uint16_t*>(&tile[is_v][tl][0])[lane] = (uint16_t)packed;
-        else reinterpret_cast<uint8_t*>(&tile[is_v][tl][0])[lane] = (uint8_t)packed;
+        const float sc = (a.scale_mode == CUDA_LLM_SCALE_PER_BLOCK)
+                             ? reinterpret_cast<const float*>(scale)[(size_t)(slot_ok ? blk : 0) * a.Hkv + h]
+                             : reinterpret_cast<const float*>(scale)[h];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) x[e] = __fdiv_rn(x[e], sc);
       }
-      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN && lane == 0) tok_scales[is_v][tl] = tsc;
-      if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0 && (lane * E) % 32 == 0) mx_scales[is_v][(lane * E) / 32][tl] = (uint8_t)eb;
+    }
+    // ---- codes: 16 bytes of E4M3, or 8 bytes of E2M1 nibble pairs (low nibble = even d)
+    uint32_t c[4] = {0u, 0u, 0u, 0u};
+    if (!fp4) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        c[j] = f32x2_to_e4m3x2(x[4 * j], x[4 * j + 1]) | (f32x2_to_e4m3x2(x[4 * j + 2], x[4 * j + 3]) << 16);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          c[j] |= (quant_e2m1_nibble(x[8 * j + 2 * e]) | (quant_e2m1_nibble(x[8 * j + 2 * e + 1]) << 4)) << (8 * e);
+    }
+    if (!slot_ok) continue;
+    if (fast) {
+      if (!fp4) *reinterpret_cast<uint4*>(&tile[is_v][tl][d0 / 4]) = make_uint4(c[0], c[1], c[2], c[3]);
+      else *reinterpret_cast<uint2*>(&tile[is_v][tl][d0 / 8]) = make_uint2(c[0], c[1]);
+      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN && sub == 0) tok_scales[is_v][tl] = tsc;
+      if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0 && (sub & 1) == 0) mx_scales[is_v][sub >> 1][tl] = (uint8_t)eb;
     } else {
       uint8_t* cache = is_v ? a.vc : a.kc;
-      void* scale = is_v ? a.vs : a.ks;
-      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN && lane == 0)
+      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN && sub == 0)
         reinterpret_cast<float*>(scale)[((size_t)blk * a.Hkv + h) * a.page + off] = tsc;
-      if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0 && (lane * E) % 32 == 0)
-        reinterpret_cast<uint8_t*>(scale)[(((size_t)blk * a.Hkv + h) * NB + (lane * E) / 32) * a.page + off] = (uint8_t)eb;
+      if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0 && (sub & 1) == 0)
+        reinterpret_cast<uint8_t*>(scale)[(((size_t)blk * a.Hkv + h) * NB + (sub >> 1)) * a.page + off] = (uint8_t)eb;
       if (!fp4) {
-        uint8_t* dst = cache + (((size_t)blk * a.Hkv + h) * D + lane * E) * a.page + off;
+        uint8_t* dst = cache + (((size_t)blk * a.Hkv + h) * D + d0) * a.page + off;
 #pragma unroll
-        for (int e = 0; e < E; ++e) dst[(size_t)e * a.page] = (uint8_t)(packed >> (8 * e));
+        for (int e = 0; e < 16; ++e) dst[(size_t)e * a.page] = (uint8_t)(c[e >> 2] >> (8 * (e & 3)));
       } else {
-        uint8_t* dst = cache + (((size_t)blk * a.Hkv + h) * (D / 2) + lane * (E / 2)) * a.page + off;
+        uint8_t* dst = cache + (((size_t)blk * a.Hkv + h) * (D / 2) + d0 / 2) * a.page + off;
 #pragma unroll
-        for (int e = 0; e < E / 2; ++e) dst[(size_t)e * a.page] = (uint8_t)(packed >> (8 * e));
+        for (int e = 0; e < 8; ++e) dst[(size_t)e * a.page] = (uint8_t)(c[e >> 2] >> (8 * (e & 3)));
       }
     }
   }

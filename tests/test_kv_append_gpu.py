@@ -82,6 +82,7 @@ def test_append_of_many_tokens_is_bit_exact(mode, vfmt, d, page, dtype):
     k = (torch.randn(n, h, d) * mag).to(dtype)
     v = (torch.randn(n, h, d) * mag).to(dtype)
     k[3] = 0
+    k[5, :, ::3] = -0.0                                         # negative zeros keep their sign bit
     k_head = (k.float().abs().amax(dim=(0, 2)) / 448.0).clamp_min(1e-8)
     v_head = (v.float().abs().amax(dim=(0, 2)) / 448.0).clamp_min(1e-8)
     kc_ref, ks_ref = O.quantize_tokens(k.float(), "fp8_e4m3", mode, k_head)
@@ -111,6 +112,34 @@ def test_append_of_many_tokens_is_bit_exact(mode, vfmt, d, page, dtype):
         assert (ks.cpu().permute(0, 3, 1, 2)[untouched] == 0xAA).all()
     elif mode == "per_token":
         assert (ks.cpu().permute(0, 2, 1)[untouched] == -1.0).all()
+
+
+def test_append_quotients_are_ieee_on_fp32_inputs():
+    """The kernel for many tokens divides by the per-token scale through a reciprocal and two fused
+    multiply-adds, which must give the IEEE quotient the oracle's recipe (torch's fp32 division) gives:
+    two million fp32 values with full-width significands, uniform over [-amax, amax] of their token, token maxima
+    over 60 binades, scales whose significand is all ones among them."""
+    from cuda_b200 import ops
+    g = torch.Generator().manual_seed(11)
+    n, h, d, page = 8192, 2, 128, 16
+    amax = torch.exp2(torch.randint(-30, 30, (n, h, 1), generator=g).float()) * (1 + torch.rand(n, h, 1, generator=g))
+    # a scale of 2^k (2 - 2^-23): amax = 448 * that, rounded; the quotient path must still be exact
+    amax[::97] = 448.0 * torch.tensor(1.9999998807907104) * torch.exp2(torch.randint(-20, 10, (len(amax[::97]), h, 1), generator=g).float())
+    k = (torch.rand(n, h, d, generator=g) * 2 - 1) * amax
+    k[..., 0] = amax[..., 0]                                    # the maximum itself is present
+    v = k.flip(0).contiguous()
+    kc_ref, ks_ref = O.quantize_tokens(k, "fp8_e4m3", "per_token", None)
+    vc_ref, vs_ref = O.quantize_tokens(v, "fp8_e4m3", "per_token", None)
+    t = torch.arange(n)
+    blk, off = (t // page).to(torch.int32).cuda(), (t % page).to(torch.int32).cuda()
+    kc = torch.zeros(n // page, h, d, page, dtype=torch.uint8, device="cuda"); vc = torch.zeros_like(kc)
+    ks = torch.zeros(n // page, h, page, device="cuda"); vs = torch.zeros_like(ks)
+    ops.kv_cache_append(k.cuda(), v.cuda(), blk, off, kc, vc, ks, vs)
+    torch.cuda.synchronize()
+    b, o = (t // page), (t % page)
+    assert torch.equal(ks.cpu()[b, :, o], ks_ref) and torch.equal(vs.cpu()[b, :, o], vs_ref)
+    assert torch.equal(kc.cpu()[b, :, :, o], kc_ref)
+    assert torch.equal(vc.cpu()[b, :, :, o], vc_ref)
 
 
 def test_append_of_many_tokens_reports_a_bad_slot():
