@@ -7,6 +7,8 @@
 //   per-head fp32 scale  : the given scale is used, code = E4M3(x / scale)
 // One warp per (token, KV head, K | V) quantises; lanes split head_dim; codes go to cache[block][head][d][offset],
 // as 16-byte rows of 16 tokens where the new tokens fill whole pages.
+#include <type_traits>
+
 #include "paged_decode_kernel.cuh"
 
 namespace b200 {
@@ -213,8 +215,10 @@ struct Divisor {
 // collected in shared memory as [token][head_dim] and written out transposed, 16 bytes (16 tokens) per
 // head_dim row, so that a page slab is written with full-width stores; per-token and E8M0 scales likewise, as
 // rows of 16.  Otherwise (ragged ends, sequences that start inside a page) every code byte is stored on its own.
-template <int D>
+template <int D, int DT, int SMODE>
 __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a) {
+  // DT: source dtype (CUDA_LLM_F32 / F16 / BF16) when the source allows vector loads, -1 for element loads of
+  // any dtype; SMODE: the scale mode.  Compile-time so that the unrolled per-value code has no run-time switches.
   constexpr int NB = D / 32;
   constexpr int LPR = D / 16;        // lanes per row
   constexpr int RPP = 32 / LPR;      // rows per warp and pass
@@ -241,8 +245,8 @@ __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a)
     }
   }
   const int sub = lane % LPR, d0 = sub * 16;
-  const bool vec = a.src_vec != 0;
-  const bool wide = vec && a.in_dtype == CUDA_LLM_F32;
+  constexpr bool vec = DT >= 0;
+  constexpr bool wide = DT == CUDA_LLM_F32;
   // the rows of this lane (row r: token r / 2, K for even r, V for odd r), all requested before the first is used
   uint4 raw[PASSES][4];
 #pragma unroll
@@ -300,7 +304,7 @@ __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a)
                              raw[ps][1].x, raw[ps][1].y, raw[ps][1].z, raw[ps][1].w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        if (a.in_dtype == CUDA_LLM_F16) {
+        if (DT == CUDA_LLM_F16) {
           x[2 * j] = f16x2_lo(w[j]);
           x[2 * j + 1] = f16x2_hi(w[j]);
         } else {
@@ -316,7 +320,7 @@ __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a)
     void* scale = is_v ? a.vs : a.ks;
     float tsc = 0.f;
     uint32_t eb = 0;
-    if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0) {
+    if (SMODE == CUDA_LLM_SCALE_MX_E8M0) {
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // a 32-element block = two adjacent lanes
       amax = fmaxf(amax, 7.888609052210118e-31f);  // 2^-100, as the host recipe clamps
       const int ef = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;  // floor(log2(amax))
@@ -327,13 +331,13 @@ __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a)
     } else {
 #pragma unroll
       for (int o = 1; o < LPR; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN) {
+      if (SMODE == CUDA_LLM_SCALE_PER_TOKEN) {
         tsc = fmaxf(__fdiv_rn(amax, 448.f), 1e-8f);
         const Divisor dv(tsc);  // |x / tsc| <= 448 (1 + 2^-23)
 #pragma unroll
         for (int e = 0; e < 16; ++e) x[e] = dv.div(x[e]);
       } else {
-        const float sc = (a.scale_mode == CUDA_LLM_SCALE_PER_BLOCK)
+        const float sc = (SMODE == CUDA_LLM_SCALE_PER_BLOCK)
                              ? reinterpret_cast<const float*>(scale)[(size_t)(slot_ok ? blk : 0) * a.Hkv + h]
                              : reinterpret_cast<const float*>(scale)[h];
 #pragma unroll
@@ -357,13 +361,13 @@ __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a)
     if (fast) {
       if (!fp4) *reinterpret_cast<uint4*>(&tile[is_v][tl][d0 / 4]) = make_uint4(c[0], c[1], c[2], c[3]);
       else *reinterpret_cast<uint2*>(&tile[is_v][tl][d0 / 8]) = make_uint2(c[0], c[1]);
-      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN && sub == 0) tok_scales[is_v][tl] = tsc;
-      if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0 && (sub & 1) == 0) mx_scales[is_v][sub >> 1][tl] = (uint8_t)eb;
+      if (SMODE == CUDA_LLM_SCALE_PER_TOKEN && sub == 0) tok_scales[is_v][tl] = tsc;
+      if (SMODE == CUDA_LLM_SCALE_MX_E8M0 && (sub & 1) == 0) mx_scales[is_v][sub >> 1][tl] = (uint8_t)eb;
     } else {
       uint8_t* cache = is_v ? a.vc : a.kc;
-      if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN && sub == 0)
+      if (SMODE == CUDA_LLM_SCALE_PER_TOKEN && sub == 0)
         reinterpret_cast<float*>(scale)[((size_t)blk * a.Hkv + h) * a.page + off] = tsc;
-      if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0 && (sub & 1) == 0)
+      if (SMODE == CUDA_LLM_SCALE_MX_E8M0 && (sub & 1) == 0)
         reinterpret_cast<uint8_t*>(scale)[(((size_t)blk * a.Hkv + h) * NB + (sub >> 1)) * a.page + off] = (uint8_t)eb;
       if (!fp4) {
         uint8_t* dst = cache + (((size_t)blk * a.Hkv + h) * D + d0) * a.page + off;
@@ -405,9 +409,9 @@ __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a)
   } else {
     // ---- scales of the 16 tokens
     void* scale = is_v ? a.vs : a.ks;
-    if (a.scale_mode == CUDA_LLM_SCALE_PER_TOKEN) {
+    if (SMODE == CUDA_LLM_SCALE_PER_TOKEN) {
       if (lane < 16) reinterpret_cast<float*>(scale)[((size_t)blk * a.Hkv + h) * a.page + off0 + lane] = tok_scales[is_v][lane];
-    } else if (a.scale_mode == CUDA_LLM_SCALE_MX_E8M0) {
+    } else if (SMODE == CUDA_LLM_SCALE_MX_E8M0) {
       if (lane < NB * 4) {
         const int b = lane >> 2, part = lane & 3;
         *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(scale) + (((size_t)blk * a.Hkv + h) * NB + b) * a.page + off0 + 4 * part) =
@@ -433,8 +437,25 @@ cudaError_t launch_kv_append(AppendArgs a, int D, cudaStream_t st) {
   }
   const long long groups = ((long long)a.n + 15) / 16;
   const unsigned grid = (unsigned)(groups * a.Hkv);
-  if (D == 64) kv_append_tile_kernel<64><<<grid, 128, 0, st>>>(a);
-  else kv_append_tile_kernel<128><<<grid, 128, 0, st>>>(a);
+  const int dt = a.src_vec ? a.in_dtype : -1;
+  auto go = [&](auto d_tag, auto dt_tag) {
+    constexpr int DD = decltype(d_tag)::value;
+    constexpr int T = decltype(dt_tag)::value;
+    switch (a.scale_mode) {
+      case CUDA_LLM_SCALE_PER_HEAD: kv_append_tile_kernel<DD, T, CUDA_LLM_SCALE_PER_HEAD><<<grid, 128, 0, st>>>(a); break;
+      case CUDA_LLM_SCALE_PER_BLOCK: kv_append_tile_kernel<DD, T, CUDA_LLM_SCALE_PER_BLOCK><<<grid, 128, 0, st>>>(a); break;
+      case CUDA_LLM_SCALE_PER_TOKEN: kv_append_tile_kernel<DD, T, CUDA_LLM_SCALE_PER_TOKEN><<<grid, 128, 0, st>>>(a); break;
+      default: kv_append_tile_kernel<DD, T, CUDA_LLM_SCALE_MX_E8M0><<<grid, 128, 0, st>>>(a); break;
+    }
+  };
+  auto go_d = [&](auto d_tag) {
+    if (dt == CUDA_LLM_F32) go(d_tag, std::integral_constant<int, CUDA_LLM_F32>{});
+    else if (dt == CUDA_LLM_F16) go(d_tag, std::integral_constant<int, CUDA_LLM_F16>{});
+    else if (dt == CUDA_LLM_BF16) go(d_tag, std::integral_constant<int, CUDA_LLM_BF16>{});
+    else go(d_tag, std::integral_constant<int, -1>{});
+  };
+  if (D == 64) go_d(std::integral_constant<int, 64>{});
+  else go_d(std::integral_constant<int, 128>{});
   return cudaGetLastError();
 }
 
