@@ -199,7 +199,7 @@ def aux_workload(args, rank, world, local):
                               "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
                               "dtype": ("bf16 mma.sync, f32 acc" if os.environ.get("CUDA_LLM_PREFILL_KERNEL") == "warp_mma"
                                         else "bf16 tcgen05.mma, f32 acc in TMEM") if args.workload == "prefill"
-                                       else "e4m3 -> f16 mma.sync, f32 acc",
+                                       else "e4m3 -> f16 (one rounding) -> tcgen05.mma, f32 acc",
                               "data": "synthetic",
                               "config": {"workload": args.workload, "batch": bsz, "heads": "32q/8kv", "seq_len": seq,
                                          "head_dim": 128, "causal": True},

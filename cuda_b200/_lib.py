@@ -72,6 +72,10 @@ SYMBOLS = {
     "cuda_llm_decode_tcgen05_counters": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]),
     "cuda_llm_paged_attention_f32_launches": (C.c_int, [C.POINTER(C.c_uint64)]),
     "cuda_llm_mx_attention": (C.c_int, [C.c_void_p] * 7 + [C.c_int32] * 5 + [C.c_float, C.c_int32, C.c_int32, C.c_void_p]),
+    "cuda_llm_mx_attention_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
+    "cuda_llm_mx_attention_ws": (C.c_int, [C.c_void_p] * 7 + [C.c_int32] * 5 + [C.c_float, C.c_int32, C.c_int32, C.c_void_p,
+                                                                                 C.c_size_t, C.c_void_p]),
+    "cuda_llm_mx_attention_tcgen05_launches": (C.c_int, [C.POINTER(C.c_uint64)]),
     "cuda_llm_dequant_pages": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                          C.c_void_p]),

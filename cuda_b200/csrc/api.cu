@@ -21,8 +21,9 @@ cudaError_t launch_dequant_pages(const void*, const void*, const int32_t*, int, 
 cudaError_t run_gqa_prefill(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hkv, int S,
                             int D, float softmax_scale, bool causal, int dtype, cudaStream_t st);
 bool gqa_prefill_sm100_supported(int Hq, int Hkv, int D, int dtype);
+cudaError_t launch_mx_to_f16(const void* codes, const float* scales, void* out, size_t n_elems, cudaStream_t st);
 cudaError_t run_gqa_prefill_sm100(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hkv, int S,
-                                  int D, float softmax_scale, bool causal, int dtype, cudaStream_t st);
+                                  int D, float softmax_scale, bool causal, int dtype, int out_dtype, cudaStream_t st);
 cudaError_t prefill_wait_timeouts(unsigned int* count);
 cudaError_t run_mx_attention(const void* q, const float* qs, const void* k, const float* ks, const void* v,
                              const float* vs, void* out, int B, int Hq, int Hkv, int S, int D, float softmax_scale,
@@ -793,7 +794,7 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
   if (!force_warp_mma && softmax_scale > 0.f && gqa_prefill_sm100_supported(num_q_heads, num_kv_heads, head_dim, dtype) &&
       encode_tiled_fn())
     e = run_gqa_prefill_sm100(q, k, v, out, batch_size, num_q_heads, num_kv_heads, seq_len, head_dim, softmax_scale,
-                              is_causal != 0, dtype, st);
+                              is_causal != 0, dtype, dtype, st);
   else
     e = run_gqa_prefill(q, k, v, out, batch_size, num_q_heads, num_kv_heads, seq_len, head_dim, softmax_scale,
                         is_causal != 0, dtype, st);
@@ -830,10 +831,29 @@ int cuda_llm_prefill_wait_timeouts(uint32_t* count) {
   return CUDA_LLM_OK;
 }
 
-int cuda_llm_mx_attention(const void* q, const float* q_scale, const void* k, const float* k_scale, const void* v,
-                          const float* v_scale, void* out, int32_t batch_size, int32_t num_q_heads,
-                          int32_t num_kv_heads, int32_t seq_len, int32_t head_dim, float softmax_scale,
-                          int32_t is_causal, int32_t out_dtype, void* stream) {
+// The tcgen05 route of the microscaled attention: operands dequantised once into f16 tensors in the
+// caller's workspace (codes times scale, one rounding: what the one-kernel route does on the way into shared
+// memory), then the tcgen05 / TMEM prefill kernel on those.
+static bool mx_attention_tcgen05_shape(int Hq, int Hkv, int D, float softmax_scale) {
+  return softmax_scale > 0.f && gqa_prefill_sm100_supported(Hq, Hkv, D, CUDA_LLM_F16) && encode_tiled_fn() != nullptr;
+}
+static size_t mx_elems(int B, int H, int S, int D) { return (size_t)B * H * S * D; }
+static std::atomic<uint64_t> g_mx_tcgen05_launches{0};
+
+size_t cuda_llm_mx_attention_workspace_bytes(int32_t batch_size, int32_t num_q_heads, int32_t num_kv_heads,
+                                             int32_t seq_len, int32_t head_dim) {
+  if (batch_size <= 0 || seq_len <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads) return 0;
+  if (!mx_attention_tcgen05_shape(num_q_heads, num_kv_heads, head_dim, 1.f)) return 0;
+  const size_t a256 = 255;
+  return ((mx_elems(batch_size, num_q_heads, seq_len, head_dim) * 2 + a256) & ~a256) +
+         2 * ((mx_elems(batch_size, num_kv_heads, seq_len, head_dim) * 2 + a256) & ~a256);
+}
+
+int cuda_llm_mx_attention_ws(const void* q, const float* q_scale, const void* k, const float* k_scale, const void* v,
+                             const float* v_scale, void* out, int32_t batch_size, int32_t num_q_heads,
+                             int32_t num_kv_heads, int32_t seq_len, int32_t head_dim, float softmax_scale,
+                             int32_t is_causal, int32_t out_dtype, void* workspace, size_t workspace_bytes,
+                             void* stream) {
   if (batch_size == 0 || seq_len == 0) return CUDA_LLM_OK;
   if (!q || !k || !v || !q_scale || !k_scale || !v_scale || !out) return fail(CUDA_LLM_EINVAL, "a required tensor pointer is null");
   if (batch_size < 0 || seq_len < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads)
@@ -844,10 +864,42 @@ int cuda_llm_mx_attention(const void* q, const float* q_scale, const void* k, co
     return fail(CUDA_LLM_EALIGN, "q, k, v and out must be 16-byte aligned");
   const int rc = check_device();
   if (rc != CUDA_LLM_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t need = cuda_llm_mx_attention_workspace_bytes(batch_size, num_q_heads, num_kv_heads, seq_len, head_dim);
+  if (workspace && need > 0 && workspace_bytes >= need && !((uintptr_t)workspace & 255) &&
+      mx_attention_tcgen05_shape(num_q_heads, num_kv_heads, head_dim, softmax_scale)) {
+    const size_t nq = mx_elems(batch_size, num_q_heads, seq_len, head_dim), nk = mx_elems(batch_size, num_kv_heads, seq_len, head_dim);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    void* qh = ws;
+    void* kh = ws + ((nq * 2 + 255) & ~(size_t)255);
+    void* vh = reinterpret_cast<uint8_t*>(kh) + ((nk * 2 + 255) & ~(size_t)255);
+    cudaError_t e = launch_mx_to_f16(q, q_scale, qh, nq, st);
+    if (e == cudaSuccess) e = launch_mx_to_f16(k, k_scale, kh, nk, st);
+    if (e == cudaSuccess) e = launch_mx_to_f16(v, v_scale, vh, nk, st);
+    if (e == cudaSuccess)
+      e = run_gqa_prefill_sm100(qh, kh, vh, out, batch_size, num_q_heads, num_kv_heads, seq_len, head_dim, softmax_scale,
+                                is_causal != 0, CUDA_LLM_F16, out_dtype, st);
+    if (e != cudaSuccess) return fail_cuda(e, "microscaled attention (tcgen05 route) launch");
+    g_mx_tcgen05_launches.fetch_add(1, std::memory_order_relaxed);
+    return CUDA_LLM_OK;
+  }
   cudaError_t e = run_mx_attention(q, q_scale, k, k_scale, v, v_scale, out, batch_size, num_q_heads, num_kv_heads,
-                                   seq_len, head_dim, softmax_scale, is_causal != 0, out_dtype,
-                                   reinterpret_cast<cudaStream_t>(stream));
+                                   seq_len, head_dim, softmax_scale, is_causal != 0, out_dtype, st);
   return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "gqa_prefill_kernel (microscaled) launch");
+}
+
+int cuda_llm_mx_attention(const void* q, const float* q_scale, const void* k, const float* k_scale, const void* v,
+                          const float* v_scale, void* out, int32_t batch_size, int32_t num_q_heads,
+                          int32_t num_kv_heads, int32_t seq_len, int32_t head_dim, float softmax_scale,
+                          int32_t is_causal, int32_t out_dtype, void* stream) {
+  return cuda_llm_mx_attention_ws(q, q_scale, k, k_scale, v, v_scale, out, batch_size, num_q_heads, num_kv_heads, seq_len,
+                                  head_dim, softmax_scale, is_causal, out_dtype, nullptr, 0, stream);
+}
+
+int cuda_llm_mx_attention_tcgen05_launches(uint64_t* launches) {
+  if (!launches) return fail(CUDA_LLM_EINVAL, "null argument");
+  *launches = g_mx_tcgen05_launches.load(std::memory_order_relaxed);
+  return CUDA_LLM_OK;
 }
 
 int cuda_llm_merge_partials(const float* parts_out, const float* parts_lse, int32_t num_parts,

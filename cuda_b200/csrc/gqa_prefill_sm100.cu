@@ -35,7 +35,8 @@ struct Prefill100Args {
   int B, Hq, Hkv, S, group;
   int gsz;   // query heads per CTA (1, 2, 4 or 8; divides group)
   int causal;
-  int bf16;  // operand / output type: 1 bf16, 0 fp16
+  int bf16;  // operand type: 1 bf16, 0 fp16
+  int out_dtype;  // CUDA_LLM_F32 / F16 / BF16 (the 16-bit types need not equal the operand type)
   float scale_log2;
 };
 
@@ -366,21 +367,28 @@ gqa_prefill_sm100_kernel(const __grid_constant__ Prefill100Args a, const __grid_
       const float l_tot = l_run + xchg[((n_tiles & 1) * 2 + (half ^ 1)) * 128 + row];
       const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
       const bool store = qpos < a.S;
-      uint4* og = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) +
-                                           (((size_t)b * a.Hq + qh) * (size_t)a.S + (store ? qpos : 0)) * D + half * OC);
+      const size_t orow = (((size_t)b * a.Hq + qh) * (size_t)a.S + (store ? qpos : 0)) * D + half * OC;
+      uint4* og = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + orow);
+      float4* ogf = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + orow);
+      const bool out_bf16 = a.out_dtype == CUDA_LLM_BF16, out_f32 = a.out_dtype == CUDA_LLM_F32;
 #pragma unroll 1
       for (int c = 0; c < OC / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem + lane_base + 256 + half * OC + c * 32, r);
         tc_wait_ld();
-        if (store) {
+        if (store && out_f32) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            ogf[c * 8 + u] = make_float4(__uint_as_float(r[4 * u]) * inv, __uint_as_float(r[4 * u + 1]) * inv,
+                                         __uint_as_float(r[4 * u + 2]) * inv, __uint_as_float(r[4 * u + 3]) * inv);
+        } else if (store) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float x0 = __uint_as_float(r[8 * u + 2 * e]) * inv, x1 = __uint_as_float(r[8 * u + 2 * e + 1]) * inv;
-              w[e] = a.bf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
+              w[e] = out_bf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
             }
             og[c * 4 + u] = make_uint4(w[0], w[1], w[2], w[3]);
           }
@@ -418,8 +426,9 @@ bool gqa_prefill_sm100_supported(int Hq, int Hkv, int D, int dtype) {
   return group == 1 || group == 2 || group == 4 || group % 8 == 0;
 }
 
+// dtype: the 16-bit type of q, k, v; out_dtype: any of the three output types.
 cudaError_t run_gqa_prefill_sm100(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hkv, int S,
-                                  int D, float softmax_scale, bool causal, int dtype, cudaStream_t st) {
+                                  int D, float softmax_scale, bool causal, int dtype, int out_dtype, cudaStream_t st) {
   if (B == 0 || S == 0) return cudaSuccess;
   EncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return cudaErrorNotSupported;
@@ -428,6 +437,7 @@ cudaError_t run_gqa_prefill_sm100(const void* q, const void* k, const void* v, v
   a.gsz = a.group < 8 ? a.group : 8;
   a.causal = causal ? 1 : 0;
   a.bf16 = dtype == CUDA_LLM_BF16 ? 1 : 0;
+  a.out_dtype = out_dtype;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   const int bq = 128 / a.gsz;
   PrefillMaps maps;

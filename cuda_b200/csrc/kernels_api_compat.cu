@@ -105,9 +105,12 @@ void dispatch_fused_microscaled_attention(const int8_t* q, const float* q_scale,
                                           const float* k_scale, const int8_t* v, const float* v_scale, T_OUT* out,
                                           int batch_size, int num_heads, int seq_len, int head_dim,
                                           float softmax_scale, bool is_causal, cudaStream_t stream) {
+  const size_t bytes = cuda_llm_mx_attention_workspace_bytes(batch_size, num_heads, num_heads, seq_len, head_dim);
+  void* ws = scratch(bytes, stream);
   report("dispatch_fused_microscaled_attention",
-         cuda_llm_mx_attention(q, q_scale, k, k_scale, v, v_scale, out, batch_size, num_heads, num_heads, seq_len,
-                               head_dim, softmax_scale, is_causal ? 1 : 0, dtype_of<T_OUT>(), stream));
+         cuda_llm_mx_attention_ws(q, q_scale, k, k_scale, v, v_scale, out, batch_size, num_heads, num_heads, seq_len,
+                                  head_dim, softmax_scale, is_causal ? 1 : 0, dtype_of<T_OUT>(), ws, ws ? bytes : 0, stream));
+  if (ws) cudaFreeAsync(ws, stream);
 }
 
 #define INSTANTIATE(T)                                                                                        \

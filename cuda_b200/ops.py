@@ -50,6 +50,20 @@ def get_workspace(device, nbytes: int) -> torch.Tensor:
     return ws
 
 
+_scratch_buffers = {}
+
+
+def _scratch(device, nbytes: int, tag: str) -> torch.Tensor:
+    """A per-(device, stream, tag) buffer that only grows, for temporaries that are not decode workspaces
+    (those carry a status header and come from ``get_workspace``)."""
+    key = (torch.device(device).index, _stream_ptr(device), tag)
+    buf = _scratch_buffers.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _scratch_buffers[key] = buf
+    return buf
+
+
 def _scale_mode(k_scale: torch.Tensor) -> int:
     if k_scale.dtype in (torch.uint8, getattr(torch, "float8_e8m0fnu", torch.uint8)):
         if k_scale.dim() != 4:
@@ -409,10 +423,15 @@ def fused_microscaled_attention(q, q_scale, k, k_scale, v, v_scale, is_causal=Tr
     scale = 1.0 / math.sqrt(d) if softmax_scale is None else float(softmax_scale)
     with torch.cuda.device(q.device):
         out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
-        L.check(L.load().cuda_llm_mx_attention(q.data_ptr(), qs.data_ptr(), k.data_ptr(), ks.data_ptr(), v.data_ptr(),
-                                               vs.data_ptr(), out.data_ptr(), b, hq, hkv, s, d, scale,
-                                               1 if is_causal else 0, _DTYPE[out_dtype], _stream_ptr(q.device)),
-                "cuda_llm_mx_attention")
+        lib = L.load()
+        need = lib.cuda_llm_mx_attention_workspace_bytes(b, hq, hkv, s, d)   # 0: no tcgen05 route for this shape
+        ws = _scratch(q.device, need, "mx_attention") if need else None
+        L.check(lib.cuda_llm_mx_attention_ws(q.data_ptr(), qs.data_ptr(), k.data_ptr(), ks.data_ptr(), v.data_ptr(),
+                                             vs.data_ptr(), out.data_ptr(), b, hq, hkv, s, d, scale,
+                                             1 if is_causal else 0, _DTYPE[out_dtype],
+                                             ws.data_ptr() if need else None, ws.numel() if need else 0,
+                                             _stream_ptr(q.device)),
+                "cuda_llm_mx_attention_ws")
     return out
 
 

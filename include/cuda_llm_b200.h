@@ -306,6 +306,22 @@ int cuda_llm_mx_attention(const void* q, const float* q_scale, const void* k, co
                           int32_t num_kv_heads, int32_t seq_len, int32_t head_dim, float softmax_scale,
                           int32_t is_causal, int32_t out_dtype, void* stream);
 
+/* The same operation with a caller-provided workspace of cuda_llm_mx_attention_workspace_bytes() bytes
+ * (256-byte aligned; 0 = the shape has no tcgen05 route): q, k and v are first dequantised once into f16
+ * tensors in the workspace (code times scale, one rounding: the same operand values the one-kernel route
+ * builds on the way into shared memory) and the tcgen05 / tensor-memory prefill kernel runs on those,
+ * several times faster on long sequences.  Without a sufficient workspace, or for group sizes that kernel
+ * does not take, the call is cuda_llm_mx_attention.  cuda_llm_mx_attention_tcgen05_launches counts the
+ * calls of this process that took the tcgen05 route. */
+size_t cuda_llm_mx_attention_workspace_bytes(int32_t batch_size, int32_t num_q_heads, int32_t num_kv_heads,
+                                             int32_t seq_len, int32_t head_dim);
+int cuda_llm_mx_attention_ws(const void* q, const float* q_scale, const void* k, const float* k_scale, const void* v,
+                             const float* v_scale, void* out, int32_t batch_size, int32_t num_q_heads,
+                             int32_t num_kv_heads, int32_t seq_len, int32_t head_dim, float softmax_scale,
+                             int32_t is_causal, int32_t out_dtype, void* workspace, size_t workspace_bytes,
+                             void* stream);
+int cuda_llm_mx_attention_tcgen05_launches(uint64_t* launches);
+
 /* Bit-exact dequantisation of whole pages to fp32 (test and debugging aid):
  * out [n_pages, Hkv, D, page] fp32 for the pages listed in `pages`. */
 int cuda_llm_dequant_pages(const void* cache, const void* scale, const int32_t* pages,

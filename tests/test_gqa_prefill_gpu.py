@@ -125,6 +125,52 @@ def test_microscaled_attention(ops, out_dtype, b, hq, hkv, s, d, causal):
         assert err.max().item() <= 8e-3
 
 
+def _mx_launches(ops):
+    import ctypes as C
+    n = C.c_uint64(0)
+    ops.L.check(ops.L.load().cuda_llm_mx_attention_tcgen05_launches(C.byref(n)), "counter")
+    return n.value
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("b,hq,hkv,s,d,causal", [(1, 32, 8, 1000, 128, True), (2, 8, 8, 333, 128, False),
+                                                 (1, 16, 2, 520, 64, True), (1, 4, 2, 129, 128, True)])
+def test_microscaled_attention_tcgen05_route(ops, out_dtype, b, hq, hkv, s, d, causal):
+    """The route through dequantised f16 operands and the tcgen05 / tensor-memory kernel (taken when the
+    caller gives a workspace, as the Python op does) and the one-kernel route of the same call without a
+    workspace, both against the oracle's dequantise-then-attend; fp32, f16 and bf16 outputs."""
+    g = torch.Generator().manual_seed(s + d + hq)
+
+    def quant(h):
+        x = torch.randn(b, h, s, d, generator=g) * torch.exp(0.3 * torch.randn(b, h, s, 1, generator=g))
+        sc = (x.view(b, h, s, d // 32, 32).abs().amax(-1) / 448.0).clamp_min(1e-8)
+        codes = (x.view(b, h, s, d // 32, 32) / sc.unsqueeze(-1)).to(torch.float8_e4m3fn).view(torch.uint8)
+        return codes.view(b, h, s, d), sc
+
+    (q8, qs), (k8, ks), (v8, vs) = quant(hq), quant(hkv), quant(hkv)
+    ref = O.ref_mx_attention(q8, qs, k8, ks, v8, vs, causal)
+    dev = [t.cuda() for t in (q8, qs, k8, ks, v8, vs)]
+    before = _mx_launches(ops)
+    out = ops.fused_microscaled_attention(*dev, is_causal=causal, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    assert _mx_launches(ops) == before + 1, "the call did not take the tcgen05 route"
+    # the same call without a workspace: the one-kernel route
+    lib = ops.L.load()
+    plain = torch.empty_like(out)
+    ops.L.check(lib.cuda_llm_mx_attention(dev[0].data_ptr(), dev[1].data_ptr(), dev[2].data_ptr(), dev[3].data_ptr(),
+                                          dev[4].data_ptr(), dev[5].data_ptr(), plain.data_ptr(), b, hq, hkv, s, d,
+                                          1.0 / d ** 0.5, 1 if causal else 0, ops._DTYPE[out_dtype], None), "mx_attention")
+    torch.cuda.synchronize()
+    assert _mx_launches(ops) == before + 1
+    scale = ref.abs().amax().clamp_min(1.0)
+    for name, o in (("tcgen05", out), ("one kernel", plain)):
+        assert o.dtype == out_dtype and torch.isfinite(o).all(), name
+        err = (o.float().cpu() - ref).abs() / scale
+        assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, (name, err.max().item(), err.mean().item())
+        if out_dtype != torch.bfloat16:
+            assert err.max().item() <= 8e-3, (name, err.max().item())
+
+
 def test_microscaled_dispatcher_symbol(ops):
     """dispatch_fused_microscaled_attention<T_OUT> exists under the reference's mangled names."""
     lib = ops.L.load()
