@@ -154,6 +154,9 @@ template <int D>
 __global__ void __launch_bounds__(128) kv_append_token_kernel(const AppendArgs a) {
   constexpr int E = D / 32;
   const int lane = threadIdx.x & 31;
+  // the decode kernel that follows is launched as a programmatic dependent: let it be scheduled now (it does
+  // not touch the cache before its own griddepcontrol.wait, i.e. before this grid has completed)
+  asm volatile("griddepcontrol.launch_dependents;");
   const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (item >= 2LL * a.n * a.Hkv) return;
   const int is_v = (int)(item & 1);
@@ -199,12 +202,21 @@ struct Divisor {
     const uint32_t b = __float_as_uint(s), e = (b >> 23) & 0xffu, ey = (__float_as_uint(y) >> 23) & 0xffu;
     fast = (b & 0x7fffffu) != 0x7fffffu && e >= 1 && e <= 253 && ey >= 1 && ey <= 253;
   }
-  __device__ __forceinline__ float div(float x) const {
-    if (!fast) return __fdiv_rn(x, sc);
-    const float q = __fmul_rn(x, y);
-    const float qq = __fmaf_rn(__fmaf_rn(-q, sc, x), y, q);
-    // the divisor is positive, so the quotient has the sign of x; the sums above turn -0 into +0
-    return __uint_as_float((__float_as_uint(qq) & 0x7fffffffu) | (__float_as_uint(x) & 0x80000000u));
+  // x[e] /= sc for N values; one test of `fast` for all of them
+  template <int N>
+  __device__ __forceinline__ void div_all(float (&x)[N]) const {
+    if (fast) {
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        const float q = __fmul_rn(x[e], y);
+        const float qq = __fmaf_rn(__fmaf_rn(-q, sc, x[e]), y, q);
+        // the divisor is positive, so the quotient has the sign of x; the sums above turn -0 into +0
+        x[e] = __uint_as_float((__float_as_uint(qq) & 0x7fffffffu) | (__float_as_uint(x[e]) & 0x80000000u));
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < N; ++e) x[e] = __fdiv_rn(x[e], sc);
+    }
   }
 };
 
@@ -334,8 +346,7 @@ __global__ void __launch_bounds__(128) kv_append_tile_kernel(const AppendArgs a)
       if (SMODE == CUDA_LLM_SCALE_PER_TOKEN) {
         tsc = fmaxf(__fdiv_rn(amax, 448.f), 1e-8f);
         const Divisor dv(tsc);  // |x / tsc| <= 448 (1 + 2^-23)
-#pragma unroll
-        for (int e = 0; e < 16; ++e) x[e] = dv.div(x[e]);
+        dv.div_all(x);
       } else {
         const float sc = (SMODE == CUDA_LLM_SCALE_PER_BLOCK)
                              ? reinterpret_cast<const float*>(scale)[(size_t)(slot_ok ? blk : 0) * a.Hkv + h]
