@@ -3,6 +3,7 @@
 // before it calls dispatch_fp8_paged_attention (fused_softmax_binding.cpp:645-669 in the
 // reference project) and turns the dispatcher's silent no-op on an unsupported shape
 // (fp8_paged_attention_kernel.cuh:176-190) into an error code.
+#include <climits>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -33,10 +34,13 @@ cudaError_t run_kv_append_prefill(const void* k, const void* v, const CudaLlmKvC
 size_t dense_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens);
 size_t paged_f32_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_tokens);
 bool paged_f32_decode_supported(int D, int page, const void* k, const void* v);
+struct F32TensorMaps {
+  CUtensorMap k, v;
+};
 cudaError_t run_paged_f32_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
-                                 const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int max_blocks,
+                                 const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int page, int max_blocks,
                                  int num_blocks, int seq_len, float softmax_scale, void* workspace, int num_sms,
-                                 cudaStream_t st);
+                                 const F32TensorMaps* maps, cudaStream_t st);
 cudaError_t run_dense_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
                              const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int page,
                              int max_blocks, int num_blocks, int seq_len, float softmax_scale, int dtype,
@@ -132,6 +136,25 @@ static int encode_cache_map(CUtensorMap* map, const void* cache, int num_blocks,
                          const_cast<void*>(cache), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, page * elem_bytes >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char msg[96];
+    snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return fail(CUDA_LLM_ECUDA, msg);
+  }
+  return CUDA_LLM_OK;
+}
+
+// Tensor map of an fp32 paged cache [num_blocks][Hkv * D][page]: boxes of 16 tokens x D head_dim rows, as stored.
+static int encode_f32_cache_map(CUtensorMap* map, const void* cache, int num_blocks, int Hkv, int D, int page) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(CUDA_LLM_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[3] = {(cuuint64_t)page, (cuuint64_t)Hkv * D, (cuuint64_t)num_blocks};
+  const cuuint64_t strides[2] = {(cuuint64_t)page * 4, (cuuint64_t)Hkv * D * page * 4};
+  const cuuint32_t box[3] = {16, (cuuint32_t)D, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(cache), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char msg[96];
     snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -674,10 +697,18 @@ int cuda_llm_paged_attention(const void* query, const void* key_cache, const voi
     return cuda_llm_paged_decode(&p, stream);
   }
   if (dtype == CUDA_LLM_F32 && paged_f32_decode_supported(head_dim, page_size, key_cache, value_cache) &&
-      !((uintptr_t)workspace & 15)) {
+      !((uintptr_t)workspace & 15) && (page_size == 16 || (num_blocks < INT_MAX && encode_tiled_fn()))) {
+    // (the C++ dispatchers of the reference carry no pool size and pass INT_MAX: they use pages of 16 tokens only)
+    F32TensorMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    if (page_size > 16) {
+      rc = encode_f32_cache_map(&maps.k, key_cache, num_blocks, num_kv_heads, head_dim, page_size);
+      if (rc == CUDA_LLM_OK) rc = encode_f32_cache_map(&maps.v, value_cache, num_blocks, num_kv_heads, head_dim, page_size);
+      if (rc != CUDA_LLM_OK) return rc;
+    }
     cudaError_t e = run_paged_f32_decode(true, query, key_cache, value_cache, block_tables, context_lens, out, num_seqs,
-                                         num_heads, num_kv_heads, head_dim, max_blocks_per_seq, num_blocks, 0,
-                                         softmax_scale, workspace, sm_count_cached(),
+                                         num_heads, num_kv_heads, head_dim, page_size, max_blocks_per_seq, num_blocks, 0,
+                                         softmax_scale, workspace, sm_count_cached(), &maps,
                                          reinterpret_cast<cudaStream_t>(stream));
     if (e == cudaSuccess) g_f32_launches.fetch_add(1, std::memory_order_relaxed);
     return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "paged_attention (fp32) launch");
@@ -747,8 +778,8 @@ int cuda_llm_flash_decode(const void* q, const void* k, const void* v, void* o, 
       !((uintptr_t)workspace & 15)) {
     // fp32 K/V: the bulk-copy kernel in its token-major mode
     cudaError_t e = run_paged_f32_decode(false, q, k, v, nullptr, nullptr, o, batch_size, num_heads, num_kv_heads,
-                                         head_dim, (seq_len + 15) / 16, 1, seq_len, softmax_scale, workspace,
-                                         sm_count_cached(), reinterpret_cast<cudaStream_t>(stream));
+                                         head_dim, 16, (seq_len + 15) / 16, 1, seq_len, softmax_scale, workspace,
+                                         sm_count_cached(), nullptr, reinterpret_cast<cudaStream_t>(stream));
     if (e == cudaSuccess) g_f32_launches.fetch_add(1, std::memory_order_relaxed);
     return e == cudaSuccess ? CUDA_LLM_OK : fail_cuda(e, "flash_decode (fp32) launch");
   }

@@ -21,6 +21,10 @@
 //   three butterfly steps) and in P.V (the lane multiplies by the probabilities of exactly the tokens it
 //   scored, so P never moves; partial outputs are summed over tq once per item).
 //
+// Pages of 32 / 64 tokens (an extension; the reference supports 16 only) have rows of 128 / 256 bytes, so a
+// 16-token tile of a slab is not contiguous: it is fetched as one TMA box (16 tokens x head_dim rows, no
+// swizzle) through a tensor map over the cache and lands in the slot in the same [head_dim][16] shape.
+//
 // The same kernel serves the reference's contiguous fp32 K/V (async_flash_decode_kernel.cuh:29-220, tensors
 // [B, H, S, D], one token = one row of head_dim floats) as its token-major mode: a slot then holds 16
 // consecutive token rows, lane (dq, tl) = (lane & 7, lane >> 3) reads the 16 bytes of head_dim values
@@ -30,6 +34,7 @@
 // Waits are bounded (mbar_wait); a warp whose wait runs out records CUDA_LLM_ST_TIMEOUT in the status
 // word, waits (bounded) for its own copies still in flight and returns.
 #include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 #include "paged_decode_kernel.cuh"
@@ -45,6 +50,10 @@ constexpr int kF32MinChunk = 8;       // pages per item, lower and upper bound
 constexpr int kF32MaxSplits = 256;    // partial results per query row
 constexpr long long kF32TargetItems = 8192;
 
+struct F32TensorMaps {
+  CUtensorMap k, v;   // cache [num_blocks][Hkv * D][page] fp32, box = 16 tokens x D rows (pages of 32 / 64 tokens)
+};
+
 struct PagedF32Args {
   const float* q;    // [S, Hq, D]
   const float* k;    // [num_blocks, Hkv, D, 16]
@@ -55,7 +64,8 @@ struct PagedF32Args {
   float* part_lse;   // [n_splits, S*Hq]   natural log
   uint32_t* status;
   uint32_t* counter;  // next item
-  int S, Hq, Hkv, group, max_blocks, num_blocks, n_splits, chunk_pages, n_rg;
+  int S, Hq, Hkv, group, max_blocks, num_blocks, n_splits, chunk_pages, n_rg;  // chunk_pages: 16-token tiles per item
+  int page;           // tokens per page (16: bulk copies of whole slabs; 32 / 64: TMA boxes)
   int seq_len;        // token-major mode: tokens of every sequence (bt and ctx are null)
   long long n_items;
   float scale_log2;
@@ -78,7 +88,8 @@ static void f32_split_plan(int S, int Hkv, int group, int max_pages, int& chunk_
 }
 
 template <int D, int GP, bool TM>
-__global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(const PagedF32Args a) {
+__global__ void __launch_bounds__(32 * kF32Warps, 1)
+paged_f32_decode_kernel(const PagedF32Args a, const __grid_constant__ F32TensorMaps tmaps) {
   constexpr int KK = D / 8;                  // head_dim values per lane
   constexpr int KB = D / 32;                 // token-major: 32-wide head_dim blocks
   constexpr uint32_t SLOT = D * 16 * 4;      // bytes of a slab
@@ -90,8 +101,9 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tq = lane & 3, dl = lane >> 2;   // paged: token quad, head_dim row
   const int dq = lane & 7, tl = lane >> 3;   // token-major: head_dim quad, token row
-  uint8_t* ring = smem_f32 + (size_t)warp * kF32Slots * SLOT;
+  uint8_t* ring = smem_f32 + ((128u - (smem_u32(smem_f32) & 127u)) & 127u) + (size_t)warp * kF32Slots * SLOT;
   const uint32_t ring_u32 = smem_u32(ring);
+  const int tpp = a.page >> 4;  // 16-token tiles per page
   const uint32_t bar0 = smem_u32(&bars[warp][0]);
   if (lane == 0) {
 #pragma unroll
@@ -106,7 +118,8 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
   // ---- issue side: a cursor over the pages of the item being fetched
   uint32_t iseq = 0, cseq = 0;  // slots issued / consumed
   int it_kvh = 0, it_page = 0, it_npages = 0, it_kv = 0, it_first_blk = 0, it_s = 0, it_ntok = 0;
-  int it_bt = 0;                // lane j: block of page (it_page & ~31) + j of the item
+  int it_bt = 0;                // lane j: block-table entry bt_base + j of the sequence
+  int bt_base = 0;
   bool it_have = false, it_done = false;
   int qw = 0, qr = 0;           // queue write / read positions
   int next_raw = 0;             // lane 0: the item the next acquire takes (fetched one item ahead)
@@ -123,14 +136,11 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
     s = (int)(item % a.S);
     split = (int)(item / a.S);
   };
-  auto load_bt = [&]() {
+  auto load_bt = [&](int first_page) {  // the 32 block-table entries from `first_page` on
     if (TM) return;
-    const int pg = it_first_blk + (it_page & ~31) + lane;
-    int b = (pg < a.max_blocks && (it_page & ~31) + lane < it_npages) ? a.bt[(size_t)it_s * a.max_blocks + pg] : 0;
-    if (b < 0 || b >= a.num_blocks) {
-      atomicOr(a.status, CUDA_LLM_ST_BAD_BLOCK);
-      b = 0;
-    }
+    bt_base = first_page;
+    const int pg = first_page + lane;
+    int b = pg < a.max_blocks ? a.bt[(size_t)it_s * a.max_blocks + pg] : 0;
     it_bt = b;
   };
   auto acquire = [&]() {
@@ -144,7 +154,7 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
       int s, kvh, split, rg;
       item_coords(item, s, kvh, split, rg);
       int ctx = TM ? a.seq_len : a.ctx[s];
-      if (!TM) ctx = max(0, min(ctx, a.max_blocks * 16));
+      if (!TM) ctx = max(0, min(ctx, a.max_blocks * a.page));
       const int t0 = split * a.chunk_pages * 16;
       const int n_tok = max(0, min(ctx - t0, a.chunk_pages * 16));
       if (n_tok == 0) {
@@ -166,7 +176,7 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
       it_first_blk = t0 >> 4;
       it_ntok = n_tok;
       it_have = true;
-      load_bt();
+      load_bt(it_first_blk / (TM ? 1 : tpp));
       if (lane == 0) queue[warp][qw & 3] = make_int2((int)item, n_tok);
       ++qw;
       break;
@@ -182,22 +192,36 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
       const size_t tok = (size_t)(it_first_blk + it_page) * 16;
       src = (it_kv ? a.v : a.k) + (((size_t)it_s * a.Hkv + it_kvh) * a.seq_len + tok) * D;
       bytes = (uint32_t)min(16, it_ntok - it_page * 16) * (D * 4);
-    } else {
-      const int blk = __shfl_sync(0xffffffffu, it_bt, it_page & 31);
+    }
+    int blk = 0, tile_in_page = 0;
+    if (!TM) {
+      const int tile = it_first_blk + it_page;   // 16-token tile of the sequence
+      const int pg = tile / tpp;
+      tile_in_page = tile - pg * tpp;
+      if (pg - bt_base >= 32) load_bt(pg);
+      blk = __shfl_sync(0xffffffffu, it_bt, pg - bt_base);
+      if (blk < 0 || blk >= a.num_blocks) {
+        if (lane == 0) atomicOr(a.status, CUDA_LLM_ST_BAD_BLOCK);
+        blk = 0;
+      }
       src = (it_kv ? a.v : a.k) + ((size_t)blk * a.Hkv + it_kvh) * (size_t)(D * 16);
     }
     const uint32_t slot = iseq % kF32Slots;
     if (lane == 0) {
       mbar_arrive_expect_tx(bar0 + 8 * slot, bytes);
-      if (!(a.stall_test && (it_s | it_kvh | it_first_blk | it_page | it_kv) == 0))  // first K slab of the launch
-        bulk_g2s_hint(ring_u32 + slot * SLOT, src, bytes, bar0 + 8 * slot, policy);
+      if (!(a.stall_test && (it_s | it_kvh | it_first_blk | it_page | it_kv) == 0)) {  // first K slab of the launch
+        if (!TM && tpp > 1)
+          tma_load_3d_hint(ring_u32 + slot * SLOT, it_kv ? &tmaps.v : &tmaps.k, tile_in_page * 16, it_kvh * D, blk,
+                           bar0 + 8 * slot, policy);
+        else
+          bulk_g2s_hint(ring_u32 + slot * SLOT, src, bytes, bar0 + 8 * slot, policy);
+      }
     }
     ++iseq;
     it_kv ^= 1;
     if (it_kv == 0) {
       ++it_page;
       if (it_page == it_npages) it_have = false;
-      else if ((it_page & 31) == 0) load_bt();
     }
   };
   auto fill = [&]() {
@@ -419,8 +443,8 @@ __global__ void __launch_bounds__(32 * kF32Warps, 1) paged_f32_decode_kernel(con
 }
 
 template <int D, int GP, bool TM>
-static cudaError_t launch_f32(const PagedF32Args& a, int grid, cudaStream_t st) {
-  const size_t dyn = (size_t)kF32Warps * kF32Slots * D * 16 * 4;
+static cudaError_t launch_f32(const PagedF32Args& a, const F32TensorMaps& maps, int grid, cudaStream_t st) {
+  const size_t dyn = (size_t)kF32Warps * kF32Slots * D * 16 * 4 + 128;  // + room to align the rings to 128 bytes
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -430,7 +454,7 @@ static cudaError_t launch_f32(const PagedF32Args& a, int grid, cudaStream_t st) 
     if (e != cudaSuccess) return e;
     if (dev < 64) attr_set[dev] = true;
   }
-  paged_f32_decode_kernel<D, GP, TM><<<grid, 32 * kF32Warps, dyn, st>>>(a);
+  paged_f32_decode_kernel<D, GP, TM><<<grid, 32 * kF32Warps, dyn, st>>>(a, maps);
   return cudaGetLastError();
 }
 
@@ -442,15 +466,16 @@ size_t paged_f32_decode_workspace_bytes(int S, int Hq, int Hkv, int D, int max_t
 }
 
 bool paged_f32_decode_supported(int D, int page, const void* k, const void* v) {
-  return page == 16 && (D == 64 || D == 128) && !(((uintptr_t)k | (uintptr_t)v) & 15);
+  return (page == 16 || page == 32 || page == 64) && (D == 64 || D == 128) && !(((uintptr_t)k | (uintptr_t)v) & 15);
 }
 
-// `paged`: K/V are caches [num_blocks, Hkv, D, 16] read through bt / ctx; otherwise contiguous tensors
-// [S, Hkv, seq_len, D] (bt and ctx unused, max_blocks = pages that cover seq_len).
+// `paged`: K/V are caches [num_blocks, Hkv, D, page] read through bt / ctx (`maps`: their tensor maps, used for
+// pages of 32 / 64 tokens, may be null for 16); otherwise contiguous tensors [S, Hkv, seq_len, D] (bt and ctx unused,
+// page 16, max_blocks = tiles that cover seq_len).
 cudaError_t run_paged_f32_decode(bool paged, const void* q, const void* k, const void* v, const int32_t* bt,
-                                 const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int max_blocks,
+                                 const int32_t* ctx, void* out, int S, int Hq, int Hkv, int D, int page, int max_blocks,
                                  int num_blocks, int seq_len, float softmax_scale, void* workspace, int num_sms,
-                                 cudaStream_t st) {
+                                 const F32TensorMaps* maps, cudaStream_t st) {
   PagedF32Args a;
   a.q = reinterpret_cast<const float*>(q);
   a.k = reinterpret_cast<const float*>(k);
@@ -458,7 +483,8 @@ cudaError_t run_paged_f32_decode(bool paged, const void* q, const void* k, const
   a.bt = bt; a.ctx = ctx;
   a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.group = Hq / Hkv; a.max_blocks = max_blocks; a.num_blocks = num_blocks;
   a.seq_len = seq_len;
-  f32_split_plan(S, Hkv, a.group, max_blocks, a.chunk_pages, a.n_splits);
+  a.page = page;
+  f32_split_plan(S, Hkv, a.group, max_blocks * (page / 16), a.chunk_pages, a.n_splits);
   a.n_rg = (a.group + 3) / 4;
   a.n_items = (long long)S * Hkv * a.n_splits * a.n_rg;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
@@ -477,10 +503,13 @@ cudaError_t run_paged_f32_decode(bool paged, const void* q, const void* k, const
   if (e != cudaSuccess) return e;
   const int grid = num_sms > 0 ? num_sms : 148;
   const int gp = a.group >= 3 ? 4 : a.group;
+  F32TensorMaps tm;
+  if (maps) tm = *maps;
+  else memset(&tm, 0, sizeof(tm));
   auto go = [&](auto d_tag, auto tm_tag) -> cudaError_t {
     constexpr int DD = decltype(d_tag)::value;
     constexpr bool T = decltype(tm_tag)::value;
-    return gp == 1 ? launch_f32<DD, 1, T>(a, grid, st) : gp == 2 ? launch_f32<DD, 2, T>(a, grid, st) : launch_f32<DD, 4, T>(a, grid, st);
+    return gp == 1 ? launch_f32<DD, 1, T>(a, tm, grid, st) : gp == 2 ? launch_f32<DD, 2, T>(a, tm, grid, st) : launch_f32<DD, 4, T>(a, tm, grid, st);
   };
   using I64 = std::integral_constant<int, 64>;
   using I128 = std::integral_constant<int, 128>;

@@ -286,9 +286,9 @@ int cuda_llm_prefill_wait_timeouts(uint32_t* count);
  * second synchronises the device).  Either pointer may be NULL. */
 int cuda_llm_decode_tcgen05_counters(uint64_t* launches, uint32_t* wait_timeouts);
 
-/* No counterpart in the reference.  Calls of cuda_llm_paged_attention (fp32 cache, pages of 16 tokens)
- * and cuda_llm_flash_decode (fp32 K/V) by this process that ran on the bulk-copy fp32 kernel; other
- * fp32 shapes run on the plain split-KV kernel.  Failure-path test of that kernel (its entry points
+/* No counterpart in the reference.  Calls of cuda_llm_paged_attention (fp32 cache) and
+ * cuda_llm_flash_decode (fp32 K/V) by this process that ran on the bulk-copy fp32 kernel; calls with
+ * pointers that are not 16-byte aligned run on the plain split-KV kernel.  Failure-path test of that kernel (its entry points
  * carry no flags word): with CUDA_LLM_TEST_STALL=1 in the environment the first copy of a launch is
  * announced and never sent and every wait gives up after a few thousand polls; the wait runs out, the
  * warp returns, CUDA_LLM_ST_TIMEOUT is set in the workspace's status word, nothing faults or hangs. */

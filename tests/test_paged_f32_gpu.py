@@ -126,10 +126,21 @@ def test_out_of_range_block_is_reported_not_read(ops):
     assert ops.decode_status(ws) & L.ST_BAD_BLOCK
 
 
-def test_other_page_sizes_keep_the_plain_kernel(ops):
-    for page in (32, 64):
-        wl = _workload([300, 17, 1025], 2, 4, 128, seed=4, page=page)
-        _check(_run(ops, wl, expect_kernel=False), _oracle(wl), f"page {page}")
+@pytest.mark.parametrize("page", [32, 64])
+@pytest.mark.parametrize("hkv,group,d", [(2, 4, 128), (3, 1, 64), (2, 8, 128), (8, 4, 128)])
+def test_pages_of_32_and_64_tokens(ops, page, hkv, group, d):
+    """Pages of 32 / 64 tokens (an extension of the reference's 16): 16-token tiles fetched as TMA boxes.  Tails at
+    every position of a page, an empty sequence, sequences of several chunks."""
+    wl = _workload([777, 0, 1, 15, 16, 17, 31, 33, 63, 64, 65, 130, 2049, 5000], hkv, group, d, seed=4 + page + hkv, page=page)
+    out = _run(ops, wl)
+    _check(out, _oracle(wl), f"page {page} hkv {hkv} group {group} d {d}")
+    assert (out[1] == 0).all()
+
+
+def test_pages_of_64_tokens_long(ops):
+    """More than 32 pages per item and a wide block table: the block list of an item is reloaded."""
+    wl = _workload([150000, 300, 70000], 1, 2, 64, seed=12, page=64, pool_factor=1.05)
+    _check(_run(ops, wl), _oracle(wl), "page 64 long")
 
 
 def test_repeatable(ops):
