@@ -813,9 +813,8 @@ int cuda_llm_gqa_prefill(const void* q, const void* k, const void* v, void* out,
   const int rc = check_device();
   if (rc != CUDA_LLM_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  // 16-bit tensors run on tcgen05 / TMEM when the group size tiles the 128 accumulator rows; the
-  // warp-MMA kernel takes the other group sizes and fp32.  CUDA_LLM_PREFILL_KERNEL=warp_mma forces the
-  // latter (A/B measurements).
+  // 16-bit tensors run on tcgen05 / TMEM (every group size); the other kernels take fp32.
+  // CUDA_LLM_PREFILL_KERNEL=warp_mma forces the warp-MMA kernel (A/B measurements).
   static const bool force_warp_mma = [] {
     const char* v = getenv("CUDA_LLM_PREFILL_KERNEL");
     return v && strcmp(v, "warp_mma") == 0;

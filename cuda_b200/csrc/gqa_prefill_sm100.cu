@@ -418,12 +418,15 @@ static bool encode_bhsd(EncodeTiledFn enc, CUtensorMap* m, const void* p, long l
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Whether the tcgen05 kernel takes this shape: 16-bit tensors, a group of 1, 2, 4, 8 or a multiple of 8.
+// Query heads of a KV head that share a CTA: the largest of 8, 4, 2, 1 that divides the group (a group of 3, 5 or
+// 7 heads runs one head per CTA like MHA, a group of 6 two, a group of 12 four).
+static int heads_per_cta(int group) { return group % 8 == 0 ? 8 : group % 4 == 0 ? 4 : group % 2 == 0 ? 2 : 1; }
+
+// Whether the tcgen05 kernel takes this shape: 16-bit tensors, any group size.
 bool gqa_prefill_sm100_supported(int Hq, int Hkv, int D, int dtype) {
   if (dtype != CUDA_LLM_F16 && dtype != CUDA_LLM_BF16) return false;
   if (D != 64 && D != 128) return false;
-  const int group = Hq / Hkv;
-  return group == 1 || group == 2 || group == 4 || group % 8 == 0;
+  return Hkv > 0 && Hq % Hkv == 0;
 }
 
 // dtype: the 16-bit type of q, k, v; out_dtype: any of the three output types.
@@ -434,7 +437,7 @@ cudaError_t run_gqa_prefill_sm100(const void* q, const void* k, const void* v, v
   if (!enc) return cudaErrorNotSupported;
   Prefill100Args a;
   a.out = out; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.group = Hq / Hkv;
-  a.gsz = a.group < 8 ? a.group : 8;
+  a.gsz = heads_per_cta(a.group);
   a.causal = causal ? 1 : 0;
   a.bf16 = dtype == CUDA_LLM_BF16 ? 1 : 0;
   a.out_dtype = out_dtype;

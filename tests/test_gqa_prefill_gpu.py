@@ -33,10 +33,12 @@ def test_reference_gqa_cases(ops, golden, case):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("b,hq,hkv,s,d,causal", [(2, 32, 8, 300, 128, True), (1, 12, 4, 129, 64, True),
                                                  (3, 16, 1, 64, 128, False), (1, 6, 2, 1, 64, True),
-                                                 (2, 5, 5, 77, 128, True), (1, 24, 2, 200, 64, False)])
+                                                 (2, 5, 5, 77, 128, True), (1, 24, 2, 200, 64, False),
+                                                 (1, 10, 2, 700, 128, True), (1, 14, 2, 513, 128, True),
+                                                 (2, 12, 2, 260, 64, True)])
 def test_gqa_shapes(ops, dtype, b, hq, hkv, s, d, causal):
-    """Group sizes 1..16 (more than eight heads per KV head are split over CTAs), ragged lengths, all
-    three dtypes of the reference's instantiations."""
+    """Group sizes 1..16 (the heads of a group share a CTA eight, four, two or one at a time, whichever divides
+    the group), ragged lengths, all three dtypes of the reference's instantiations."""
     g = torch.Generator().manual_seed(b * 1000 + s)
     q = torch.randn(b, hq, s, d, generator=g).to(dtype)
     k = torch.randn(b, hkv, s, d, generator=g).to(dtype)
