@@ -71,6 +71,70 @@ merge_partials_kernel(const float* __restrict__ parts_out, const float* __restri
   if (lse && lane == 0) lse[row] = wsum > 0.f ? mu + logf(wsum) : -__builtin_huge_valf();
 }
 
+// The same merge for rows with many parts (a few long sequences cut into hundreds of chunks): one block of W
+// warps per row, warp w takes parts w, w + W, ...
+template <int D, int W>
+__global__ void __launch_bounds__(32 * W)
+merge_partials_wide_kernel(const float* __restrict__ parts_out, const float* __restrict__ parts_lse, size_t out_stride,
+                           size_t lse_stride, int num_parts, long long rows, void* out, int out_dtype, float* lse) {
+  constexpr int VPL = D / 32;
+  constexpr float LOG2E = 1.4426950408889634f;
+  constexpr float NEG_INF = -__builtin_huge_valf();
+  __shared__ float s_max[W];
+  __shared__ float s_sum[W];
+  __shared__ float s_acc[W][D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = blockIdx.x;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  float mx = NEG_INF;
+  for (int p = threadIdx.x; p < num_parts; p += 32 * W) mx = fmaxf(mx, parts_lse[(size_t)p * lse_stride + row]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) s_max[warp] = mx;
+  __syncthreads();
+  mx = s_max[0];
+#pragma unroll
+  for (int w = 1; w < W; ++w) mx = fmaxf(mx, s_max[w]);
+  const float mu = (mx == NEG_INF) ? 0.f : mx;
+  float acc[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) acc[v] = 0.f;
+  float wsum = 0.f;
+  // 32 of the warp's parts at a time: one weight per lane, then every lane walks their rows
+  for (int base = warp; base < num_parts; base += 32 * W) {
+    const int mine = base + W * lane;
+    const float wl = mine < num_parts ? fast_exp2((parts_lse[(size_t)mine * lse_stride + row] - mu) * LOG2E) : 0.f;
+    const int cnt = min(32, (num_parts - base + W - 1) / W);
+#pragma unroll 8
+    for (int j = 0; j < cnt; ++j) {
+      const float w = __shfl_sync(0xffffffffu, wl, j);
+      wsum += w;
+      const float* po = parts_out + (size_t)(base + W * j) * out_stride + (size_t)row * D + lane * VPL;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) acc[v] = fmaf(w, po[v], acc[v]);
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) s_acc[warp][lane * VPL + v] = acc[v];
+  if (lane == 0) s_sum[warp] = wsum;
+  __syncthreads();
+  if (warp == 0) {
+    wsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) wsum += s_sum[w];
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const int d = lane * VPL + v;
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < W; ++w) sum += s_acc[w][d];
+      store_out_elem(out, out_dtype, (size_t)row * D + d, sum * inv);
+    }
+    if (lse && lane == 0) lse[row] = wsum > 0.f ? mu + logf(wsum) : NEG_INF;
+  }
+}
+
 cudaError_t launch_merge_partials_strided(const float* parts_out, const float* parts_lse, size_t part_stride,
                                           int num_parts, long long rows, int head_dim, void* out, int out_dtype,
                                           float* lse, cudaStream_t st) {
@@ -99,6 +163,15 @@ cudaError_t launch_merge_partials(const float* parts_out, const float* parts_lse
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (num_parts > 64) {  // many parts per row: a block of 16 warps per row
+    cfg.gridDim = dim3((unsigned)rows);
+    cfg.blockDim = dim3(512);
+    if (head_dim == 64)
+      return cudaLaunchKernelEx(&cfg, merge_partials_wide_kernel<64, 16>, parts_out, parts_lse, os, ls, num_parts, rows, out,
+                                out_dtype, lse);
+    return cudaLaunchKernelEx(&cfg, merge_partials_wide_kernel<128, 16>, parts_out, parts_lse, os, ls, num_parts, rows, out,
+                              out_dtype, lse);
+  }
   if (head_dim == 64)
     return cudaLaunchKernelEx(&cfg, merge_partials_kernel<64>, parts_out, parts_lse, os, ls, num_parts, rows, out,
                               out_dtype, lse);

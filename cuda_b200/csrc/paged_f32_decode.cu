@@ -47,7 +47,7 @@ cudaError_t launch_merge_partials(const float*, const float*, int, long long, in
 constexpr int kF32Warps = 7;    // workers per CTA
 constexpr int kF32Slots = 4;    // ring slots per worker (K, V, K, V)
 constexpr int kF32MinChunk = 8;       // pages per item, lower and upper bound
-constexpr int kF32MaxSplits = 256;    // partial results per query row
+constexpr int kF32MaxSplits = 512;    // partial results per query row
 constexpr long long kF32TargetItems = 8192;
 
 struct F32TensorMaps {

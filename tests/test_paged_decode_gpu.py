@@ -227,19 +227,20 @@ def test_split_invariance_and_merge(ops):
         assert (o.float() - outs[0].float()).abs().max() <= 2e-2
 
 
-def test_merge_partials_matches_oracle(ops):
+@pytest.mark.parametrize("P,rows,d", [(5, 37, 128), (64, 9, 64), (65, 9, 128), (300, 6, 64), (513, 3, 128)])
+def test_merge_partials_matches_oracle(ops, P, rows, d):
+    """Few parts (a warp per row) and many (a block of 16 warps per row, warp w taking parts w, w + 16, ...)."""
     torch.manual_seed(1)
-    P, rows, d = 5, 37, 128
     o = torch.randn(P, rows, d)
     l = torch.randn(P, rows) * 3
     l[2, :5] = float("-inf")
-    l[:, 7] = float("-inf")
+    l[:, rows - 1] = float("-inf")
     ro, rl = O.merge_partials(o, l)
     go, gl = ops.merge_partials(o.cuda(), l.cuda(), return_lse=True)
     assert (go.cpu() - ro).abs().max() < 1e-5
     fin = torch.isfinite(rl)
     assert torch.equal(torch.isfinite(gl.cpu()), fin) and (gl.cpu()[fin] - rl[fin]).abs().max() < 1e-5
-    assert (go.cpu()[7] == 0).all()
+    assert (go.cpu()[rows - 1] == 0).all()
 
 
 def test_bad_block_index_is_reported_not_faulted(ops):
