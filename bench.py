@@ -430,7 +430,8 @@ def build_leg(B, cfg_id, args, batch=None, ctx_scale=1.0):
         kw.update(ctx_scale=ctx_scale / world, seed=1000 + cfg_id + 7919 * rank)
         split_ctx = world > 1
     elif cfg_id == 5:
-        parallelism = f"sequence-sharded x{world}, dealt longest-first by context length (no collective)"
+        parallelism = (f"sequence-sharded x{world}, dealt heaviest-first by context length x row weight "
+                       "(2 for more than 8 query rows per KV head; no collective)")
         if world > 1:
             kw.update(batch=(batch or 256), len_seed=1005, deal=(world, rank))
     else:

@@ -28,17 +28,32 @@ from .workloads import DecodeWorkload, SCALE_NONE, SCALE_PER_HEAD
 # --------------------------------------------------------------------------------------
 # partition plans (pure integer logic)
 # --------------------------------------------------------------------------------------
-def shard_sequences(context_lens: Sequence[int], world: int) -> List[List[int]]:
-    """Deal sequences to ``world`` ranks, longest first onto the least loaded rank (LPT), so that
-    every rank streams about the same number of KV bytes.  Returns the sequence ids per rank, each
-    list in ascending order."""
-    loads = [0] * world
+def shard_sequences(context_lens: Sequence[int], world: int,
+                    weights: Optional[Sequence[float]] = None) -> List[List[int]]:
+    """Deal sequences to ``world`` ranks, heaviest first onto the least loaded rank (LPT), so that
+    every rank has about the same work.  The work of a sequence is its context length (the KV bytes it
+    streams), or ``weights[s]`` where the caller knows better: the 8-bit decode kernel computes every
+    stage of a sequence with more than 8 query rows per KV head twice (one row half per warp of a pair),
+    so a router that knows the query lengths passes ``context_len * (2 if group * q_len > 8 else 1)``.
+    Returns the sequence ids per rank, each list in ascending order."""
+    cost = [max(float(w), 0.0) for w in (context_lens if weights is None else weights)]
+    if len(cost) != len(context_lens):
+        raise ValueError("weights must have one entry per sequence")
+    loads = [0.0] * world
     out: List[List[int]] = [[] for _ in range(world)]
-    for s in sorted(range(len(context_lens)), key=lambda i: (-int(context_lens[i]), i)):
+    for s in sorted(range(len(cost)), key=lambda i: (-cost[i], i)):
         r = min(range(world), key=lambda i: (loads[i], i))
         out[r].append(s)
-        loads[r] += max(int(context_lens[s]), 0)
+        loads[r] += cost[s]
     return [sorted(x) for x in out]
+
+
+def decode_cost_weights(context_lens: Sequence[int], q_lens: Optional[Sequence[int]], group: int) -> List[float]:
+    """Work of each sequence for ``shard_sequences``: its context length, doubled where ``group * q_len``
+    exceeds the 8 rows one warp of the decode kernel handles."""
+    if q_lens is None:
+        return [float(max(int(c), 0)) for c in context_lens]
+    return [float(max(int(c), 0)) * (2.0 if group * int(q) > 8 else 1.0) for c, q in zip(context_lens, q_lens)]
 
 
 def shard_kv_heads(num_kv_heads: int, world: int, rank: int) -> Tuple[int, int]:

@@ -268,19 +268,20 @@ def make_config(config_id: int, device="cpu", *, batch: Optional[int] = None,
     ``head_shards`` builds one KV-head shard (1/head_shards of the KV and query heads);
     ``len_seed`` fixes the length draw independently of the data seed (ranks of a sharded run
     share the lengths and differ in the data); ``deal = (world, rank)`` draws the lengths of the
-    whole job (``batch`` sequences in total) and keeps the sequences that longest-first dealing
-    balanced by context length (``sharding.shard_sequences``) gives to ``rank``."""
+    whole job (``batch`` sequences in total) and keeps the sequences that heaviest-first dealing
+    (``sharding.shard_sequences``: by context length, for config 5 by context length times the row
+    weight of the query length) gives to ``rank``."""
     seed = 1000 + config_id if seed is None else seed
     cg = torch.Generator()
     cg.manual_seed(seed if len_seed is None else len_seed)
     hs = head_shards
     sc = lambda x: max(1, int(round(x * ctx_scale)))
 
-    def dealt(lens, *extras):
+    def dealt(lens, *extras, weights=None):
         if deal is None:
             return (lens,) + extras
         from .sharding import shard_sequences
-        ids = shard_sequences(lens, deal[0])[deal[1]]
+        ids = shard_sequences(lens, deal[0], weights)[deal[1]]
         return tuple([x[i] for i in ids] for x in (lens,) + extras)
 
     if config_id == 1:
@@ -315,7 +316,8 @@ def make_config(config_id: int, device="cpu", *, batch: Optional[int] = None,
         lens = _lognormal_lens(b, 2048 * ctx_scale, 1.0, max(4, sc(16)), sc(16384), cg)
         ql = torch.where(torch.rand(b, generator=cg) < 0.7, 1, 4).tolist()
         ql = [min(q, l) for q, l in zip(ql, lens)]
-        lens, ql = dealt(lens, ql)
+        from .sharding import decode_cost_weights
+        lens, ql = dealt(lens, ql, weights=decode_cost_weights(lens, ql, 32 // 8))
         return build_workload("cfg5_continuous_batching_mx8k_mx4v", context_lens=lens, q_lens=ql,
                               num_q_heads=32, num_kv_heads=8, head_dim=128, page_size=16,
                               q_dtype=torch.bfloat16, k_format=KV_FP8_E4M3, v_format=KV_FP4_E2M1,

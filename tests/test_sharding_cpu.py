@@ -14,6 +14,25 @@ from helpers import to_oracle
 from oracle import paged_decode_oracle as O
 
 
+def test_shard_sequences_by_cost_weights():
+    """With query lengths known, the work of a sequence is its context length times 2 where group * q_len exceeds
+    8 rows: dealing by that weight balances the ranks' cost, dealing by length alone does not."""
+    import random
+    rnd = random.Random(3)
+    lens = [rnd.randint(16, 16384) for _ in range(256)]
+    qls = [1 if rnd.random() < 0.7 else 4 for _ in lens]
+    w = S.decode_cost_weights(lens, qls, group=4)
+    assert w[0] == lens[0] * (2 if qls[0] == 4 else 1)
+    for world in (2, 4, 8):
+        by_cost = S.shard_sequences(lens, world, w)
+        assert sorted(i for p in by_cost for i in p) == list(range(256))
+        loads = [sum(w[i] for i in p) for p in by_cost]
+        assert max(loads) <= 1.01 * sum(loads) / world
+        by_len = [sum(w[i] for i in p) for p in S.shard_sequences(lens, world)]
+        assert max(loads) <= max(by_len)
+    assert S.decode_cost_weights([5, 7], None, 4) == [5.0, 7.0]
+
+
 def test_shard_sequences_balances_and_covers():
     lens = [8192, 100, 4000, 4100, 50, 7000, 1, 0, 3000]
     for world in (1, 2, 4, 8):
