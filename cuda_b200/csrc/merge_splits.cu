@@ -8,10 +8,22 @@ template <int D>
 cudaError_t launch_merge_splits(const DecodeArgs& a, int page, int decode_grid, cudaStream_t st) {
   const long long blocks = (long long)a.S * a.Hq;
   if (blocks == 0) return cudaSuccess;
-  // few sequences cut across many CTAs leave many results per row: more warps per block then
-  const bool many_parts = (long long)decode_grid >= 4LL * a.S * a.n_hg;
+  // few sequences cut across many CTAs leave many results per row: more warps per block then.  (Blocks of 16
+  // warps fit four to an SM and the kernel is a chain of dependent loads, so they are taken only where a row
+  // really has that many parts: about grid / (S n_hg) + 2 CTAs per row, SUBS results each, two for helper pairs;
+  // measured: 48 parts per row take 16 us with 4 warps and 29 us with 16.)
+  const long long est_parts = ((long long)decode_grid / ((long long)a.S * a.n_hg) + 2) * a.SUBS *
+                              ((a.helper_pairs && a.rows_max == 16) ? 2 : 1);
+  const bool many_parts = est_parts > 128;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)blocks);
+  // y: the query tokens of a sequence (blocks beyond its q_len return at once), so that the rows of a
+  // multi-token query are merged side by side instead of one after the other
+  // (as long as that keeps the grid to about 8192 blocks: with many sequences the blocks that find no token
+  // of their own cost more than the serial loop)
+  const int q_max = a.cuq ? (a.rows_max / a.group > 1 ? a.rows_max / a.group : 1) : 1;
+  long long q_par = 8192 / blocks;
+  q_par = q_par < 1 ? 1 : q_par > q_max ? q_max : q_par;
+  cfg.gridDim = dim3((unsigned)blocks, (unsigned)q_par);
   cfg.blockDim = dim3(many_parts ? 512 : 128);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;

@@ -1225,7 +1225,7 @@ paged_decode_kernel(const __grid_constant__ DecodeArgs a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------
-// Split merge: one block of W warps per (sequence, query head); the warps share the partials of every
+// Split merge: one block of W warps per (sequence, query head, query token); the warps share the partials of every
 // CTA and sub-tile warp that touched the sequence and combine them (algebra of
 // combine_softmax_state, fused_online_softmax_kernel.cuh:40-49 in the reference project, in
 // base 2).  Launched as a programmatic dependent of the decode kernel: blocks may start early
@@ -1249,8 +1249,9 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
   const int sh = s * a.n_hg + hg;
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (qlen <= 0) return;
+  if (qlen <= 0 || (int)blockIdx.y >= qlen) return;
   if (ctx <= 0) {
+    if (blockIdx.y != 0) return;
     for (int j = warp; j < qlen; j += W) {
       const size_t row = (size_t)(qbase + j) * a.Hq + qh;
 #pragma unroll
@@ -1268,7 +1269,7 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
   const bool entry_ok = cta_first >= 0 && n_cta >= 1 && n_cta <= a.grid && cta_first <= a.grid - n_cta &&
                         (long long)sh + cta_first + n_cta <= (long long)a.n_slots;
   if (!entry_ok) {
-    if (threadIdx.x == 0) atomicOr(a.status, CUDA_LLM_ST_INCOMPLETE);
+    if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(a.status, CUDA_LLM_ST_INCOMPLETE);
     n_cta = 0;
     cta_first = 0;
   } else if (direct) {
@@ -1279,7 +1280,8 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
   const int n_parts = n_cta * a.SUBS * dup;
   const size_t pstride = (size_t)a.HG * a.rows_max;  // rows between consecutive sub-tile results
   auto part_row = [&](size_t row0, int p) -> size_t { return row0 + (size_t)(p / dup) * pstride + (size_t)(p % dup) * 8; };
-  for (int j = 0; j < qlen; ++j) {
+  for (int j = (int)blockIdx.y; j < qlen; j += (int)gridDim.y) {  // blockIdx.y: a share of the query tokens
+    if (j != (int)blockIdx.y) __syncthreads();                  // the shared arrays are reused
     const int r = j * a.group + i;
     const size_t row = (size_t)(qbase + j) * a.Hq + qh;
     const size_t row0 = (((size_t)(sh + cta_first) * a.SUBS) * a.HG + h) * a.rows_max + r;
@@ -1336,7 +1338,6 @@ merge_splits_kernel(const __grid_constant__ DecodeArgs a, int page) {
       if (a.lse && lane == 0)
         a.lse[row] = wsum > 0.f ? (mu + log2f(wsum)) * 0.69314718055994531f : NEG_INF;
     }
-    __syncthreads();
   }
 }
 
