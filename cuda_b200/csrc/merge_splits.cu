@@ -24,7 +24,8 @@ cudaError_t launch_merge_splits(const DecodeArgs& a, int page, int decode_grid, 
   long long q_par = 8192 / blocks;
   q_par = q_par < 1 ? 1 : q_par > q_max ? q_max : q_par;
   cfg.gridDim = dim3((unsigned)blocks, (unsigned)q_par);
-  cfg.blockDim = dim3(many_parts ? 512 : 128);
+  const bool some_parts = !many_parts && est_parts > 32;  // 8 warps: eight such blocks still fit an SM
+  cfg.blockDim = dim3(many_parts ? 512 : some_parts ? 256 : 128);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -33,6 +34,7 @@ cudaError_t launch_merge_splits(const DecodeArgs& a, int page, int decode_grid, 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (many_parts) return cudaLaunchKernelEx(&cfg, merge_splits_kernel<D, 16>, a, page);
+  if (some_parts) return cudaLaunchKernelEx(&cfg, merge_splits_kernel<D, 8>, a, page);
   return cudaLaunchKernelEx(&cfg, merge_splits_kernel<D, 4>, a, page);
 }
 template cudaError_t launch_merge_splits<64>(const DecodeArgs&, int, int, cudaStream_t);
