@@ -253,15 +253,18 @@ static int make_layout(int S, int Hq, int Hkv, int D, int page, int max_q_len, i
 
 // Work layout of the tcgen05 decode kernel (paged_decode_sm100.cu): two adjacent KV heads per unit, tiles of
 // 128 tokens, one result of `rows_max` rows per (CTA, sequence, KV head).
+// `q_lens_given`: the call carries cu_q_lens.  A query may then be longer than max_q_len declares and still be
+// served as long as it fits the rows of the launch, so the four-row variant is for calls without query lengths only
+// (one token per sequence); with them the launch has the 8 or 16 rows the default kernel would have.
 static int make_layout_sm100(int S, int Hq, int Hkv, int D, int page, int max_q_len, int v_format, int scale_mode,
-                             int num_ctas, Layout& L) {
+                             int num_ctas, bool q_lens_given, Layout& L) {
   if (S < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || Hkv % 2 || D != 128 || page != 16) return CUDA_LLM_EINVAL;
   const int group = Hq / Hkv;
   if (max_q_len < 1) max_q_len = 1;
   if (group * max_q_len > 16) return CUDA_LLM_EINVAL;
   memset(&L, 0, sizeof(L));
   L.NT = (group * max_q_len <= 8) ? 1 : 2;
-  L.rows_max = (group * max_q_len <= 4) ? 4 : 8 * L.NT;  // the kernel's padded row counts: 4, 8, 16
+  L.rows_max = (group * max_q_len <= 4 && !q_lens_given) ? 4 : 8 * L.NT;  // the kernel's padded row counts: 4, 8, 16
   L.HG = 2;
   L.SUBS = 1;
   L.tok_stage = 128;
@@ -365,7 +368,7 @@ size_t cuda_llm_paged_decode_workspace_bytes(int32_t num_seqs, int32_t num_q_hea
     need = L.ws_total;
   // and the tcgen05 kernel's one-head units
   if (make_layout_sm100(num_seqs, num_q_heads, num_kv_heads, head_dim, page_size, max_q_len, CUDA_LLM_KV_FP8_E4M3,
-                        CUDA_LLM_SCALE_PER_TOKEN, num_ctas, L) == CUDA_LLM_OK && L.ws_total > need)
+                        CUDA_LLM_SCALE_PER_TOKEN, num_ctas, true, L) == CUDA_LLM_OK && L.ws_total > need)
     need = L.ws_total;
   return need;
 }
@@ -404,7 +407,7 @@ int cuda_llm_paged_decode(const CudaLlmPagedDecodeParams* p, void* stream) {
   const bool sm100 = decode_sm100_wanted(p);
   if (sm100) {
     rc = make_layout_sm100(p->num_seqs, p->num_q_heads, p->num_kv_heads, p->head_dim, p->page_size, p->max_q_len,
-                           p->v_format, p->scale_mode, p->num_ctas, L);
+                           p->v_format, p->scale_mode, p->num_ctas, p->cu_q_lens != nullptr, L);
     if (rc != CUDA_LLM_OK) return rc;
   }
   if (!p->workspace || p->workspace_bytes < L.ws_total)

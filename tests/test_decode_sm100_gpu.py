@@ -78,6 +78,20 @@ def test_multi_token_queries_causal(ops, scale_mode):
     assert_parity(out, oracle_out(wl), torch.bfloat16, "q_len mix")
 
 
+def test_query_longer_than_declared_still_fits_the_rows(ops):
+    """A call with query lengths whose max_q_len under-declares them: a query of two tokens and a group of four
+    fits the 8 rows the launch has (the four-row variant is for calls without query lengths only)."""
+    wl = _workload([300, 40, 1000, 17], q_lens=[2, 1, 2, 2], hq=8, hkv=2, seed=31)
+    ref = oracle_out(wl)
+    g = wl.to("cuda")
+    before = _launches(ops)
+    out = ops.fp8_paged_attention_forward(g.query, g.key_cache, g.value_cache, g.k_scale, g.v_scale, g.block_tables,
+                                          g.context_lens, g.softmax_scale, cu_q_lens=g.cu_q_lens, max_q_len=1,
+                                          check_status=True, flags=ops.L.FLAG_TCGEN05)
+    assert _launches(ops) == before + 1
+    assert_parity(out, ref, torch.bfloat16, "q_len 2 with max_q_len 1")
+
+
 @pytest.mark.parametrize("hq,hkv", [(64, 8), (16, 4)])
 def test_mx_block_scales(ops, hq, hkv):
     wl = _workload([1, 31, 200, 1500, 77, 640], hq=hq, hkv=hkv, scale_mode="mx_e8m0", seed=21, mx_exponent_range=(-4, 4))

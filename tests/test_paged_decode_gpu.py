@@ -392,6 +392,9 @@ def test_reference_cxx_dispatcher_paged_and_decode(ops, golden):
 def test_segment_table_matches_host_plan(ops, hkv, q4, num_ctas):
     """The (first CTA, number of CTAs) the kernel records per (sequence, head group) is exactly what
     the host restatement of the plan predicts: integer parity of the range partition."""
+    import os
+    if os.environ.get("CUDA_LLM_DECODE_KERNEL") == "tcgen05":
+        pytest.skip("the host restatement describes the default kernel's stage layout")
     import partition_plan as P
     W = _W()
     g = torch.Generator().manual_seed(51)
