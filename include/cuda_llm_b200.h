@@ -188,7 +188,10 @@ int cuda_llm_decode_status(void* workspace, void* stream, uint32_t* status_out);
 
 /* ---- unquantised KV ------------------------------------------------------------------- */
 /* Workspace for the two entry points below; max_tokens = max_blocks_per_seq * page_size (paged)
- * or seq_len (contiguous). */
+ * or seq_len (contiguous).  The partial results start behind the 256-byte header; of the header the
+ * calls use the status word (an out-of-range block index of an fp32 cache is replaced by block 0 and
+ * reported as CUDA_LLM_ST_BAD_BLOCK) and, for fp32 tensors, a work counter at byte 128 that every
+ * call resets itself, so the buffer may be the one cuda_llm_paged_decode uses on the same stream. */
 size_t cuda_llm_dense_decode_workspace_bytes(int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads,
                                              int32_t head_dim, int32_t max_tokens);
 
