@@ -184,7 +184,9 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
       mbar_init(sb0 + C::kBarPFull + 8 * g, 4);
       mbar_init(sb0 + C::kBarPvDone + 8 * g, 1);
       mbar_init(sb0 + C::kBarQReady + 8 * g, 1);
-      mbar_init(sb0 + C::kBarQFree + 8 * g, 1);
+      // freed by the MMA warp (its products with the operand are done) and by every softmax thread (it has read
+      // the segment's row factors, which live in the same buffer)
+      mbar_init(sb0 + C::kBarQFree + 8 * g, 1 + 256);
       *reinterpret_cast<volatile uint32_t*>(smem + C::kGrp + g * C::kGrpBytes + 2192) = 0;
     }
     *done_flag = 0;
@@ -633,6 +635,10 @@ paged_decode_sm100_kernel(const __grid_constant__ DecodeArgs a) {
           qsr[r] = qs[r];
           l_t[r] = 0.f;
         }
+        // this thread is done with the buffer: without this arrival the query warp, released by the MMA warp
+        // alone, could refill it (and complete q_ready a second time) while a group that lags two one-stage
+        // segments behind had not yet waited for the first completion, which it would then never see
+        if (!finished) mbar_arrive(sb0 + C::kBarQFree + 8 * qbi);
       }
       // ---- raw logits of this token: S accumulators -> x[r] (log2 domain, softmax scale applied)
       float x[RP];

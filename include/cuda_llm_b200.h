@@ -66,8 +66,7 @@ extern "C" {
                                     * other calls ignore the flag.  The environment variable
                                     * CUDA_LLM_DECODE_KERNEL=tcgen05 sets it for every call of the process.
                                     * Same results contract; measured slower than the default warp-MMA
-                                    * kernel on a B200, and seen to report CUDA_LLM_ST_TIMEOUT intermittently on batches of
-                                    * many sequences shorter than a 128-token tile: experimental, read the status word. */
+                                    * kernel on a B200, which is why it is opt-in. */
 
 #ifdef CUDA_LLM_DIAGNOSTICS /* honoured only by a library built with -DCUDA_LLM_DIAGNOSTICS */
 #define CUDA_LLM_FLAG_DIAG_NO_MATH 2 /* diagnostics: stream the pages but skip the attention math
