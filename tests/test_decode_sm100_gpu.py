@@ -136,6 +136,24 @@ def test_v_dequant_bit_exact(ops, e_lo, e_hi):
         assert torch.equal(out[s], want), (s, (out[s].float() - want.float()).abs().max())
 
 
+@pytest.mark.parametrize("scale_mode", ["per_token", "mx_e8m0"])
+@pytest.mark.parametrize("with_q_lens", [False, True])
+def test_many_one_stage_segments_on_few_ctas(ops, scale_mode, with_q_lens):
+    """Dozens of sequences shorter than one 128-token tile on 3 and 7 CTAs: every stage starts and ends a segment,
+    so the query warp runs two segments ahead of the softmax groups all the time.  (A group that lagged two such
+    segments behind used to miss a phase of the query barrier and give up; the buffer is now released by the
+    groups as well.)  Repeated, with the status word checked every time."""
+    lens = [40, 44, 874, 14, 29, 35, 360, 7, 99, 120, 5, 61, 33, 127, 128, 1, 90, 17, 64, 12] * 2
+    q_lens = [1] * len(lens) if with_q_lens else None
+    wl = _workload(lens, q_lens=q_lens, hq=2, hkv=2, scale_mode=scale_mode, seed=210)
+    ref = oracle_out(wl)
+    dev = wl.to("cuda")
+    for num_ctas in (7, 3):
+        for _ in range(15):
+            out = _run(ops, dev, num_ctas=num_ctas)            # check_status=True: a wait that ran out raises
+        assert_parity(out, ref, torch.bfloat16, f"{num_ctas} CTAs")
+
+
 def test_split_across_many_ctas_and_few(ops):
     """Two long sequences over all SMs (every segment straddles many CTAs) and the same on 3 CTAs."""
     wl = _workload([20000, 9000], hq=32, hkv=8, seed=31)
